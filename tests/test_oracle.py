@@ -1,0 +1,141 @@
+"""The numpy oracle against fixtures produced by the reference's kernels under the
+Triton interpreter (tests/golden/make_golden.py), and against the reference tests'
+own torch formulations (python/tutorials/06-fused-attention.py:533-559,
+python/tutorials/03-matrix-multiplication.py:357-371)."""
+import hashlib
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import ref_ops as R
+
+
+def sha(t):
+    return hashlib.sha256(t.contiguous().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+def f32(t):
+    return t.detach().to(torch.float32).numpy()
+
+
+@pytest.mark.parametrize("name", list(cases.MATMUL_CASES))
+def test_matmul_matches_interpreter(golden, name):
+    c = cases.MATMUL_CASES[name]
+    a, b = cases.matmul_inputs(c)
+    assert sha(a) == str(golden[f"matmul.{name}.sha_a"]) and sha(b) == str(golden[f"matmul.{name}.sha_b"])
+    got = R.matmul(f32(a), f32(b), activation=c.get("activation", ""))
+    want = golden[f"matmul.{name}.c"].astype(np.float32)
+    # same tile order and fp32 accumulation: differences are BLAS summation order only
+    np.testing.assert_allclose(got, want, rtol=1e-3, atol=1e-3)
+    assert (got != want).mean() < 0.02
+
+
+def test_matmul_c1_reference_test_tolerance():
+    # python/tutorials/03-matrix-multiplication.py:357-371 compares with torch.matmul at atol 1e-2;
+    # an fp16 ulp is 0.03 at |c| > 32, so a one-ulp rounding difference needs the rtol term too
+    a, b = cases.matmul_inputs(cases.MATMUL_CASES["c1_512"])
+    got = R.matmul(f32(a), f32(b))
+    want = torch.matmul(a.float(), b.float()).half().float().numpy()
+    np.testing.assert_allclose(got, want, atol=1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("name", list(cases.FP8_CASES))
+def test_fp8_matches_interpreter(golden, name):
+    c = cases.FP8_CASES[name]
+    a8, b8, sa, sb = cases.fp8_inputs(c)
+    assert sha(a8) == str(golden[f"fp8.{name}.sha_a"])
+    acc = R.matmul_fp8(a8.view(torch.uint8).numpy(), b8.view(torch.uint8).numpy(), out="fp32")
+    want = golden[f"fp8.{name}.acc"]
+    # python/test/unit/language/test_core.py:5172-5173 tolerance for e4m3
+    np.testing.assert_allclose(acc, want, rtol=1e-2, atol=1e-2)
+    rel = np.linalg.norm(acc - want) / np.linalg.norm(want)
+    assert rel < 1e-5
+    # decode table agrees with torch's e4m3fn
+    np.testing.assert_array_equal(R.decode_e4m3(a8.view(torch.uint8).numpy()), a8.float().numpy())
+
+
+def test_bf16_rounding_matches_torch():
+    x = torch.randn(100000, generator=torch.Generator().manual_seed(7)) * 100
+    np.testing.assert_array_equal(R.round_bf16(x.numpy()), x.to(torch.bfloat16).float().numpy())
+
+
+FP16_ATTN = [n for n, c in cases.ATTN_CASES.items() if c["dtype"] == "fp16"]
+
+
+@pytest.mark.parametrize("name", FP16_ATTN)
+def test_attention_fwd_matches_interpreter(golden, name):
+    c = cases.ATTN_CASES[name]
+    q, k, v, do = cases.attn_inputs(c)
+    assert sha(q) == str(golden[f"attn.{name}.sha_q"])
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), c["causal"], c["sm_scale"], "fp16")
+    np.testing.assert_allclose(o, golden[f"attn.{name}.o"].astype(np.float32), atol=2e-3, rtol=0)
+    np.testing.assert_allclose(M, golden[f"attn.{name}.m"], atol=1e-4, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name", [n for n in FP16_ATTN if cases.ATTN_CASES[n].get("bwd")])
+def test_attention_bwd_matches_interpreter(golden, name):
+    c = cases.ATTN_CASES[name]
+    q, k, v, do = cases.attn_inputs(c)
+    o = golden[f"attn.{name}.o"].astype(np.float32)
+    M = golden[f"attn.{name}.m"]
+    dq, dk, dv = R.attention_bwd(f32(q), f32(k), f32(v), o, f32(do), M, c["sm_scale"], "fp16")
+    for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        want = golden[f"attn.{name}.{key}"].astype(np.float32)
+        np.testing.assert_allclose(got, want, atol=4e-3, rtol=1e-3)
+    # dense restatement agrees with the blocked one
+    dq2, dk2, dv2 = R.attention_bwd_full(f32(q), f32(k), f32(v), o, f32(do), M, c["sm_scale"], True, "fp16")
+    for a_, b_ in ((dq, dq2), (dk, dk2), (dv, dv2)):
+        np.testing.assert_allclose(a_, b_, atol=1e-2, rtol=1e-2)
+
+
+def test_attention_old_style_second_opinion(golden):
+    # python/test/unit/hopper/test_flashattention.py:361-403 (atol 1e-2)
+    name = "causal_d64"
+    c = cases.ATTN_CASES[name]
+    q, k, v, do = cases.attn_inputs(c)
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), True, c["sm_scale"], "fp16")
+    np.testing.assert_allclose(o, golden[f"attn_old.{name}.o"].astype(np.float32), atol=1e-2, rtol=0)
+    dq, dk, dv = R.attention_bwd(f32(q), f32(k), f32(v), o, f32(do), M, c["sm_scale"], "fp16")
+    for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+        np.testing.assert_allclose(got, golden[f"attn_old.{name}.{key}"].astype(np.float32), atol=1e-2, rtol=0)
+
+
+def _torch_reference(q, k, v, do, causal, sm_scale):
+    # the reference test's formulation: python/tutorials/06-fused-attention.py:533-549
+    q, k, v = (t.detach().clone().float().requires_grad_(True) for t in (q, k, v))
+    N = q.shape[2]
+    p = torch.matmul(q, k.transpose(2, 3)) * sm_scale
+    if causal:
+        p = p.masked_fill(~torch.tril(torch.ones(N, N, dtype=torch.bool)), float("-inf"))
+    p = torch.softmax(p, dim=-1)
+    o = torch.matmul(p, v)
+    o.backward(do.float())
+    return o.detach().numpy(), q.grad.numpy(), k.grad.numpy(), v.grad.numpy()
+
+
+@pytest.mark.parametrize("name", ["causal_d64", "causal_d64_bf16", "causal_d128"])
+def test_attention_against_torch_formulation(name):
+    c = cases.ATTN_CASES[name]
+    q, k, v, do = cases.attn_inputs(c)
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), c["causal"], c["sm_scale"], c["dtype"])
+    dq, dk, dv = R.attention_bwd(f32(q), f32(k), f32(v), o, f32(do), M, c["sm_scale"], c["dtype"])
+    ro, rdq, rdk, rdv = _torch_reference(q, k, v, do, c["causal"], c["sm_scale"])
+    tol = 1e-2 if c["dtype"] == "fp16" else 3e-2
+    for got, want in ((o, ro), (dq, rdq), (dk, rdk), (dv, rdv)):
+        np.testing.assert_allclose(got, want, atol=tol, rtol=1e-2)
+    # natural-log LSE = M * ln2
+    s = torch.matmul(q.float(), k.float().transpose(2, 3)) * c["sm_scale"]
+    s = s.masked_fill(~torch.tril(torch.ones(c["N"], c["N"], dtype=torch.bool)), float("-inf"))
+    np.testing.assert_allclose(M * np.log(2.0), torch.logsumexp(s, -1).numpy(), atol=1e-3, rtol=1e-4)
+
+
+def test_noncausal_bwd_full_against_torch():
+    c = dict(cases.ATTN_CASES["full_d64"])
+    q, k, v, do = cases.attn_inputs(c)
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), False, c["sm_scale"], "fp16")
+    dq, dk, dv = R.attention_bwd_full(f32(q), f32(k), f32(v), o, f32(do), M, c["sm_scale"], False, "fp16")
+    ro, rdq, rdk, rdv = _torch_reference(q, k, v, do, False, c["sm_scale"])
+    for got, want in ((o, ro), (dq, rdq), (dk, rdk), (dv, rdv)):
+        np.testing.assert_allclose(got, want, atol=1e-2, rtol=1e-2)
