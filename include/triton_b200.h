@@ -1,0 +1,71 @@
+/* triton_b200 — C ABI of the B200 (sm_100a) dense hot path: tiled matmul and flash attention.
+ *
+ * These entry points are what a host-language binding of the reference's op wrappers would
+ * call instead of the reference's JIT launcher.  Conventions (they mirror the reference's
+ * launcher, third_party/nvidia/backend/driver.py:274-325, and its ahead-of-time C template,
+ * python/triton/tools/compile.h:12-14 — `CUresult kernel(CUstream stream, args...)`):
+ *   - every pointer is a DEVICE pointer on the current device; the caller owns all memory,
+ *     the library allocates nothing and keeps no pointer after the call returns;
+ *   - launches are asynchronous on the given stream of the current device;
+ *   - strides are in ELEMENTS, as in the reference kernels' argument lists;
+ *   - the return value is 0 on success or a B200_ERR_* code; b200_last_error() gives the text
+ *     (the reference raises RuntimeError / assert at this point, driver.py:154-169).
+ * There is no CPU fallback: on a machine without an sm_100 device every compute entry point
+ * returns B200_ERR_DEVICE.
+ */
+#ifndef TRITON_B200_H_
+#define TRITON_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define B200_API __attribute__((visibility("default")))
+#else
+#define B200_API
+#endif
+
+typedef struct CUstream_st* b200_stream_t; /* a cudaStream_t / CUstream */
+
+enum b200_dtype { B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3 };
+enum b200_activation { B200_ACT_NONE = 0, B200_ACT_LEAKY_RELU = 1 };
+enum b200_error {
+  B200_OK = 0,
+  B200_ERR_ARG = 1,         /* shapes / dtypes / null pointers (the reference's Python asserts) */
+  B200_ERR_UNSUPPORTED = 2, /* layout the TMA path cannot address (alignment, stride) */
+  B200_ERR_CUDA = 3,        /* a CUDA runtime or driver call failed */
+  B200_ERR_DEVICE = 4,      /* no sm_100 device current */
+  B200_ERR_KERNEL = 5       /* a bounded device-side wait ran out (see b200_status) */
+};
+
+/* Library version, and the text of the last error on the calling thread. */
+B200_API int b200_version(void);
+B200_API const char* b200_last_error(void);
+
+/* Device status word of the current device: 0 when every kernel since the last clear ran
+ * to completion normally; otherwise the code of the first bounded wait that gave up
+ * (site | parity << 8 | block << 16).  Synchronises the device.  `clear` != 0 resets it. */
+B200_API int b200_status(unsigned* value, int clear);
+
+/* C[M,N] = act(A[M,K] @ B[K,N]) with fp32 accumulation.
+ * Replaces matmul_kernel + its launch in python/tutorials/03-matrix-multiplication.py:241-348
+ * (pointer, size and stride arguments in the same order; ACTIVATION becomes `activation`), and
+ * the fp8 matmul_kernel of python/test/unit/language/test_core.py:5110-5140 when in_dtype is
+ * B200_E4M3.  scale_a / scale_b are optional DEVICE pointers to one fp32 each: the epilogue
+ * multiplies the accumulator by (*scale_a) * (*scale_b) before the activation and the single
+ * rounding to out_dtype (per-tensor fp8 scaling; pass NULL for 1.0).
+ * A and B may each be row- or column-major (one of the two strides must be 1); C must have
+ * stride_cn == 1.  Base addresses and the non-unit strides must be multiples of 16 bytes.
+ * in_dtype: F16, BF16 or E4M3 (both operands); out_dtype: F16, BF16 or F32. */
+B200_API int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
+                int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
+                int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
+                const float* scale_a, const float* scale_b);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITON_B200_H_ */

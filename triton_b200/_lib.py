@@ -1,0 +1,58 @@
+"""ctypes binding of the C ABI declared in include/triton_b200.h.
+
+The shared library is built in-tree by `python -m triton_b200.build`.  There is no
+fallback: if the library is missing, loading raises; if no sm_100 device is current,
+every compute call raises RuntimeError with the library's error text.
+"""
+import ctypes
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libtriton_b200.so")
+
+F16, BF16, E4M3, F32 = 0, 1, 2, 3
+ACT_NONE, ACT_LEAKY_RELU = 0, 1
+
+_i, _i64, _p, _f = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
+
+# name -> argument types; every function returns int except where noted below
+SIGNATURES = {
+    "b200_version": [],
+    "b200_last_error": [],
+    "b200_status": [ctypes.POINTER(ctypes.c_uint), _i],
+    "b200_matmul": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p],
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m triton_b200.build` (needs nvcc); "
+                "there is no fallback implementation")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = ctypes.c_char_p if name == "b200_last_error" else ctypes.c_int
+        _lib = L
+    return _lib
+
+
+def last_error():
+    return lib().b200_last_error().decode()
+
+
+def check(code, what):
+    if code != 0:
+        raise RuntimeError(f"triton_b200 error [{what}] code {code}: {last_error()}")
+
+
+def status(clear=True):
+    """Device status word (0 = all kernels completed normally). Synchronises the device."""
+    v = ctypes.c_uint(0)
+    check(lib().b200_status(ctypes.byref(v), 1 if clear else 0), "status")
+    return v.value

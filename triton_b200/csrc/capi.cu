@@ -1,0 +1,180 @@
+// C ABI of the library (include/triton_b200.h): argument validation, per-device context,
+// error strings, TMA tensor-map encoding.  The kernels live in gemm.cu / attn_fwd.cu / attn_bwd.cu.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "host.h"
+
+namespace tb {
+
+// Status word read by b200_status(); kernels receive its device address as a parameter.
+__device__ unsigned g_status_word[4];
+
+namespace {
+thread_local char g_err[512] = "";
+std::mutex g_mu;
+DeviceCtx g_ctx[64];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+DeviceCtx* current_ctx() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    fail(B200_ERR_DEVICE, "no CUDA device current: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceCtx& c = g_ctx[dev];
+  if (c.device == dev) return &c;
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) {
+    fail(B200_ERR_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (prop.major != 10) {
+    fail(B200_ERR_DEVICE, "device %d is sm_%d%d; this library contains sm_100a code only", dev, prop.major,
+         prop.minor);
+    return nullptr;
+  }
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+      fail(B200_ERR_CUDA, "cuTensorMapEncodeTiled not available from the driver");
+      return nullptr;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  void* st = nullptr;
+  e = cudaGetSymbolAddress(&st, g_status_word);
+  if (e != cudaSuccess) {
+    fail(B200_ERR_CUDA, "cudaGetSymbolAddress(status): %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  c.status = static_cast<unsigned*>(st);
+  c.sm_count = prop.multiProcessorCount;
+  c.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+  c.device = dev;
+  return &c;
+}
+
+bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
+                 const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+  CUtensorMapDataType dt;
+  switch (dtype) {
+    case B200_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
+    case B200_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
+    case B200_E4M3: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case B200_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
+    default: fail(B200_ERR_ARG, "bad dtype %d", dtype); return false;
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) {
+    fail(B200_ERR_UNSUPPORTED, "tensor base address %p is not 16-byte aligned", base);
+    return false;
+  }
+  cuuint64_t d[5], s[4];
+  cuuint32_t b[5], es[5];
+  const int eb = dtype_bytes(dtype);
+  uint64_t extent = dims[0] * eb;
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    es[i] = 1;
+    if (i > 0) {
+      uint64_t st = strides_bytes[i - 1];
+      if (dims[i] == 1) st = (extent + 15) & ~15ull;  // stride of a size-1 dimension is never used
+      if (st % 16 != 0) {
+        fail(B200_ERR_UNSUPPORTED, "stride of dimension %d (%llu bytes) is not a multiple of 16 bytes", i,
+             (unsigned long long)st);
+        return false;
+      }
+      s[i - 1] = st;
+      extent = st * dims[i];
+    }
+    if (dims[i] == 0) {
+      fail(B200_ERR_ARG, "empty tensor dimension");
+      return false;
+    }
+  }
+  CUresult r = g_encode(out, dt, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fail(B200_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu)", (int)r,
+         rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 1));
+    return false;
+  }
+  return true;
+}
+
+}  // namespace tb
+
+using namespace tb;
+
+extern "C" {
+
+int b200_version(void) { return 100; }
+
+const char* b200_last_error(void) { return g_err; }
+
+int b200_status(unsigned* value, int clear) {
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+  unsigned v = 0;
+  e = cudaMemcpy(&v, ctx->status, sizeof(v), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
+  if (value) *value = v;
+  if (clear && v != 0) {
+    e = cudaMemset(ctx->status, 0, sizeof(unsigned));
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "status clear: %s", cudaGetErrorString(e));
+  }
+  return B200_OK;
+}
+
+int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K, int64_t stride_am,
+                int64_t stride_ak, int64_t stride_bk, int64_t stride_bn, int64_t stride_cm, int64_t stride_cn,
+                int in_dtype, int out_dtype, int activation, const float* scale_a, const float* scale_b) {
+  if (M < 0 || N < 0 || K < 0) return fail(B200_ERR_ARG, "negative dimension");
+  if (in_dtype != B200_F16 && in_dtype != B200_BF16 && in_dtype != B200_E4M3)
+    return fail(B200_ERR_ARG, "in_dtype must be F16, BF16 or E4M3");
+  if (out_dtype != B200_F16 && out_dtype != B200_BF16 && out_dtype != B200_F32)
+    return fail(B200_ERR_ARG, "out_dtype must be F16, BF16 or F32");
+  if (activation != B200_ACT_NONE && activation != B200_ACT_LEAKY_RELU) return fail(B200_ERR_ARG, "bad activation");
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  if (M == 0 || N == 0) return B200_OK;
+  if (!a || !b || !c) return fail(B200_ERR_ARG, "null pointer");
+  if (stride_cn != 1 && N != 1) return fail(B200_ERR_UNSUPPORTED, "C must have stride_cn == 1");
+  if (K == 0) {
+    // an empty sum: the reference's K loop does not run and the zero accumulator is stored
+    const int es = dtype_bytes(out_dtype);
+    cudaError_t e = cudaMemset2DAsync(c, (size_t)stride_cm * es, 0, (size_t)N * es, (size_t)M,
+                                      reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "memset: %s", cudaGetErrorString(e));
+    return B200_OK;
+  }
+  return launch_gemm(ctx, reinterpret_cast<cudaStream_t>(stream), a, b, c, M, N, K, stride_am, stride_ak, stride_bk,
+                     stride_bn, stride_cm, in_dtype, out_dtype, activation, scale_a, scale_b);
+}
+
+}  // extern "C"

@@ -1,0 +1,46 @@
+// Host-side helpers shared by the launchers: per-device context, error reporting and
+// TMA tensor-map encoding.  Internal to the library (the public surface is include/triton_b200.h).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/triton_b200.h"
+
+namespace tb {
+
+struct DeviceCtx {
+  int device = -1;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  unsigned* status = nullptr;  // device address of the status word (a __device__ symbol, never cudaMalloc'd)
+};
+
+// Context of the CURRENT device; created on first use.  Returns nullptr (and sets the error
+// string) when no usable sm_100 device is current.
+DeviceCtx* current_ctx();
+
+// Record an error message for b200_last_error() and return `code`.
+int fail(int code, const char* fmt, ...);
+
+// Encode a tiled tensor map.  dims/strides innermost first; strides_bytes[0] is the stride of
+// dimension 1 (dimension 0 is contiguous).  swizzle128: 128-byte swizzle when true, none otherwise.
+bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
+                 const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
+
+inline int dtype_bytes(int dt) {
+  switch (dt) {
+    case B200_F16:
+    case B200_BF16: return 2;
+    case B200_E4M3: return 1;
+    case B200_F32: return 4;
+    default: return 0;
+  }
+}
+
+// launchers implemented in the kernel translation units
+int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
+                int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t scm, int in_dtype, int out_dtype,
+                int activation, const float* scale_a, const float* scale_b);
+
+}  // namespace tb

@@ -1,0 +1,84 @@
+"""Host side of the hot path: the reference's op wrappers, same names and argument meaning.
+
+  matmul(a, b, activation="")                python/tutorials/03-matrix-multiplication.py:330-348
+                                             (stand-in for triton.ops.matmul(a, b),
+                                              python/test/regression/test_performance.py:73)
+  attention(q, k, v, causal, sm_scale)       python/tutorials/06-fused-attention.py:438-520
+                                             (triton.ops.attention, test_performance.py:194)
+
+Tensors are torch CUDA tensors (torch supplies device memory, streams and autograd
+plumbing); the arithmetic is done by the library's sm_100a kernels through the C ABI.
+"""
+import torch
+
+from . import _lib
+
+_DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
+if hasattr(torch, "float8_e4m3fn"):
+    _DT[torch.float8_e4m3fn] = _lib.E4M3
+_ACT = {"": _lib.ACT_NONE, None: _lib.ACT_NONE, "leaky_relu": _lib.ACT_LEAKY_RELU}
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise RuntimeError("triton_b200 ops take CUDA tensors; there is no CPU fallback")
+    dev = ts[0].device
+    for t in ts:
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+    return dev
+
+
+def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, out=None):
+    """C = act(A @ B) with fp32 accumulation.
+
+    Same contract as the reference wrapper: `a.shape[1] == b.shape[0]`, `a` contiguous, `b`
+    any 2-D tensor with one unit stride; returns a new [M, N] tensor (fp16 for fp16 inputs,
+    as the reference; bf16 for bf16 and fp8 inputs unless `out_dtype` says otherwise).
+    fp8-e4m3 inputs take optional per-tensor dequantisation scales (`scale_a`, `scale_b`:
+    python floats or 1-element fp32 CUDA tensors) that the epilogue multiplies in.
+    """
+    assert a.dim() == 2 and b.dim() == 2, "matmul takes 2-D tensors"
+    assert a.shape[1] == b.shape[0], "Incompatible dimensions"
+    assert a.is_contiguous(), "Matrix A must be contiguous"
+    assert a.dtype == b.dtype, "A and B must have the same dtype"
+    assert a.dtype in _DT and a.dtype != torch.float32, f"unsupported input dtype {a.dtype}"
+    assert activation in _ACT, f"unknown activation {activation!r}"
+    dev = _require_cuda(a, b)
+    M, K = a.shape
+    _, N = b.shape
+    if out_dtype is None:
+        out_dtype = torch.float16 if a.dtype == torch.float16 else torch.bfloat16
+    with torch.cuda.device(dev):
+        c = out if out is not None else torch.empty((M, N), device=dev, dtype=out_dtype)
+        assert c.shape == (M, N) and c.dtype == out_dtype and c.stride(1) == 1 or N == 1
+
+        def scale_ptr(s):
+            if s is None:
+                return None, None
+            if not torch.is_tensor(s):
+                s = torch.tensor([float(s)], dtype=torch.float32, device=dev)
+            assert s.dtype == torch.float32 and s.numel() == 1 and s.device == dev
+            return s.data_ptr(), s
+
+        pa, keep_a = scale_ptr(scale_a)
+        pb, keep_b = scale_ptr(scale_b)
+        code = _lib.lib().b200_matmul(
+            _stream(a), a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K,
+            a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
+            _DT[a.dtype], _DT[out_dtype], _ACT[activation], pa, pb)
+        _lib.check(code, "matmul")
+    return c
+
+
+def quantize_e4m3(x):
+    """Per-tensor amax scaling to the e4m3 range; returns (x8, scale) with x ~= x8 * scale.
+    `scale` is a 1-element fp32 tensor on x's device (no host synchronisation)."""
+    amax = x.abs().amax().float().clamp_min(1e-12)
+    s = 448.0 / amax
+    return (x.float() * s).to(torch.float8_e4m3fn), (1.0 / s).reshape(1)
