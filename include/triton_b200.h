@@ -65,6 +65,20 @@ B200_API int b200_matmul(b200_stream_t stream, const void* a, const void* b, voi
                 int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
                 const float* scale_a, const float* scale_b);
 
+/* Flash-attention forward: O = softmax(Q K^T * sm_scale, causal mask optional) V, and per-row
+ * statistics M[Z,H,N] (fp32) = base-2 log-sum-exp of the scores scaled by sm_scale * log2(e)
+ * (natural-log LSE = M * ln 2).
+ * Replaces _attn_fwd and its launch in _attention.forward,
+ * python/tutorials/06-fused-attention.py:98-187, 441-475 (Q, K, V, sm_scale, M, Out, the four
+ * stride quadruples, Z, H, N_CTX, HEAD_DIM, STAGE -> causal).
+ * q, k, v, o: [Z, H, N, D] of `dtype` (F16 or BF16) with element strides {z, h, n, d} each; the d
+ * stride must be 1 and the others multiples of 8 elements; D is 64 or 128; sm_scale > 0.
+ * m: contiguous [Z, H, N] fp32. */
+B200_API int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m,
+                                int Z, int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
+                                const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal,
+                                int dtype);
+
 #ifdef __cplusplus
 }
 #endif

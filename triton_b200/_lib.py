@@ -14,6 +14,7 @@ F16, BF16, E4M3, F32 = 0, 1, 2, 3
 ACT_NONE, ACT_LEAKY_RELU = 0, 1
 
 _i, _i64, _p, _f = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
+_s4 = ctypes.c_int64 * 4  # an element-stride quadruple {z, h, n, d}
 
 # name -> argument types; every function returns int except where noted below
 SIGNATURES = {
@@ -21,6 +22,7 @@ SIGNATURES = {
     "b200_last_error": [],
     "b200_status": [ctypes.POINTER(ctypes.c_uint), _i],
     "b200_matmul": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p],
+    "b200_attention_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
 }
 
 _lib = None
@@ -49,6 +51,10 @@ def last_error():
 def check(code, what):
     if code != 0:
         raise RuntimeError(f"triton_b200 error [{what}] code {code}: {last_error()}")
+
+
+def strides4(t):
+    return _s4(*t.stride())
 
 
 def status(clear=True):

@@ -1,0 +1,367 @@
+// Flash-attention forward for sm_100a.
+//
+// Computes what the reference's _attn_fwd / _attn_fwd_inner compute
+// (python/tutorials/06-fused-attention.py:25-187): O = softmax(Q K^T * sm_scale [causal]) V with
+// an online softmax in base 2 (scores scaled by sm_scale * log2 e, :160-161), fp32 statistics,
+// P rounded to the storage type before the second product (:66-69), O = acc / l rounded once,
+// and M = m + log2(l) per row (:183-187).  Masked scores contribute exactly 0.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong so that the
+// tensor pipe works on one tile while the other tile's softmax runs.
+//   warps 0-3 / 4-7   softmax of tile 0 / 1: one thread per row.  tcgen05.ld S (128 fp32), running
+//                     max and sum, exp2, P packed to 16 bit and written back over S in TMEM
+//                     (tcgen05.st) as the A operand of the second MMA.  The accumulator O is
+//                     rescaled lazily: only when the running max grew by more than 2^8 does the
+//                     warp multiply its O rows in TMEM (the reference rescales every step; the
+//                     result is the same up to fp32 rounding since P and l carry the same factor).
+//                     At the end: O / l -> storage type -> global, M -> global.
+//   warp 8            MMA issuer (one thread): S_i = Q_i K_j^T (operands in shared memory) and
+//                     O_i += P_i V_j (P from TMEM, V from shared memory, N-major).  MMAs of one
+//                     thread execute in issue order, which is what lets P alias S.
+//   warp 9            TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_i = first 64 columns of S_i.
+#include <cmath>
+#include <cstdlib>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int BLK = 128;           // rows of a Q tile and of a K/V block
+constexpr int FWD_THREADS = 320;   // 8 softmax warps + MMA warp + TMA warp
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdParams {
+  void* o;
+  float* m;  // [Z*H, N] base-2 log-sum-exp of the scaled scores
+  long long o_sz, o_sh, o_sn;  // element strides of O
+  int Z, H, N;
+  int causal;
+  float scale_log2;  // sm_scale * log2(e)
+  int num_qb;        // 256-row query blocks per head
+  unsigned* status;
+};
+
+template <int D>
+struct FwdCfg {
+  static constexpr int TILE_BYTES = BLK * D * 2;               // one Q tile or one K / V block
+  static constexpr int KV_STAGES = (D == 128) ? 4 : 8;
+  static constexpr int SUBTILES = D / 64;                      // 64-column (128-byte) boxes per tile
+  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 10) * 8 + 16 + 1024;
+};
+
+template <int D>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int z) {
+#pragma unroll
+  for (int b = 0; b < D / 64; ++b) tma_load_4d(dst + b * (BLK * 128), map, bar, b * 64, row0, h, z);
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  using Cfg = FwdCfg<D>;
+  constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  uint8_t* sq = smem;                // Q tiles 0, 1
+  uint8_t* skv = smem + 2 * TILE;    // ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(skv + NST * TILE);
+  uint64_t* q_full = bars;            // [2]
+  uint64_t* kv_full = bars + 2;       // [NST]
+  uint64_t* kv_empty = kv_full + NST; // [NST]
+  uint64_t* s_full = kv_empty + NST;  // [2] S_i(j) is in TMEM
+  uint64_t* p_full = s_full + 2;      // [2] P_i(j) is in TMEM (and O_i rescaled if it had to be)
+  uint64_t* o_full = p_full + 2;      // [2] last P V of tile i done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heavy (late) query blocks first within a head
+  const int qb = p.num_qb - 1 - (int)blockIdx.x;
+  const int zh = blockIdx.y, z = zh / p.H, h = zh % p.H;
+  const int nkv_all = (p.N + BLK - 1) / BLK;
+  // K/V blocks per tile: up to and including the block that holds the tile's diagonal when causal
+  const int n0 = p.causal ? min(2 * qb + 1, nkv_all) : nkv_all;
+  const int n1 = p.causal ? min(2 * qb + 2, nkv_all) : nkv_all;  // n0 <= n1 <= n0 + 1
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_full[i], 1);
+    }
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const uint32_t tm_s[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tm_o[2] = {tmem_base + 256, tmem_base + 384};
+
+  if (warp == 9) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      for (int i = 0; i < 2; ++i) {
+        mbar_expect_tx(&q_full[i], TILE);
+        load_tile<D>(sq + i * TILE, &tm_q, &q_full[i], qb * 256 + i * BLK, h, z);
+      }
+      uint32_t s = 0, ph = 0;
+      for (int j = 0; j < n1; ++j) {
+        for (int kv = 0; kv < 2; ++kv) {  // K_j then V_j
+          mbar_wait(&kv_empty[s], ph ^ 1u, p.status, SITE_FWD_KV_EMPTY);
+          mbar_expect_tx(&kv_full[s], TILE);
+          load_tile<D>(skv + s * TILE, kv == 0 ? &tm_k : &tm_v, &kv_full[s], j * BLK, h, z);
+          if (++s == NST) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr int FMT = BF16 ? 1 : 0;
+      constexpr uint32_t IDESC_S = make_idesc(FMT, FMT, 0, 0, 128, BLK);  // Q (K-major) x K (K-major)
+      constexpr uint32_t IDESC_O = make_idesc(FMT, FMT, 0, 1, 128, D);    // P (TMEM) x V (N-major)
+      const uint64_t dq0 = smem_desc_sw128(smem_u32(sq), 0, 1024);
+      const uint64_t dk0 = smem_desc_sw128(smem_u32(skv), 0, 1024);
+      const uint64_t dv0 = smem_desc_sw128(smem_u32(skv), BLK * 128, 1024);  // LBO: next 64-column box
+      uint32_t s = 0, ph = 0;  // ring position of the next unconsumed K / V block
+
+      auto issue_s = [&](int i, uint32_t stage) {  // S_i = Q_i K^T, D/16 MMAs
+        const uint64_t dq = dq0 + i * (TILE >> 4), dk = dk0 + stage * (TILE >> 4);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * ((BLK * 128) >> 4) + (kk & 3) * 2;  // 64-col box, 32 B per step
+          umma_ss<false>(tm_s[i], dq + off, dk + off, IDESC_S, kk != 0);
+        }
+        tc_commit(&s_full[i]);
+      };
+      auto issue_pv = [&](int i, uint32_t stage, uint32_t accum) {  // O_i (+)= P_i V, 8 MMAs of 16 kv rows
+        const uint64_t dv = dv0 + stage * (TILE >> 4);
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)
+          umma_ts_f16(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
+      };
+      auto advance = [&]() { if (++s == NST) { s = 0; ph ^= 1u; } };
+
+      // prologue: S_0(0), S_1(0) on K_0
+      mbar_wait(&kv_full[s], ph, p.status, SITE_FWD_KV_FULL);
+      mbar_wait(&q_full[0], 0, p.status, SITE_FWD_Q);
+      issue_s(0, s);
+      mbar_wait(&q_full[1], 0, p.status, SITE_FWD_Q);
+      issue_s(1, s);
+      tc_commit(&kv_empty[s]);
+      advance();
+      for (int j = 0; j < n1; ++j) {
+        const uint32_t vs = s, vph = ph;  // V_j
+        advance();
+        const uint32_t ks = s, kph = ph;  // K_{j+1} (if any)
+        const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
+        mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
+        if (j < n0) {
+          mbar_wait(&p_full[0], j & 1, p.status, SITE_FWD_P_FULL);
+          tc_fence_after();
+          issue_pv(0, vs, j > 0);
+          if (j == n0 - 1) tc_commit(&o_full[0]);
+          if (more0) {
+            mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+            issue_s(0, ks);
+          }
+        }
+        mbar_wait(&p_full[1], j & 1, p.status, SITE_FWD_P_FULL);
+        tc_fence_after();
+        issue_pv(1, vs, j > 0);
+        tc_commit(&kv_empty[vs]);
+        if (j == n1 - 1) tc_commit(&o_full[1]);
+        if (more1) {
+          mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+          issue_s(1, ks);
+          tc_commit(&kv_empty[ks]);
+          advance();
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int i = warp >> 2;                // tile
+    const uint32_t quarter = warp & 3u;     // TMEM lanes [32*quarter, +32)
+    const int row_in_tile = quarter * 32 + lane;
+    const int row = qb * 256 + i * BLK + row_in_tile;  // query index
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    const int nb = i ? n1 : n0;
+    const float scale = p.scale_log2;
+    float m_ref = -INFINITY, l = 0.f;
+
+    for (int j = 0; j < nb; ++j) {
+      mbar_wait(&s_full[i], j & 1, p.status, SITE_FWD_S_FULL);
+      tc_fence_after();
+      uint32_t r[BLK];
+#pragma unroll
+      for (int c = 0; c < BLK; c += 32) tmem_ld32(tm_s[i] + lane_addr + c, r + c);
+      tmem_ld_wait();
+      const int col0 = j * BLK;
+      const bool need_mask = (p.causal && col0 + BLK - 1 > qb * 256 + i * BLK) || (col0 + BLK > p.N);
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < BLK; ++c) {
+          const int col = col0 + c;
+          const bool ok = (col < p.N) && (!p.causal || col <= row);
+          const float v = ok ? __uint_as_float(r[c]) : -INFINITY;
+          r[c] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < BLK; ++c) mx = fmaxf(mx, __uint_as_float(r[c]));
+      }
+      const float m_new = fmaxf(m_ref, mx * scale);  // mx is finite: every row sees >= 1 valid column
+      // lazy rescale of the accumulator (warp-uniform decision: tcgen05.ld/st are warp collectives)
+      const bool grow = (m_new - m_ref) > kRescaleThreshold;  // true on the first block (m_ref = -inf)
+      if (__any_sync(0xffffffffu, grow)) {
+        const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
+        if (grow) { m_ref = m_new; l *= alpha; }
+        if (j > 0) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(tm_o[i] + lane_addr + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+            tmem_st32(tm_o[i] + lane_addr + c, o);
+          }
+        }
+      }
+      const float neg_m = -m_ref;
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < BLK; c += 32) {
+        uint32_t w[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const float p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
+          const float p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));
+          sum += p0 + p1;
+          w[k] = pack2<BF16>(p0, p1);
+        }
+        tmem_st16(tm_s[i] + lane_addr + (c >> 1), w);
+      }
+      l += sum;
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&p_full[i]);
+    }
+
+    // epilogue: O / l and M
+    mbar_wait(&o_full[i], 0, p.status, SITE_FWD_O_FULL);
+    tc_fence_after();
+    const float inv_l = 1.f / l;
+    const bool valid = row < p.N;
+    uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)z * p.o_sz + (long long)h * p.o_sh +
+                     (long long)row * p.o_sn;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.o) & 15) == 0) && ((p.o_sn & 7) == 0) && ((p.o_sh & 7) == 0) &&
+                        ((p.o_sz & 7) == 0);
+#pragma unroll 1
+    for (int c = 0; c < D; c += 32) {
+      uint32_t o[32];
+      tmem_ld32(tm_o[i] + lane_addr + c, o);
+      tmem_ld_wait();
+      if (valid) {
+        uint32_t w[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          w[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
+        if (vec_ok) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            orow[c + 2 * k] = (uint16_t)(w[k] & 0xFFFFu);
+            orow[c + 2 * k + 1] = (uint16_t)(w[k] >> 16);
+          }
+        }
+      }
+    }
+    if (valid) p.m[(long long)zh * p.N + row] = m_ref + log2f(l);
+  }
+
+  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D, bool BF16>
+int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, const CUtensorMap& tk,
+                 const CUtensorMap& tv, const FwdParams& p) {
+  static bool attr_done[64] = {};
+  constexpr size_t smem = FwdCfg<D>::SMEM;
+  if (!attr_done[ctx->device]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(attn fwd): %s", cudaGetErrorString(e));
+    attr_done[ctx->device] = true;
+  }
+  dim3 grid(p.num_qb, p.Z * p.H, 1);
+  attn_fwd_kernel<D, BF16><<<grid, FWD_THREADS, smem, stream>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn fwd launch: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+}  // namespace
+
+// 4-D map over [Z, H, N, D] (D contiguous) with boxes of 64 columns x 128 rows
+bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
+                    int64_t sn, int box_rows) {
+  uint64_t dims[4] = {(uint64_t)D, (uint64_t)N, (uint64_t)H, (uint64_t)Z};
+  uint64_t strides[3] = {(uint64_t)sn * 2, (uint64_t)sh * 2, (uint64_t)sz * 2};
+  uint32_t box[4] = {64, (uint32_t)box_rows, 1, 1};
+  return encode_tmap(out, dtype, 4, base, dims, strides, box, true);
+}
+
+int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,
+                    float* m, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
+                    const int64_t* so, float sm_scale, int causal, int dtype) {
+  CUtensorMap tq, tk, tv;
+  if (!encode_qkv_map(&tq, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], BLK)) return B200_ERR_UNSUPPORTED;
+  if (!encode_qkv_map(&tk, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], BLK)) return B200_ERR_UNSUPPORTED;
+  if (!encode_qkv_map(&tv, dtype, v, Z, H, N, D, sv[0], sv[1], sv[2], BLK)) return B200_ERR_UNSUPPORTED;
+  FwdParams p{};
+  p.o = o; p.m = m;
+  p.o_sz = so[0]; p.o_sh = so[1]; p.o_sn = so[2];
+  p.Z = Z; p.H = H; p.N = N; p.causal = causal;
+  p.scale_log2 = sm_scale * 1.44269504f;  // the reference's constant (06-fused-attention.py:161)
+  p.num_qb = (N + 255) / 256;
+  p.status = ctx->status;
+  const bool bf16 = dtype == B200_BF16;
+  if (D == 128) return bf16 ? launch_fwd_t<128, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<128, false>(ctx, stream, tq, tk, tv, p);
+  if (D == 64) return bf16 ? launch_fwd_t<64, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<64, false>(ctx, stream, tq, tk, tv, p);
+  return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
+}
+
+}  // namespace tb

@@ -177,4 +177,23 @@ int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int
                      stride_bn, stride_cm, in_dtype, out_dtype, activation, scale_a, scale_b);
 }
 
+int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m, int Z,
+                       int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
+                       const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal, int dtype) {
+  if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
+  if (dtype != B200_F16 && dtype != B200_BF16) return fail(B200_ERR_ARG, "attention dtype must be F16 or BF16");
+  if (D != 64 && D != 128) return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
+  if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
+  if (!stride_q || !stride_k || !stride_v || !stride_o) return fail(B200_ERR_ARG, "null stride array");
+  if (stride_q[3] != 1 || stride_k[3] != 1 || stride_v[3] != 1 || stride_o[3] != 1)
+    return fail(B200_ERR_UNSUPPORTED, "the head dimension must be contiguous");
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  if (Z == 0 || H == 0 || N == 0) return B200_OK;
+  if (!q || !k || !v || !o || !m) return fail(B200_ERR_ARG, "null pointer");
+  if ((long long)Z * H > 65535) return fail(B200_ERR_UNSUPPORTED, "Z*H exceeds 65535");
+  return launch_attn_fwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, m, Z, H, N, D, stride_q, stride_k,
+                         stride_v, stride_o, sm_scale, causal, dtype);
+}
+
 }  // extern "C"

@@ -59,7 +59,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and records `site`) when the limit is reached or another
 // thread already recorded a failure.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, unsigned* status, unsigned site) {
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, unsigned* status, unsigned site) {
   if (*(volatile unsigned*)status != 0) return false;
   const unsigned long long t0 = gtimer_ns();
   uint32_t spins = 0;

@@ -43,4 +43,12 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
                 int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t scm, int in_dtype, int out_dtype,
                 int activation, const float* scale_a, const float* scale_b);
 
+int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,
+                    float* m, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
+                    const int64_t* so, float sm_scale, int causal, int dtype);
+
+// 4-D tensor map over [Z, H, N, D] (D contiguous): boxes of 64 columns x box_rows rows, 128-byte swizzle
+bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
+                    int64_t sn, int box_rows);
+
 }  // namespace tb

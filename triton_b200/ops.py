@@ -82,3 +82,25 @@ def quantize_e4m3(x):
     amax = x.abs().amax().float().clamp_min(1e-12)
     s = 448.0 / amax
     return (x.float() * s).to(torch.float8_e4m3fn), (1.0 / s).reshape(1)
+
+
+def attention_forward(q, k, v, causal, sm_scale):
+    """Forward only: returns (O, M).  M[Z,H,N] is the reference's saved statistics tensor, the
+    base-2 log-sum-exp of the scores scaled by sm_scale*log2(e) (06-fused-attention.py:183-184);
+    the natural-log LSE is M * ln 2."""
+    HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
+    assert q.dim() == 4 and k.shape == q.shape and v.shape == q.shape, "q, k, v must be [Z, H, N, D] of one shape"
+    assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
+    assert HEAD_DIM_K in {16, 32, 64, 128, 256}  # the reference's set; this library has kernels for 64 and 128
+    assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+    dev = _require_cuda(q, k, v)
+    Z, H, N, D = q.shape
+    with torch.cuda.device(dev):
+        o = torch.empty_like(q)
+        M = torch.empty((Z, H, N), device=dev, dtype=torch.float32)
+        code = _lib.lib().b200_attention_fwd(
+            _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), M.data_ptr(), Z, H, N, D,
+            _lib.strides4(q), _lib.strides4(k), _lib.strides4(v), _lib.strides4(o),
+            float(sm_scale), 1 if causal else 0, _DT[q.dtype])
+        _lib.check(code, "attention_fwd")
+    return o, M
