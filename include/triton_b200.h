@@ -79,6 +79,23 @@ B200_API int b200_attention_fwd(b200_stream_t stream, const void* q, const void*
                                 const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal,
                                 int dtype);
 
+/* Flash-attention backward: dQ, dK, dV from Q, K, V, O, dO and the forward's statistics M.
+ * Replaces _attn_bwd_preprocess, _attn_bwd and their launches in _attention.backward,
+ * python/tutorials/06-fused-attention.py:190-435, 478-517 (Q, K, V, sm_scale, DO, DQ, DK, DV, M, D
+ * -> delta, strides, H, N_CTX; the host-side pre-scaling of K at :491-492 is folded into the kernels).
+ * All tensors [Z, H, N, D] of `dtype` with their own element strides {z, h, n, d} (d stride 1, the
+ * others multiples of 8); m and delta are contiguous [Z, H, N] fp32.  `delta` is SCRATCH memory the
+ * caller provides (Z*H*N floats): the pre-pass writes rowsum(O * dO) there and the main kernels
+ * read it; its contents after the call are that intermediate.  N must be a multiple of 128 (the
+ * reference asserts the same, :494).  `causal` selects the mask for both kernels (the reference's
+ * backward always applies the causal mask; pass the flag the forward was run with). */
+B200_API int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const void* v, const void* o,
+                                const void* d_o, const float* m, float* delta, void* dq, void* dk, void* dv, int Z,
+                                int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
+                                const int64_t stride_v[4], const int64_t stride_o[4], const int64_t stride_do[4],
+                                const int64_t stride_dq[4], const int64_t stride_dk[4], const int64_t stride_dv[4],
+                                float sm_scale, int causal, int dtype);
+
 #ifdef __cplusplus
 }
 #endif

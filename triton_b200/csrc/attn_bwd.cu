@@ -1,0 +1,454 @@
+// Flash-attention backward for sm_100a.
+//
+// Computes what the reference's backward computes (python/tutorials/06-fused-attention.py:190-435,
+// 478-517), with its decomposition: a pre-pass delta = rowsum(O * dO) (_attn_bwd_preprocess), then
+// per 128-row K/V block dK and dV from a loop over Q blocks (_attn_bwd_dkdv), and per 128-row Q
+// block dQ from a loop over K/V blocks (_attn_bwd_dq).  No atomics: every output element has one
+// writer, results are deterministic.  P and dS are rounded to the storage type before the second
+// products (:244, :251, :297), everything else is fp32.  The reference folds sm_scale/ln2 into a
+// 16-bit copy of K on the host (:491-492); here the fp32 scores are scaled instead, which saves
+// the extra pass over K and one rounding.
+//
+// Both main kernels are one pipeline (template parameter DQ):
+//   resident operands R1, R2 (128 x D each) stay in shared memory, the other side streams through
+//   a ring as pairs (U1, U2) of 128 x D tiles.  Per step
+//       T1 = R1 U1^T        (scores: S^T = K Q^T, or S = Q K^T)
+//       T2 = R2 U2^T        (dP^T = V dO^T, or dP = dO V^T)
+//       P  = exp2(T1 * scale - M) masked;   dS = P * (T2 - delta)       (fp32, one thread per row)
+//       accB += P  U2       (dV += P^T dO; dK/dV kernel only)
+//       accA += dS U1       (dK += dS^T Q, or dQ += dS K)
+//   T1/T2 live in TMEM and P/dS overwrite them as 16-bit A operands of the last two MMAs, which
+//   read U1/U2 through an N-major view of the same shared-memory tiles.
+// Warps 0-3 compute (one thread per TMEM lane), warp 4 issues MMAs, warp 5 runs TMA.
+#include <cmath>
+
+#include "common.cuh"
+#include "host.h"
+
+namespace tb {
+
+namespace {
+
+constexpr int BLK = 128;
+constexpr int BWD_THREADS = 192;
+
+struct BwdParams {
+  const float* m;      // [Z*H, N] base-2 LSE from the forward
+  const float* delta;  // [Z*H, N]
+  void* out_a;         // dK (dK/dV kernel) or dQ (dQ kernel)
+  void* out_b;         // dV (dK/dV kernel)
+  long long oa_sz, oa_sh, oa_sn, ob_sz, ob_sh, ob_sn;
+  int Z, H, N;
+  int causal;
+  float scale_log2;  // sm_scale * log2(e)
+  float sm_scale;
+  unsigned* status;
+};
+
+template <int D>
+struct BwdCfg {
+  static constexpr int TILE = BLK * D * 2;
+  static constexpr int NST = (D == 128) ? 2 : 3;
+  static constexpr int STAGE = 2 * TILE + 1024;  // U1, U2, column statistics (M, delta of the streamed rows)
+  static constexpr size_t SMEM = 2 * TILE + (size_t)NST * STAGE + (2 * NST + 8) * 8 + 16 + 1024;
+};
+
+template <int D>
+__device__ __forceinline__ void load_tile_b(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int z) {
+#pragma unroll
+  for (int b = 0; b < D / 64; ++b) tma_load_4d(dst + b * (BLK * 128), map, bar, b * 64, row0, h, z);
+}
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+// DQ = false: block = K/V block, R1 = K, R2 = V, stream (Q_i, dO_i), outputs dK (A), dV (B)
+// DQ = true : block = Q block,  R1 = Q, R2 = dO, stream (K_j, V_j), output dQ (A)
+template <int D, bool BF16, bool DQ>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
+                const __grid_constant__ CUtensorMap tm_u1, const __grid_constant__ CUtensorMap tm_u2,
+                const BwdParams p) {
+  using Cfg = BwdCfg<D>;
+  constexpr int TILE = Cfg::TILE, NST = Cfg::NST, STAGE = Cfg::STAGE;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  uint8_t* sres = smem;                 // R1, R2
+  uint8_t* sring = smem + 2 * TILE;     // stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sring + NST * STAGE);
+  uint64_t* r_full = bars;              // [1] resident tiles loaded
+  uint64_t* full = bars + 1;            // [NST]
+  uint64_t* empty = full + NST;         // [NST]
+  uint64_t* t1_full = empty + NST;      // T1(t) in TMEM
+  uint64_t* t2_full = t1_full + 1;      // T2(t) in TMEM
+  uint64_t* p_full = t2_full + 1;       // P(t) written (dK/dV kernel)
+  uint64_t* ds_full = p_full + 1;       // dS(t) written
+  uint64_t* acc_full = ds_full + 1;     // accumulators final
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblk = p.N / BLK;
+  // heavy blocks first: the dK/dV kernel's early K/V blocks and the dQ kernel's late Q blocks see most steps
+  const int blk = DQ ? (nblk - 1 - (int)blockIdx.x) : (int)blockIdx.x;
+  const int zh = blockIdx.y, z = zh / p.H, h = zh % p.H;
+  // streamed range [t_lo, t_hi)
+  const int t_lo = DQ ? 0 : (p.causal ? blk : 0);
+  const int t_hi = DQ ? (p.causal ? blk + 1 : nblk) : nblk;
+
+  if (threadIdx.x == 0) {
+    mbar_init(r_full, 1);
+    for (int s = 0; s < NST; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(t1_full, 1);
+    mbar_init(t2_full, 1);
+    mbar_init(p_full, 128);
+    mbar_init(ds_full, 128);
+    mbar_init(acc_full, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_r1);
+    tma_prefetch_desc(&tm_r2);
+    tma_prefetch_desc(&tm_u1);
+    tma_prefetch_desc(&tm_u2);
+  }
+  if (warp == 4) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const uint32_t tm_t1 = tmem_base, tm_t2 = tmem_base + 128, tm_a = tmem_base + 256, tm_b = tmem_base + 256 + D;
+
+  if (warp == 5) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      mbar_expect_tx(r_full, 2 * TILE);
+      load_tile_b<D>(sres, &tm_r1, r_full, blk * BLK, h, z);
+      load_tile_b<D>(sres + TILE, &tm_r2, r_full, blk * BLK, h, z);
+      uint32_t s = 0, ph = 0;
+      for (int t = t_lo; t < t_hi; ++t) {
+        mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_BWD_LOAD_EMPTY);
+        uint8_t* st = sring + s * STAGE;
+        mbar_expect_tx(&full[s], 2 * TILE + (DQ ? 0 : 1024));
+        load_tile_b<D>(st, &tm_u1, &full[s], t * BLK, h, z);
+        load_tile_b<D>(st + TILE, &tm_u2, &full[s], t * BLK, h, z);
+        if (!DQ) {  // statistics of the streamed Q rows: M then delta, 128 floats each
+          bulk_load(st + 2 * TILE, p.m + (long long)zh * p.N + t * BLK, 512, &full[s]);
+          bulk_load(st + 2 * TILE + 512, p.delta + (long long)zh * p.N + t * BLK, 512, &full[s]);
+        }
+        if (++s == NST) { s = 0; ph ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr int FMT = BF16 ? 1 : 0;
+      constexpr uint32_t IDESC_T = make_idesc(FMT, FMT, 0, 0, 128, BLK);  // R (K-major) x U (K-major)
+      constexpr uint32_t IDESC_ACC = make_idesc(FMT, FMT, 0, 1, 128, D);  // P/dS (TMEM) x U (N-major)
+      const uint64_t dr0 = smem_desc_sw128(smem_u32(sres), 0, 1024);
+      const uint64_t du0 = smem_desc_sw128(smem_u32(sring), 0, 1024);
+      const uint64_t dun0 = smem_desc_sw128(smem_u32(sring), BLK * 128, 1024);  // N-major view of a streamed tile
+
+      auto issue_t = [&](uint32_t tm, uint64_t dr, uint64_t du) {  // T = R U^T, D/16 MMAs
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * ((BLK * 128) >> 4) + (kk & 3) * 2;
+          umma_ss<false>(tm, dr + off, du + off, IDESC_T, kk != 0);
+        }
+      };
+      auto issue_acc = [&](uint32_t tm_acc, uint32_t tm_opnd, uint64_t dun, uint32_t accum) {  // acc (+)= X U, 8 MMAs
+#pragma unroll
+        for (int kk = 0; kk < BLK / 16; ++kk)
+          umma_ts_f16(tm_acc, tm_opnd + kk * 8, dun + kk * ((16 * 128) >> 4), IDESC_ACC, (accum | kk) != 0);
+      };
+
+      mbar_wait(r_full, 0, p.status, SITE_BWD_KV);
+      const int steps = t_hi - t_lo;
+      uint32_t s = 0, ph = 0;
+      if (steps > 0) {
+        mbar_wait(&full[0], 0, p.status, SITE_BWD_LOAD_FULL);
+        issue_t(tm_t1, dr0, du0);
+        tc_commit(t1_full);
+        issue_t(tm_t2, dr0 + (TILE >> 4), du0 + (TILE >> 4));
+        tc_commit(t2_full);
+      }
+      for (int it = 0; it < steps; ++it) {
+        const uint32_t cs = s;
+        uint32_t ns = s + 1, nph = ph;
+        if (ns == NST) { ns = 0; nph ^= 1u; }
+        const uint64_t dun1 = dun0 + cs * (STAGE >> 4), dun2 = dun1 + (TILE >> 4);
+        const bool more = it + 1 < steps;
+        if (!DQ) {
+          mbar_wait(p_full, it & 1, p.status, SITE_BWD_P_FULL);
+          tc_fence_after();
+          issue_acc(tm_b, tm_t1, dun2, it > 0);  // dV += P^T dO
+        }
+        if (more) {  // T1 of the next step may start as soon as P was consumed (in-order pipe)
+          mbar_wait(&full[ns], nph, p.status, SITE_BWD_LOAD_FULL);
+          if (DQ) {
+            // the dQ kernel has no consumer of P in TMEM: T1 is free once the compute warps have read it,
+            // which ds_full(it) implies; wait for it below before reusing T1
+          } else {
+            issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
+            tc_commit(t1_full);
+          }
+        }
+        mbar_wait(ds_full, it & 1, p.status, SITE_BWD_DS_FULL);
+        tc_fence_after();
+        issue_acc(tm_a, tm_t2, dun1, it > 0);  // dK += dS^T Q   /   dQ += dS K
+        tc_commit(&empty[cs]);
+        if (more) {
+          if (DQ) {
+            issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
+            tc_commit(t1_full);
+          }
+          issue_t(tm_t2, dr0 + (TILE >> 4), du0 + ns * (STAGE >> 4) + (TILE >> 4));
+          tc_commit(t2_full);
+        }
+        s = ns; ph = nph;
+      }
+      tc_commit(acc_full);
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ compute (one thread per TMEM lane)
+    const uint32_t quarter = warp & 3u;
+    const int r = quarter * 32 + lane;       // row inside the block
+    const int grow = blk * BLK + r;          // kv index (dK/dV kernel) or q index (dQ kernel)
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    const float scale = p.scale_log2;
+    float m_row = 0.f, d_row = 0.f;
+    if (DQ) {
+      m_row = p.m[(long long)zh * p.N + grow];
+      d_row = p.delta[(long long)zh * p.N + grow];
+    }
+    const int steps = t_hi - t_lo;
+    uint32_t s = 0;
+    for (int it = 0; it < steps; ++it) {
+      const int t = t_lo + it;
+      const float* sm = reinterpret_cast<const float*>(sring + s * STAGE + 2 * TILE);  // column M
+      const float* sd = sm + 128;                                                       // column delta
+      // the diagonal block is the only one that needs the causal mask
+      const bool diag = p.causal && (t == blk);
+      mbar_wait(t1_full, it & 1, p.status, SITE_BWD_S_FULL);
+      tc_fence_after();
+      uint32_t pr[BLK];  // P as fp32 bits
+#pragma unroll
+      for (int c = 0; c < BLK; c += 32) tmem_ld32(tm_t1 + lane_addr + c, pr + c);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c = 0; c < BLK; ++c) {
+        const float mm = DQ ? m_row : sm[c];
+        float pv = ex2(fmaf(__uint_as_float(pr[c]), scale, -mm));
+        // dK/dV kernel: row = kv, column = q, keep q >= kv.   dQ kernel: row = q, column = kv, keep kv <= q.
+        if (diag && (DQ ? (c > r) : (c < r))) pv = 0.f;
+        pr[c] = __float_as_uint(pv);
+      }
+      if (!DQ) {
+#pragma unroll
+        for (int c = 0; c < BLK; c += 32) {
+          uint32_t w[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) w[k] = pack2<BF16>(__uint_as_float(pr[c + 2 * k]), __uint_as_float(pr[c + 2 * k + 1]));
+          tmem_st16(tm_t1 + lane_addr + (c >> 1), w);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(p_full);
+      }
+      mbar_wait(t2_full, it & 1, p.status, SITE_BWD_DP_FULL);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < BLK; c += 32) {
+        uint32_t dp[32];
+        tmem_ld32(tm_t2 + lane_addr + c, dp);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+          const float d0 = DQ ? d_row : sd[c + 2 * k];
+          const float d1 = DQ ? d_row : sd[c + 2 * k + 1];
+          const float ds0 = __uint_as_float(pr[c + 2 * k]) * (__uint_as_float(dp[2 * k]) - d0);
+          const float ds1 = __uint_as_float(pr[c + 2 * k + 1]) * (__uint_as_float(dp[2 * k + 1]) - d1);
+          w[k] = pack2<BF16>(ds0, ds1);
+        }
+        // all 128 columns of T2 must be read before the packed dS overwrites its first 64 columns:
+        // chunk c writes columns [c/2, c/2+16), which chunk c' > c has not read only if c/2+16 > c' -> c' < 32
+        // i.e. only chunk 0's write (columns 0-15) could clobber unread data of chunk 0 itself (already read).
+        tmem_st16(tm_t2 + lane_addr + (c >> 1), w);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+      if (++s == NST) s = 0;
+    }
+
+    // epilogue
+    mbar_wait(acc_full, 0, p.status, SITE_BWD_ACC_FULL);
+    tc_fence_after();
+    auto store_rows = [&](uint32_t tm_acc, void* out, long long sz, long long sh, long long sn, float mul) {
+      uint16_t* orow = reinterpret_cast<uint16_t*>(out) + (long long)z * sz + (long long)h * sh + (long long)grow * sn;
+      const bool vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((sn & 7) == 0) && ((sh & 7) == 0) && ((sz & 7) == 0);
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tm_acc + lane_addr + c, o);
+        tmem_ld_wait();
+        uint32_t w[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          w[k] = (steps > 0) ? pack2<BF16>(__uint_as_float(o[2 * k]) * mul, __uint_as_float(o[2 * k + 1]) * mul) : 0u;
+        if (vec_ok) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {
+            orow[c + 2 * k] = (uint16_t)(w[k] & 0xFFFFu);
+            orow[c + 2 * k + 1] = (uint16_t)(w[k] >> 16);
+          }
+        }
+      }
+    };
+    store_rows(tm_a, p.out_a, p.oa_sz, p.oa_sh, p.oa_sn, p.sm_scale);  // dK or dQ carry sm_scale
+    if (!DQ) store_rows(tm_b, p.out_b, p.ob_sz, p.ob_sh, p.ob_sn, 1.0f);
+  }
+
+  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[zh, n] = sum_d O * dO in fp32 (_attn_bwd_preprocess, 06-fused-attention.py:190-204).
+// HBM-bound: one warp per row chunk, 16-byte loads; 8 rows per warp for D = 64, 4 for D = 128 ... generic:
+// each thread reads 8 elements (16 bytes) of O and dO, D/8 threads per row.
+template <int D, bool BF16>
+__global__ void __launch_bounds__(256)
+attn_bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ dout, float* __restrict__ delta,
+                      long long o_sz, long long o_sh, long long o_sn, long long d_sz, long long d_sh, long long d_sn,
+                      int H, int N, long long rows_total) {
+  constexpr int TPR = D / 8;  // threads per row
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / TPR;
+  const int part = (int)(gid % TPR);
+  float acc = 0.f;
+  if (row < rows_total) {
+    const int n = (int)(row % N);
+    const long long zh = row / N;
+    const int hh = (int)(zh % H);
+    const long long zz = zh / H;
+    const uint4 ov = *reinterpret_cast<const uint4*>(o + zz * o_sz + hh * o_sh + (long long)n * o_sn + part * 8);
+    const uint4 dv = *reinterpret_cast<const uint4*>(dout + zz * d_sz + hh * d_sh + (long long)n * d_sn + part * 8);
+    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a, b;
+      if (BF16) {
+        a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[k]));
+        b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dw[k]));
+      } else {
+        a = __half22float2(*reinterpret_cast<const __half2*>(&ow[k]));
+        b = __half22float2(*reinterpret_cast<const __half2*>(&dw[k]));
+      }
+      acc = fmaf(a.x, b.x, acc);
+      acc = fmaf(a.y, b.y, acc);
+    }
+  }
+#pragma unroll
+  for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < rows_total && part == 0) delta[row] = acc;
+}
+
+template <int D, bool BF16, bool DQ>
+int launch_bwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& r1, const CUtensorMap& r2,
+                 const CUtensorMap& u1, const CUtensorMap& u2, const BwdParams& p) {
+  static bool attr_done[64] = {};
+  constexpr size_t smem = BwdCfg<D>::SMEM;
+  if (!attr_done[ctx->device]) {
+    cudaError_t e =
+        cudaFuncSetAttribute(attn_bwd_kernel<D, BF16, DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(attn bwd): %s", cudaGetErrorString(e));
+    attr_done[ctx->device] = true;
+  }
+  dim3 grid(p.N / BLK, p.Z * p.H, 1);
+  attn_bwd_kernel<D, BF16, DQ><<<grid, BWD_THREADS, smem, stream>>>(r1, r2, u1, u2, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd launch: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+template <int D, bool BF16>
+int launch_bwd_all(DeviceCtx* ctx, cudaStream_t stream, const void* o, const void* dout, float* delta,
+                   const int64_t* so, const int64_t* sdo, const CUtensorMap& tq, const CUtensorMap& tk,
+                   const CUtensorMap& tv, const CUtensorMap& tdo, BwdParams p, void* dq, void* dk, void* dv,
+                   const int64_t* sdq, const int64_t* sdk, const int64_t* sdv) {
+  const long long rows = (long long)p.Z * p.H * p.N;
+  const long long threads = rows * (D / 8);
+  attn_bwd_delta_kernel<D, BF16><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const uint16_t*>(o), reinterpret_cast<const uint16_t*>(dout), delta, so[0], so[1], so[2],
+      sdo[0], sdo[1], sdo[2], p.H, p.N, rows);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd delta launch: %s", cudaGetErrorString(e));
+  p.delta = delta;
+  // dK, dV: resident (K, V), streamed (Q, dO)
+  p.out_a = dk; p.oa_sz = sdk[0]; p.oa_sh = sdk[1]; p.oa_sn = sdk[2];
+  p.out_b = dv; p.ob_sz = sdv[0]; p.ob_sh = sdv[1]; p.ob_sn = sdv[2];
+  int rc = launch_bwd_t<D, BF16, false>(ctx, stream, tk, tv, tq, tdo, p);
+  if (rc) return rc;
+  // dQ: resident (Q, dO), streamed (K, V)
+  p.out_a = dq; p.oa_sz = sdq[0]; p.oa_sh = sdq[1]; p.oa_sn = sdq[2];
+  p.out_b = nullptr;
+  return launch_bwd_t<D, BF16, true>(ctx, stream, tq, tdo, tk, tv, p);
+}
+
+}  // namespace
+
+int launch_attn_bwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, const void* o,
+                    const void* dout, const float* m, float* delta, void* dq, void* dk, void* dv, int Z, int H, int N,
+                    int D, const int64_t* sq, const int64_t* sk, const int64_t* sv, const int64_t* so,
+                    const int64_t* sdo, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv, float sm_scale,
+                    int causal, int dtype) {
+  CUtensorMap tq, tk, tv, tdo;
+  if (!encode_qkv_map(&tq, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], BLK)) return B200_ERR_UNSUPPORTED;
+  if (!encode_qkv_map(&tk, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], BLK)) return B200_ERR_UNSUPPORTED;
+  if (!encode_qkv_map(&tv, dtype, v, Z, H, N, D, sv[0], sv[1], sv[2], BLK)) return B200_ERR_UNSUPPORTED;
+  if (!encode_qkv_map(&tdo, dtype, dout, Z, H, N, D, sdo[0], sdo[1], sdo[2], BLK)) return B200_ERR_UNSUPPORTED;
+  for (const int64_t* s : {so, sdo}) {
+    if ((s[0] & 7) || (s[1] & 7) || (s[2] & 7)) return fail(B200_ERR_UNSUPPORTED, "O / dO strides must be multiples of 8 elements");
+  }
+  if ((reinterpret_cast<uintptr_t>(o) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15))
+    return fail(B200_ERR_UNSUPPORTED, "O / dO must be 16-byte aligned");
+  BwdParams p{};
+  p.m = m;
+  p.Z = Z; p.H = H; p.N = N; p.causal = causal;
+  p.scale_log2 = sm_scale * 1.44269504f;
+  p.sm_scale = sm_scale;
+  p.status = ctx->status;
+  const bool bf16 = dtype == B200_BF16;
+  if (D == 128) {
+    return bf16 ? launch_bwd_all<128, true>(ctx, stream, o, dout, delta, so, sdo, tq, tk, tv, tdo, p, dq, dk, dv, sdq, sdk, sdv)
+                : launch_bwd_all<128, false>(ctx, stream, o, dout, delta, so, sdo, tq, tk, tv, tdo, p, dq, dk, dv, sdq, sdk, sdv);
+  }
+  if (D == 64) {
+    return bf16 ? launch_bwd_all<64, true>(ctx, stream, o, dout, delta, so, sdo, tq, tk, tv, tdo, p, dq, dk, dv, sdq, sdk, sdv)
+                : launch_bwd_all<64, false>(ctx, stream, o, dout, delta, so, sdo, tq, tk, tv, tdo, p, dq, dk, dv, sdq, sdk, sdv);
+  }
+  return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
+}
+
+}  // namespace tb

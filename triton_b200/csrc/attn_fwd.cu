@@ -49,7 +49,6 @@ template <int D>
 struct FwdCfg {
   static constexpr int TILE_BYTES = BLK * D * 2;               // one Q tile or one K / V block
   static constexpr int KV_STAGES = (D == 128) ? 4 : 8;
-  static constexpr int SUBTILES = D / 64;                      // 64-column (128-byte) boxes per tile
   static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 10) * 8 + 16 + 1024;
 };
 

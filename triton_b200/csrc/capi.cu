@@ -39,6 +39,14 @@ DeviceCtx* current_ctx() {
     cudaGetLastError();
     return nullptr;
   }
+  // Bind the device's primary context to THIS thread: the driver entry point used for tensor maps
+  // needs a current context, and a thread that has made no runtime call yet (an autograd worker
+  // calling the backward, say) does not have one.
+  e = cudaSetDevice(dev);
+  if (e != cudaSuccess) {
+    fail(B200_ERR_CUDA, "cudaSetDevice(%d): %s", dev, cudaGetErrorString(e));
+    return nullptr;
+  }
   std::lock_guard<std::mutex> lk(g_mu);
   DeviceCtx& c = g_ctx[dev];
   if (c.device == dev) return &c;
@@ -194,6 +202,33 @@ int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const
   if ((long long)Z * H > 65535) return fail(B200_ERR_UNSUPPORTED, "Z*H exceeds 65535");
   return launch_attn_fwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, m, Z, H, N, D, stride_q, stride_k,
                          stride_v, stride_o, sm_scale, causal, dtype);
+}
+
+int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const void* v, const void* o,
+                       const void* d_o, const float* m, float* delta, void* dq, void* dk, void* dv, int Z, int H, int N,
+                       int D, const int64_t stride_q[4], const int64_t stride_k[4], const int64_t stride_v[4],
+                       const int64_t stride_o[4], const int64_t stride_do[4], const int64_t stride_dq[4],
+                       const int64_t stride_dk[4], const int64_t stride_dv[4], float sm_scale, int causal, int dtype) {
+  if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
+  if (dtype != B200_F16 && dtype != B200_BF16) return fail(B200_ERR_ARG, "attention dtype must be F16 or BF16");
+  if (D != 64 && D != 128) return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
+  if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
+  if (N % 128 != 0) return fail(B200_ERR_ARG, "backward needs N to be a multiple of 128 (N = %d)", N);
+  const int64_t* all[8] = {stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk, stride_dv};
+  for (const int64_t* st : all) {
+    if (!st) return fail(B200_ERR_ARG, "null stride array");
+    if (st[3] != 1) return fail(B200_ERR_UNSUPPORTED, "the head dimension must be contiguous");
+  }
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  if (Z == 0 || H == 0 || N == 0) return B200_OK;
+  if (!q || !k || !v || !o || !d_o || !m || !delta || !dq || !dk || !dv) return fail(B200_ERR_ARG, "null pointer");
+  if ((long long)Z * H > 65535) return fail(B200_ERR_UNSUPPORTED, "Z*H exceeds 65535");
+  if ((reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(delta) & 15))
+    return fail(B200_ERR_UNSUPPORTED, "m and delta must be 16-byte aligned");
+  return launch_attn_bwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, d_o, m, delta, dq, dk, dv, Z, H, N, D,
+                         stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk, stride_dv, sm_scale,
+                         causal, dtype);
 }
 
 }  // extern "C"

@@ -47,6 +47,12 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
                     float* m, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
                     const int64_t* so, float sm_scale, int causal, int dtype);
 
+int launch_attn_bwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, const void* o,
+                    const void* dout, const float* m, float* delta, void* dq, void* dk, void* dv, int Z, int H, int N,
+                    int D, const int64_t* sq, const int64_t* sk, const int64_t* sv, const int64_t* so,
+                    const int64_t* sdo, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv, float sm_scale,
+                    int causal, int dtype);
+
 // 4-D tensor map over [Z, H, N, D] (D contiguous): boxes of 64 columns x box_rows rows, 128-byte swizzle
 bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
                     int64_t sn, int box_rows);

@@ -104,3 +104,46 @@ def attention_forward(q, k, v, causal, sm_scale):
             float(sm_scale), 1 if causal else 0, _DT[q.dtype])
         _lib.check(code, "attention_fwd")
     return o, M
+
+
+def attention_backward(q, k, v, o, M, do, causal, sm_scale):
+    """dq, dk, dv.  Same checks as the reference's backward (06-fused-attention.py:478-494)."""
+    assert do.is_contiguous()
+    assert q.stride() == k.stride() == v.stride() == o.stride() == do.stride()
+    Z, H, N, D = q.shape
+    assert N % 128 == 0
+    dev = _require_cuda(q, k, v, o, do, M)
+    with torch.cuda.device(dev):
+        dq = torch.empty_like(q)
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        delta = torch.empty_like(M)
+        code = _lib.lib().b200_attention_bwd(
+            _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
+            delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), Z, H, N, D,
+            _lib.strides4(q), _lib.strides4(k), _lib.strides4(v), _lib.strides4(o), _lib.strides4(do),
+            _lib.strides4(dq), _lib.strides4(dk), _lib.strides4(dv), float(sm_scale), 1 if causal else 0, _DT[q.dtype])
+        _lib.check(code, "attention_bwd")
+    return dq, dk, dv
+
+
+class _attention(torch.autograd.Function):
+    """Mirror of the reference's autograd wrapper (06-fused-attention.py:438-520)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, sm_scale):
+        o, M = attention_forward(q, k, v, causal, sm_scale)
+        ctx.save_for_backward(q, k, v, o, M)
+        ctx.sm_scale = sm_scale
+        ctx.causal = causal
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, M = ctx.saved_tensors
+        dq, dk, dv = attention_backward(q, k, v, o, M, do.contiguous() if not do.is_contiguous() else do,
+                                        ctx.causal, ctx.sm_scale)
+        return dq, dk, dv, None, None
+
+
+attention = _attention.apply
