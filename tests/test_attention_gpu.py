@@ -1,0 +1,159 @@
+"""Parity of the CUDA flash attention (through the C ABI) with the CPU oracle and the
+interpreter-generated golden fixtures; edge cases; full-size checks of configs 4 and 5 on
+sampled heads.  Tolerance: rtol = atol = 1e-2 (python/tutorials/06-fused-attention.py:551-559
+uses atol 1e-2); bf16 gradients get 2e-2 absolute because one bf16 ulp at |x| ~ 4 is 3e-2."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+import triton_b200
+from oracle import ref_ops as R
+from triton_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+def status_ok():
+    assert _lib.status() == 0, "a bounded device-side wait ran out"
+
+
+def run_gpu(q, k, v, do, causal, sm_scale, bwd):
+    qd, kd, vd = (t.to(DEV).requires_grad_(bwd) for t in (q, k, v))
+    o, M = triton_b200.attention_forward(qd.detach(), kd.detach(), vd.detach(), causal, sm_scale)
+    out = dict(o=f32(o), m=f32(M))
+    if bwd:
+        o2 = triton_b200.attention(qd, kd, vd, causal, sm_scale)
+        o2.backward(do.to(DEV))
+        assert torch.equal(o2.detach(), o)
+        out.update(dq=f32(qd.grad), dk=f32(kd.grad), dv=f32(vd.grad))
+    status_ok()
+    return out
+
+
+@pytest.mark.parametrize("name", list(cases.ATTN_CASES))
+def test_attention_parity_with_oracle(golden, name):
+    c = cases.ATTN_CASES[name]
+    q, k, v, do = cases.attn_inputs(c)
+    got = run_gpu(q, k, v, do, c["causal"], c["sm_scale"], c.get("bwd", False))
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), c["causal"], c["sm_scale"], c["dtype"])
+    np.testing.assert_allclose(got["o"], o, rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(got["m"], M, rtol=1e-4, atol=1e-3)
+    if c["dtype"] == "fp16":
+        np.testing.assert_allclose(got["o"], golden[f"attn.{name}.o"].astype(np.float32), rtol=1e-2, atol=1e-2)
+        np.testing.assert_allclose(got["m"], golden[f"attn.{name}.m"], rtol=1e-4, atol=1e-3)
+    if c.get("bwd"):
+        dq, dk, dv = R.attention_bwd(f32(q), f32(k), f32(v), o, f32(do), M, c["sm_scale"], c["dtype"])
+        tol = 1e-2 if c["dtype"] == "fp16" else 2e-2
+        for key, want in (("dq", dq), ("dk", dk), ("dv", dv)):
+            np.testing.assert_allclose(got[key], want, rtol=1e-2, atol=tol, err_msg=key)
+            if c["dtype"] == "fp16":
+                np.testing.assert_allclose(got[key], golden[f"attn.{name}.{key}"].astype(np.float32), rtol=1e-2,
+                                           atol=1e-2, err_msg="golden " + key)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("N", [128, 200, 384, 1000])
+@pytest.mark.parametrize("causal", [True, False])
+def test_forward_ragged_lengths(dtype, D, N, causal):
+    c = dict(Z=1, H=2, N=N, D=D, dtype=dtype, seed=N + D)
+    q, k, v, _ = cases.attn_inputs(c)
+    got = run_gpu(q, k, v, None, causal, D ** -0.5, False)
+    # the oracle walks 128-row blocks like the reference; pad the ragged tail with masked keys
+    pad = (-N) % 128
+    if pad:
+        qp, kp, vp = (torch.cat([t, torch.zeros(1, 2, pad, D, dtype=t.dtype)], 2) for t in (q, k, v))
+        if causal:
+            o, M = R.attention_fwd(f32(qp), f32(kp), f32(vp), True, D ** -0.5, dtype)
+            o, M = o[:, :, :N], M[:, :, :N]
+        else:  # full attention over exactly N keys: dense fp32 softmax with P rounded to the storage type
+            s = (q.float() @ k.float().transpose(2, 3)) * D ** -0.5
+            M = (torch.logsumexp(s, -1) / math.log(2.0)).numpy()
+            p = torch.softmax(s, -1)
+            o = (p @ v.float()).numpy()
+    else:
+        o, M = R.attention_fwd(f32(q), f32(k), f32(v), causal, D ** -0.5, dtype)
+    np.testing.assert_allclose(got["o"], o, rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(got["m"], M, rtol=1e-4, atol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("D", [64, 128])
+def test_backward_noncausal(dtype, D):
+    c = dict(Z=2, H=2, N=384, D=D, dtype=dtype, seed=77 + D)
+    q, k, v, do = cases.attn_inputs(c)
+    got = run_gpu(q, k, v, do, False, 0.5, True)
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), False, 0.5, dtype)
+    dq, dk, dv = R.attention_bwd_full(f32(q), f32(k), f32(v), o, f32(do), M, 0.5, False, dtype)
+    tol = 1e-2 if dtype == "fp16" else 2e-2
+    for key, want in (("dq", dq), ("dk", dk), ("dv", dv)):
+        np.testing.assert_allclose(got[key], want, rtol=1e-2, atol=tol, err_msg=key)
+
+
+def test_strided_inputs_and_errors():
+    # q, k, v as slices of one packed [Z, N, 3, H, D] buffer (strided, head dim contiguous)
+    Z, H, N, D = 2, 3, 256, 64
+    g = torch.Generator().manual_seed(3)
+    packed = (torch.randn(Z, N, 3, H, D, generator=g) * 0.5).half().to(DEV)
+    q, k, v = (packed[:, :, i].permute(0, 2, 1, 3) for i in range(3))
+    o, M = triton_b200.attention_forward(q, k, v, True, 0.125)
+    oc, Mc = triton_b200.attention_forward(q.contiguous(), k.contiguous(), v.contiguous(), True, 0.125)
+    assert torch.equal(o, oc) and torch.equal(M, Mc)
+    with pytest.raises(RuntimeError, match="head dim"):
+        x = torch.zeros(1, 1, 128, 32, dtype=torch.float16, device=DEV)
+        triton_b200.attention_forward(x, x, x, True, 0.5)
+    status_ok()
+
+
+def _check_heads(q, k, v, do, got, heads, causal, sm_scale, dtype, bwd):
+    for (z, h) in heads:
+        sl = (slice(z, z + 1), slice(h, h + 1))
+        qq, kk, vv = (f32(t[sl]) for t in (q, k, v))
+        o, M = R.attention_fwd(qq, kk, vv, causal, sm_scale, dtype)
+        np.testing.assert_allclose(got["o"][sl], o, rtol=1e-2, atol=1e-2)
+        np.testing.assert_allclose(got["m"][sl], M, rtol=1e-4, atol=1e-3)
+        if bwd:
+            dq, dk, dv = R.attention_bwd(qq, kk, vv, o, f32(do[sl]), M, sm_scale, dtype)
+            for key, want in (("dq", dq), ("dk", dk), ("dv", dv)):
+                np.testing.assert_allclose(got[key][sl], want, rtol=1e-2, atol=2e-2, err_msg=key)
+
+
+def test_config4_full_size_forward():
+    """Z4 H32 N4096 D128 fp16 causal: three sampled heads against the oracle, bitwise repeatability,
+    and the row-stochastic property: with V = 1 every output element is 1."""
+    c = dict(Z=4, H=32, N=4096, D=128, dtype="fp16", seed=20)
+    q, k, v, _ = cases.attn_inputs(c)
+    sm = 128 ** -0.5
+    got = run_gpu(q, k, v, None, True, sm, False)
+    _check_heads(q, k, v, None, got, [(0, 0), (2, 17), (3, 31)], True, sm, "fp16", False)
+    qd, kd = q.to(DEV), k.to(DEV)
+    o2, M2 = triton_b200.attention_forward(qd, kd, v.to(DEV), True, sm)
+    assert np.array_equal(f32(o2), got["o"]) and np.array_equal(f32(M2), got["m"])
+    ones, _ = triton_b200.attention_forward(qd, kd, torch.ones_like(qd), True, sm)
+    np.testing.assert_allclose(f32(ones), 1.0, atol=2e-3)
+    status_ok()
+
+
+def test_config5_full_size_forward_backward():
+    """Z4 H48 N1024 D64 bf16 causal forward + backward on sampled heads; dV of an all-ones dO
+    equals the column sums of P (checked through sum over keys = number of queries)."""
+    c = dict(Z=4, H=48, N=1024, D=64, dtype="bf16", seed=20)
+    q, k, v, do = cases.attn_inputs(c)
+    got = run_gpu(q, k, v, do, True, 0.5, True)
+    _check_heads(q, k, v, do, got, [(0, 0), (1, 23), (3, 47)], True, 0.5, "bf16", True)
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    o, M = triton_b200.attention_forward(qd, kd, vd, True, 0.5)
+    dq, dk, dv = triton_b200.attention_backward(qd, kd, vd, o, M, torch.ones_like(qd), True, 0.5)
+    col = dv.float().sum(2)  # sum over keys of sum_q P[q, key] = N per (z, h, d)
+    np.testing.assert_allclose(f32(col), 1024.0, rtol=2e-2)
+    dq2, dk2, dv2 = triton_b200.attention_backward(qd, kd, vd, o, M, torch.ones_like(qd), True, 0.5)
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    status_ok()

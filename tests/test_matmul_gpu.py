@@ -1,0 +1,172 @@
+"""Parity of the CUDA matmul (through the C ABI) with the CPU oracle, the interpreter-generated
+golden fixtures and, at the benchmark's full size, size-independent properties.
+
+Tolerances: rtol = atol = 1e-2 for fp16 / bf16 (python/tutorials/03-matrix-multiplication.py:
+367-368 uses atol 1e-2 against torch), relative Frobenius error <= 2e-2 for fp8 with scales
+(python/test/unit/language/test_core.py:5172-5173 uses rtol = atol = 1e-2 on the accumulator)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import triton_b200
+from oracle import ref_ops as R
+from triton_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def f32(t):
+    return t.detach().float().cpu().numpy()
+
+
+def status_ok():
+    assert _lib.status() == 0, "a bounded device-side wait ran out"
+
+
+@pytest.mark.parametrize("name", list(cases.MATMUL_CASES))
+def test_matmul_parity_with_oracle_and_golden(golden, name):
+    c = cases.MATMUL_CASES[name]
+    a, b = cases.matmul_inputs(c)
+    got = triton_b200.matmul(a.to(DEV), b.to(DEV), activation=c.get("activation", ""))
+    status_ok()
+    assert got.dtype == torch.float16 and got.shape == (c["M"], c["N"])
+    want = R.matmul(f32(a), f32(b), activation=c.get("activation", ""))
+    np.testing.assert_allclose(f32(got), want, rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(f32(got), golden[f"matmul.{name}.c"].astype(np.float32), rtol=1e-2, atol=1e-2)
+    # one fp32 accumulation and one rounding on both sides: almost all elements are bit-identical
+    assert (f32(got) != want).mean() < 0.05
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(128, 64, 64), (1, 8, 8), (129, 257, 72), (1000, 520, 200), (2048, 2048, 512),
+                                   (8192, 8192, 1024)])
+@pytest.mark.parametrize("b_layout", ["kn", "nk"])
+def test_matmul_shapes_layouts(dtype, shape, b_layout):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M * 7 + N * 3 + K)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(K, N, generator=g).to(dtype)
+    bd = b.to(DEV)
+    if b_layout == "nk":
+        bd = bd.t().contiguous().t()
+    got = triton_b200.matmul(a.to(DEV), bd)
+    status_ok()
+    assert got.dtype == dtype
+    if M * N * K <= 2048 * 2048 * 512:
+        want = R.matmul(f32(a), f32(b), out="fp16" if dtype == torch.float16 else "bf16")
+    else:  # the python tile loop is too slow here; same arithmetic through one fp32 matmul
+        want = (a.float() @ b.float()).to(dtype).float().numpy()
+    tol = 1e-2 if dtype == torch.float16 else 2e-2
+    np.testing.assert_allclose(f32(got), want, rtol=tol, atol=tol)
+
+
+@pytest.mark.parametrize("tile", ["128064", "128128", "128256", "256256", "2256"])
+def test_every_tile_shape(monkeypatch, tile):
+    monkeypatch.setenv("B200_GEMM_TILE", tile)
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(600, 328, generator=g).half()
+    b = torch.randn(328, 712, generator=g).half()
+    got = triton_b200.matmul(a.to(DEV), b.to(DEV))
+    status_ok()
+    np.testing.assert_allclose(f32(got), R.matmul(f32(a), f32(b)), rtol=1e-2, atol=1e-2)
+
+
+def test_empty_and_degenerate():
+    a = torch.zeros(0, 16, dtype=torch.float16, device=DEV)
+    b = torch.zeros(16, 8, dtype=torch.float16, device=DEV)
+    assert triton_b200.matmul(a, b).shape == (0, 8)
+    a = torch.ones(5, 0, dtype=torch.float16, device=DEV)
+    b = torch.ones(0, 8, dtype=torch.float16, device=DEV)
+    c = triton_b200.matmul(a, b)
+    assert c.shape == (5, 8) and float(c.abs().sum()) == 0.0  # empty sum
+    # a stride the TMA path cannot address is an error, not a silent fallback
+    a = torch.ones(8, 12, dtype=torch.float16, device=DEV)
+    b = torch.ones(12, 6, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError, match="16 bytes"):
+        triton_b200.matmul(a, b)
+    status_ok()
+
+
+@pytest.mark.parametrize("name", list(cases.FP8_CASES))
+def test_fp8_accumulator_matches_golden(golden, name):
+    c = cases.FP8_CASES[name]
+    a8, b8, sa, sb = cases.fp8_inputs(c)
+    acc = triton_b200.matmul(a8.to(DEV), b8.to(DEV), out_dtype=torch.float32)
+    status_ok()
+    want = golden[f"fp8.{name}.acc"]
+    np.testing.assert_allclose(f32(acc), want, rtol=1e-2, atol=1e-2)
+    assert np.linalg.norm(f32(acc) - want) / np.linalg.norm(want) < 1e-5
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 512), (1024, 1024, 2048), (4096, 4096, 1024)])
+def test_fp8_scaled_parity(shape):
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g)
+    b = torch.randn(K, N, generator=g)
+    a8, sa = cases.quantize_e4m3(a)
+    b8, sb = cases.quantize_e4m3(b)
+    got = triton_b200.matmul(a8.to(DEV), b8.to(DEV), scale_a=sa, scale_b=sb)
+    status_ok()
+    assert got.dtype == torch.bfloat16
+    want = R.matmul_fp8(a8.view(torch.uint8).numpy(), b8.view(torch.uint8).numpy(), sa, sb, out="bf16")
+    rel = np.linalg.norm(f32(got) - want) / np.linalg.norm(want)
+    assert rel < 2e-2, rel
+    # and against the unquantised product: quantisation noise only
+    exact = (a @ b).numpy()
+    assert np.linalg.norm(f32(got) - exact) / np.linalg.norm(exact) < 6e-2
+    # device-side quantisation helper gives the same bits
+    a8d, sad = triton_b200.quantize_e4m3(a.to(DEV))
+    assert torch.equal(a8d.view(torch.uint8).cpu(), a8.view(torch.uint8))
+    assert abs(float(sad) - sa) / sa < 1e-6
+
+
+def _full_size_inputs(dtype):
+    g = torch.Generator().manual_seed(2024)
+    n = 8192
+    a = (torch.randn(n, n, generator=g) / n ** 0.5)
+    b = (torch.randn(n, n, generator=g) / n ** 0.5)
+    return a, b
+
+
+def test_full_size_fp16_properties():
+    """Config 2 (8192^3 fp16): sampled entries against fp64 dot products, the checksum identity
+    sum(C) = (1^T A)(B 1), and bitwise repeatability (catches shared-memory / TMEM races)."""
+    a, b = _full_size_inputs(torch.float16)
+    ah, bh = a.half(), b.half()
+    ad, bd = ah.to(DEV), bh.to(DEV)
+    c1 = triton_b200.matmul(ad, bd)
+    c2 = triton_b200.matmul(ad, bd)
+    status_ok()
+    assert torch.equal(c1, c2)
+    rs = np.random.RandomState(0)
+    rows = rs.randint(0, 8192, 64)
+    cols = rs.randint(0, 8192, 64)
+    a64 = ah[rows].double().numpy()
+    b64 = bh[:, cols].double().numpy()
+    want = a64 @ b64
+    got = c1[rows][:, cols].float().cpu().numpy()
+    np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2)
+    total = float(c1.double().sum())
+    ident = float(ah.double().sum(0) @ bh.double().sum(1))
+    assert abs(total - ident) < 1e-3 * max(1.0, abs(ident)) + 8192 * 8192 * 2e-5  # fp16 output rounding noise
+    # linearity in A: (2A) B = 2 (A B) exactly in binary floating point
+    c3 = triton_b200.matmul(ad * 2, bd)
+    assert torch.equal(c3, c1 * 2)
+
+
+def test_full_size_fp8_properties():
+    a, b = _full_size_inputs(torch.float32)
+    a8, sa = cases.quantize_e4m3(a * 8192 ** 0.5)
+    b8, sb = cases.quantize_e4m3(b * 8192 ** 0.5)
+    got = triton_b200.matmul(a8.to(DEV), b8.to(DEV), scale_a=sa, scale_b=sb)
+    got2 = triton_b200.matmul(a8.to(DEV), b8.to(DEV), scale_a=sa, scale_b=sb)
+    status_ok()
+    assert torch.equal(got, got2)
+    rs = np.random.RandomState(1)
+    rows, cols = rs.randint(0, 8192, 48), rs.randint(0, 8192, 48)
+    want = (a8[rows].double().numpy() @ b8[:, cols].double().numpy()) * (sa * sb)
+    g = got[rows][:, cols].float().cpu().numpy()
+    assert np.linalg.norm(g - want) / np.linalg.norm(want) < 2e-2
