@@ -171,7 +171,7 @@ int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int
   DeviceCtx* ctx = current_ctx();
   if (!ctx) return B200_ERR_DEVICE;
   if (M == 0 || N == 0) return B200_OK;
-  if (!a || !b || !c) return fail(B200_ERR_ARG, "null pointer");
+  if (!c || (K > 0 && (!a || !b))) return fail(B200_ERR_ARG, "null pointer");
   if (stride_cn != 1 && N != 1) return fail(B200_ERR_UNSUPPORTED, "C must have stride_cn == 1");
   if (K == 0) {
     // an empty sum: the reference's K loop does not run and the zero accumulator is stored
