@@ -226,6 +226,39 @@ def other_configs(torch, tb, dev):
     return out
 
 
+def run_profile_case(name):
+    """A few launches of one configuration's kernels and nothing else: the command line that the
+    ncu captures summarised under profiles/ were taken with (python bench.py --profile c4 ...)."""
+    import torch
+    import cases
+    import triton_b200 as tb
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(0)
+    if name == "c2":
+        a = (torch.randn(M, K, generator=g) / K ** 0.5).half().to(dev)
+        b = (torch.randn(K, N, generator=g) / K ** 0.5).half().to(dev)
+        fn = lambda: tb.matmul(a, b)
+    elif name == "c3":
+        a8, sa = tb.quantize_e4m3(torch.randn(M, K, generator=g).to(dev))
+        b8, sb = tb.quantize_e4m3(torch.randn(K, N, generator=g).to(dev))
+        fn = lambda: tb.matmul(a8, b8, scale_a=sa, scale_b=sb)
+    elif name == "c4":
+        q, k, v, _ = (t.to(dev) for t in cases.attn_inputs(dict(Z=4, H=32, N=4096, D=128, dtype="fp16", seed=20)))
+        fn = lambda: tb.attention_forward(q, k, v, True, 128 ** -0.5)
+    elif name == "c5":
+        q, k, v, do = (t.to(dev) for t in cases.attn_inputs(dict(Z=4, H=48, N=1024, D=64, dtype="bf16", seed=20)))
+
+        def fn():
+            o, m = tb.attention_forward(q, k, v, True, 0.5)
+            tb.attention_backward(q, k, v, o, m, do, True, 0.5)
+    else:
+        raise SystemExit("unknown profile case " + name)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    print("profile case", name, "done")
+
+
 def run_ours(args, rank, local_rank, world):
     import torch
     import triton_b200 as tb
@@ -324,13 +357,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the short timings of configs 1, 3, 4, 5")
+    ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5"],
+                    help="run three launches of one configuration and exit (for ncu captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
-    if args.impl == "reference":
+    if args.profile:
+        run_profile_case(args.profile)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, local_rank, world)
