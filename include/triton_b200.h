@@ -96,6 +96,32 @@ B200_API int b200_attention_bwd(b200_stream_t stream, const void* q, const void*
                                 const int64_t stride_dq[4], const int64_t stride_dk[4], const int64_t stride_dv[4],
                                 float sm_scale, int causal, int dtype);
 
+/* Same computation as b200_attention_bwd, for callers that may not allocate device memory.
+ * (No counterpart in the reference, whose Python wrapper allocates `delta` with torch.empty_like.)
+ * Some hosts of this library hand every byte of device memory to their own arena or planner at
+ * start-up - an inference server with a fixed memory plan, a runtime that forbids allocation on
+ * its hot path - and have nowhere to take the Z*H*N-float `delta` scratch from without going back
+ * to the allocator.  Here that scratch is a fixed array built into the library image: 2^20 floats
+ * (4 MiB), held by every GPU that loads the library until the process exits.  The call makes no
+ * cudaMalloc / cudaFree and uses no allocating library routine; inputs and outputs are still the
+ * caller's.
+ *   - Z*H*N must not exceed b200_attention_bwd_noalloc_capacity() (2^20); larger problems are
+ *     rejected with B200_ERR_UNSUPPORTED and a message.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on a device share the one array.  It keeps whatever the previous call left there;
+ *     nothing in it needs to start at zero because the pre-pass overwrites every row the main
+ *     kernels read.  Two calls whose kernels overlap on the GPU (different streams) race on it:
+ *     serialise them. */
+B200_API int b200_attention_bwd_noalloc(b200_stream_t stream, const void* q, const void* k, const void* v,
+                                        const void* o, const void* d_o, const float* m, void* dq, void* dk, void* dv,
+                                        int Z, int H, int N, int D, const int64_t stride_q[4],
+                                        const int64_t stride_k[4], const int64_t stride_v[4],
+                                        const int64_t stride_o[4], const int64_t stride_do[4],
+                                        const int64_t stride_dq[4], const int64_t stride_dk[4],
+                                        const int64_t stride_dv[4], float sm_scale, int causal, int dtype);
+B200_API long long b200_attention_bwd_noalloc_capacity(void);
+
 #ifdef __cplusplus
 }
 #endif

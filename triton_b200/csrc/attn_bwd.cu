@@ -21,6 +21,7 @@
 //   read U1/U2 through an N-major view of the same shared-memory tiles.
 // Warps 0-3 compute (one thread per TMEM lane), warp 4 issues MMAs, warp 5 runs TMA.
 #include <cmath>
+#include <mutex>
 
 #include "common.cuh"
 #include "host.h"
@@ -417,6 +418,33 @@ int launch_bwd_all(DeviceCtx* ctx, cudaStream_t stream, const void* o, const voi
 }
 
 }  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// Built-in scratch for b200_attention_bwd_noalloc: the delta vector lives in this fixed device
+// array instead of caller memory.  Every GPU that loads the library holds these 4 MiB until the
+// process exits.  In host code the name below is only a host-side stand-in for the symbol, not a
+// device address, so the address is looked up once per device with cudaGetSymbolAddress.
+constexpr long long kScratchFloats = 1ll << 20;  // rows (Z*H*N) one call may use
+static __device__ __align__(256) float g_delta_scratch[kScratchFloats];
+
+long long attn_bwd_scratch_capacity() { return kScratchFloats; }
+
+// Device address of the scratch array on the CURRENT device (looked up on first use per device).
+float* attn_bwd_scratch(DeviceCtx* ctx) {
+  static std::mutex mu;
+  static float* ptr[64] = {};
+  std::lock_guard<std::mutex> lk(mu);
+  if (!ptr[ctx->device]) {
+    float* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_delta_scratch);
+    if (e != cudaSuccess || !p) {
+      fail(B200_ERR_CUDA, "cudaGetSymbolAddress(delta scratch): %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptr[ctx->device] = p;
+  }
+  return ptr[ctx->device];
+}
 
 int launch_attn_bwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, const void* o,
                     const void* dout, const float* m, float* delta, void* dq, void* dk, void* dv, int Z, int H, int N,

@@ -231,4 +231,29 @@ int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const
                          causal, dtype);
 }
 
+long long b200_attention_bwd_noalloc_capacity(void) { return attn_bwd_scratch_capacity(); }
+
+int b200_attention_bwd_noalloc(b200_stream_t stream, const void* q, const void* k, const void* v, const void* o,
+                               const void* d_o, const float* m, void* dq, void* dk, void* dv, int Z, int H, int N,
+                               int D, const int64_t stride_q[4], const int64_t stride_k[4], const int64_t stride_v[4],
+                               const int64_t stride_o[4], const int64_t stride_do[4], const int64_t stride_dq[4],
+                               const int64_t stride_dk[4], const int64_t stride_dv[4], float sm_scale, int causal,
+                               int dtype) {
+  if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
+  const long long rows = (long long)Z * H * N;
+  if (rows > attn_bwd_scratch_capacity())
+    return fail(B200_ERR_UNSUPPORTED,
+                "Z*H*N = %lld rows exceed the built-in scratch of %lld rows; use b200_attention_bwd with caller "
+                "scratch for this size",
+                rows, attn_bwd_scratch_capacity());
+  if (rows == 0) return B200_OK;
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  float* delta = attn_bwd_scratch(ctx);
+  if (!delta) return B200_ERR_CUDA;
+  // same validation and launches as the caller-scratch entry point, on the built-in array
+  return b200_attention_bwd(stream, q, k, v, o, d_o, m, delta, dq, dk, dv, Z, H, N, D, stride_q, stride_k, stride_v,
+                            stride_o, stride_do, stride_dq, stride_dk, stride_dv, sm_scale, causal, dtype);
+}
+
 }  // extern "C"

@@ -53,6 +53,10 @@ int launch_attn_bwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
                     const int64_t* sdo, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv, float sm_scale,
                     int causal, int dtype);
 
+// built-in scratch of the no-allocation backward entry point (attn_bwd.cu)
+long long attn_bwd_scratch_capacity();
+float* attn_bwd_scratch(DeviceCtx* ctx);
+
 // 4-D tensor map over [Z, H, N, D] (D contiguous): boxes of 64 columns x box_rows rows, 128-byte swizzle
 bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
                     int64_t sn, int box_rows);
