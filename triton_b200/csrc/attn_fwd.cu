@@ -8,17 +8,20 @@
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong so that the
 // tensor pipe works on one tile while the other tile's softmax runs.
-//   warps 0-3 / 4-7   softmax of tile 0 / 1: one thread per row.  tcgen05.ld S (128 fp32), running
-//                     max and sum, exp2, P packed to 16 bit and written back over S in TMEM
+//   warps 0-7 / 8-15  softmax of tile 0 / 1: two threads per row (warps w and w+4 own the same TMEM
+//                     lanes and split the 128 columns; row max and row sum are exchanged through
+//                     shared memory), so the softmax of a block takes about half the time of a
+//                     one-thread-per-row layout - it sits on the S -> P -> PV dependency chain.
+//                     tcgen05.ld S, running max and sum, exp2, P packed to 16 bit and written back over S in TMEM
 //                     (tcgen05.st) as the A operand of the second MMA.  The accumulator O is
 //                     rescaled lazily: only when the running max grew by more than 2^8 does the
 //                     warp multiply its O rows in TMEM (the reference rescales every step; the
 //                     result is the same up to fp32 rounding since P and l carry the same factor).
 //                     At the end: O / l -> storage type -> global, M -> global.
-//   warp 8            MMA issuer (one thread): S_i = Q_i K_j^T (operands in shared memory) and
+//   warp 16           MMA issuer (one thread): S_i = Q_i K_j^T (operands in shared memory) and
 //                     O_i += P_i V_j (P from TMEM, V from shared memory, N-major).  MMAs of one
 //                     thread execute in issue order, which is what lets P alias S.
-//   warp 9            TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
+//   warp 17           TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_i = first 64 columns of S_i.
 #include <cmath>
 #include <cstdlib>
@@ -31,7 +34,7 @@ namespace tb {
 namespace {
 
 constexpr int BLK = 128;           // rows of a Q tile and of a K/V block
-constexpr int FWD_THREADS = 320;   // 8 softmax warps + MMA warp + TMA warp
+constexpr int FWD_THREADS = 576;   // 16 softmax warps + MMA warp + TMA warp
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdParams {
@@ -49,7 +52,8 @@ template <int D>
 struct FwdCfg {
   static constexpr int TILE_BYTES = BLK * D * 2;               // one Q tile or one K / V block
   static constexpr int KV_STAGES = (D == 128) ? 4 : 8;
-  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 10) * 8 + 16 + 1024;
+  // tiles + barriers + TMEM slot + 3 x 512 floats of row statistics exchanged between column halves
+  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 10) * 8 + 16 + 3 * 512 * 4 + 1024;
 };
 
 template <int D>
@@ -58,12 +62,21 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, 
   for (int b = 0; b < D / 64; ++b) tma_load_4d(dst + b * (BLK * 128), map, bar, b * 64, row0, h, z);
 }
 
+// named barrier over the 256 softmax threads of one tile (ids 1 and 2; 0 is __syncthreads)
+__device__ __forceinline__ void tile_sync(int tile) {
+  if (tile == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
+  else asm volatile("bar.sync 2, 256;" ::: "memory");
+}
+
 template <int D, bool BF16>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using Cfg = FwdCfg<D>;
   constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES;
+  constexpr int MMA_WARP = 16, TMA_WARP = 17;
+  constexpr int HC = BLK / 2;  // score columns per softmax thread
+  constexpr int HD = D / 2;    // accumulator columns per softmax thread
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
@@ -78,6 +91,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* p_full = s_full + 2;      // [2] P_i(j) is in TMEM (and O_i rescaled if it had to be)
   uint64_t* o_full = p_full + 2;      // [2] last P V of tile i done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  // row statistics exchanged between the two threads of a row: [buffer][tile][half][row]
+  float* xchg = reinterpret_cast<float*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heavy (late) query blocks first within a head
@@ -92,7 +107,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 256);
       mbar_init(&o_full[i], 1);
     }
     for (int s = 0; s < NST; ++s) {
@@ -104,7 +119,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
   }
-  if (warp == 8) {
+  if (warp == MMA_WARP) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -115,7 +130,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tm_s[2] = {tmem_base, tmem_base + 128};
   const uint32_t tm_o[2] = {tmem_base + 256, tmem_base + 384};
 
-  if (warp == 9) {
+  if (warp == TMA_WARP) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       for (int i = 0; i < 2; ++i) {
@@ -133,8 +148,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp == 8) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
+    // One thread issues for both tiles.  (Two issuing threads, one per tile, were measured 20 %
+    // slower: MMAs of different threads interleave in the pipe at a cost.)
     if (lane == 0) {
       constexpr int FMT = BF16 ? 1 : 0;
       constexpr uint32_t IDESC_S = make_idesc(FMT, FMT, 0, 0, 128, BLK);  // Q (K-major) x K (K-major)
@@ -201,115 +218,130 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    const int i = warp >> 2;                // tile
-    const uint32_t quarter = warp & 3u;     // TMEM lanes [32*quarter, +32)
+    // 8 warps per tile: warps w and w+4 share TMEM lanes (rows) and split the columns in halves.
+    const int i = warp >> 3;                 // tile
+    const int half = (warp >> 2) & 1;        // column half of the scores / of the accumulator
+    const uint32_t quarter = warp & 3u;      // TMEM lanes [32*quarter, +32)
     const int row_in_tile = quarter * 32 + lane;
     const int row = qb * 256 + i * BLK + row_in_tile;  // query index
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const int nb = i ? n1 : n0;
     const float scale = p.scale_log2;
-    float m_ref = -INFINITY, l = 0.f;
+    float* x_mine = xchg + (i * 2 + half) * BLK + row_in_tile;        // + buffer * 512
+    float* x_other = xchg + (i * 2 + (half ^ 1)) * BLK + row_in_tile;
+    float m_ref = -INFINITY, l = 0.f;  // l: this thread's half of the row sum
 
     for (int j = 0; j < nb; ++j) {
       mbar_wait(&s_full[i], j & 1, p.status, SITE_FWD_S_FULL);
       tc_fence_after();
-      uint32_t r[BLK];
+      uint32_t r[HC];
 #pragma unroll
-      for (int c = 0; c < BLK; c += 32) tmem_ld32(tm_s[i] + lane_addr + c, r + c);
+      for (int c = 0; c < HC; c += 32) tmem_ld32(tm_s[i] + lane_addr + half * HC + c, r + c);
       tmem_ld_wait();
-      const int col0 = j * BLK;
-      const bool need_mask = (p.causal && col0 + BLK - 1 > qb * 256 + i * BLK) || (col0 + BLK > p.N);
-      float mx = -INFINITY;
+      const int col0 = j * BLK + half * HC;
+      const bool need_mask = (p.causal && j * BLK + BLK - 1 > qb * 256 + i * BLK) || (j * BLK + BLK > p.N);
       if (need_mask) {
 #pragma unroll
-        for (int c = 0; c < BLK; ++c) {
+        for (int c = 0; c < HC; ++c) {
           const int col = col0 + c;
           const bool ok = (col < p.N) && (!p.causal || col <= row);
-          const float v = ok ? __uint_as_float(r[c]) : -INFINITY;
-          r[c] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          if (!ok) r[c] = __float_as_uint(-INFINITY);
         }
-      } else {
-#pragma unroll
-        for (int c = 0; c < BLK; ++c) mx = fmaxf(mx, __uint_as_float(r[c]));
       }
-      const float m_new = fmaxf(m_ref, mx * scale);  // mx is finite: every row sees >= 1 valid column
-      // lazy rescale of the accumulator (warp-uniform decision: tcgen05.ld/st are warp collectives)
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < HC; c += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          mx4[u] = max3(mx4[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // combine with the other half of the row (double-buffered by block parity)
+      x_mine[(j & 1) * 512] = mx;
+      tile_sync(i);
+      mx = fmaxf(mx, x_other[(j & 1) * 512]);
+      // mx is finite: every row sees at least one valid column in every block it visits
+      const float m_new = fmaxf(m_ref, mx * scale);
+      // lazy rescale of the accumulator (both threads of a row take the same decision; the ld/st
+      // below are warp collectives, so the warp rescales if any of its rows has to)
       const bool grow = (m_new - m_ref) > kRescaleThreshold;  // true on the first block (m_ref = -inf)
       if (__any_sync(0xffffffffu, grow)) {
         const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
         if (grow) { m_ref = m_new; l *= alpha; }
         if (j > 0) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t o[32];
-            tmem_ld32(tm_o[i] + lane_addr + c, o);
+          for (int c = 0; c < HD; c += 16) {
+            uint32_t o[16];
+            tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
-            tmem_st32(tm_o[i] + lane_addr + c, o);
+            for (int k = 0; k < 16; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+            tmem_st16(tm_o[i] + lane_addr + half * HD + c, o);
           }
         }
       }
       const float neg_m = -m_ref;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < BLK; c += 32) {
+      for (int c = 0; c < HC; c += 32) {
         uint32_t w[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
           const float p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
           const float p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));
-          sum += p0 + p1;
+          sum4[k & 3] += p0 + p1;
           w[k] = pack2<BF16>(p0, p1);
         }
-        tmem_st16(tm_s[i] + lane_addr + (c >> 1), w);
+        tmem_st16(tm_s[i] + lane_addr + ((half * HC + c) >> 1), w);
       }
-      l += sum;
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full[i]);
     }
 
-    // epilogue: O / l and M
+    // epilogue: the row sum is the two halves' sums; O / l and M
+    x_mine[1024] = l;
+    tile_sync(i);
+    l += x_other[1024];
     mbar_wait(&o_full[i], 0, p.status, SITE_FWD_O_FULL);
     tc_fence_after();
     const float inv_l = 1.f / l;
     const bool valid = row < p.N;
     uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)z * p.o_sz + (long long)h * p.o_sh +
-                     (long long)row * p.o_sn;
+                     (long long)row * p.o_sn + half * HD;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.o) & 15) == 0) && ((p.o_sn & 7) == 0) && ((p.o_sh & 7) == 0) &&
                         ((p.o_sz & 7) == 0);
 #pragma unroll 1
-    for (int c = 0; c < D; c += 32) {
-      uint32_t o[32];
-      tmem_ld32(tm_o[i] + lane_addr + c, o);
+    for (int c = 0; c < HD; c += 16) {
+      uint32_t o[16];
+      tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
       tmem_ld_wait();
       if (valid) {
-        uint32_t w[16];
+        uint32_t w[8];
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
+        for (int k = 0; k < 8; ++k)
           w[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
         if (vec_ok) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
+          for (int k = 0; k < 2; ++k)
             reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
         } else {
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
+          for (int k = 0; k < 8; ++k) {
             orow[c + 2 * k] = (uint16_t)(w[k] & 0xFFFFu);
             orow[c + 2 * k + 1] = (uint16_t)(w[k] >> 16);
           }
         }
       }
     }
-    if (valid) p.m[(long long)zh * p.N + row] = m_ref + log2f(l);
+    if (valid && half == 0) p.m[(long long)zh * p.N + row] = m_ref + log2f(l);
   }
 
   if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
