@@ -19,7 +19,7 @@
 //       accA += dS U1       (dK += dS^T Q, or dQ += dS K)
 //   T1/T2 live in TMEM and P/dS overwrite them as 16-bit A operands of the last two MMAs, which
 //   read U1/U2 through an N-major view of the same shared-memory tiles.
-// Warps 0-3 compute (one thread per TMEM lane), warp 4 issues MMAs, warp 5 runs TMA.
+// Warps 0-7 compute (two threads per row, splitting the columns), warp 8 issues MMAs, warp 9 runs TMA.
 #include <cmath>
 #include <mutex>
 
@@ -31,7 +31,7 @@ namespace tb {
 namespace {
 
 constexpr int BLK = 128;
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // 8 compute warps + MMA warp + TMA warp
 
 struct BwdParams {
   const float* m;      // [Z*H, N] base-2 LSE from the forward
@@ -110,8 +110,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
     mbar_init(t1_full, 1);
     mbar_init(t2_full, 1);
-    mbar_init(p_full, 128);
-    mbar_init(ds_full, 128);
+    mbar_init(p_full, 256);
+    mbar_init(ds_full, 256);
     mbar_init(acc_full, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tm_r1);
@@ -119,7 +119,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     tma_prefetch_desc(&tm_u1);
     tma_prefetch_desc(&tm_u2);
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -129,7 +129,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const uint32_t tm_t1 = tmem_base, tm_t2 = tmem_base + 128, tm_a = tmem_base + 256, tm_b = tmem_base + 256 + D;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       mbar_expect_tx(r_full, 2 * TILE);
@@ -150,7 +150,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       }
     }
     __syncwarp();
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr int FMT = BF16 ? 1 : 0;
@@ -222,8 +222,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------------ compute (one thread per TMEM lane)
+    // ------------------------------------------------------------------ compute
+    // Two threads per row: warps w and w+4 own the same TMEM lanes and split the 128 columns of
+    // T1 / T2 (and, in the epilogue, of the accumulators) in halves.  P and dS are packed over the
+    // FIRST 64 columns of T1 / T2, i.e. over columns the other half's thread reads, so a named
+    // barrier separates "both halves have read" from "either half writes".
     const uint32_t quarter = warp & 3u;
+    const int half = warp >> 2;
+    constexpr int HC = BLK / 2, HD = D / 2;
     const int r = quarter * 32 + lane;       // row inside the block
     const int grow = blk * BLK + r;          // kv index (dK/dV kernel) or q index (dQ kernel)
     const uint32_t lane_addr = (quarter * 32u) << 16;
@@ -237,31 +243,33 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     uint32_t s = 0;
     for (int it = 0; it < steps; ++it) {
       const int t = t_lo + it;
-      const float* sm = reinterpret_cast<const float*>(sring + s * STAGE + 2 * TILE);  // column M
-      const float* sd = sm + 128;                                                       // column delta
+      const float* sm = reinterpret_cast<const float*>(sring + s * STAGE + 2 * TILE) + half * HC;  // column M
+      const float* sd = sm + 128;                                                                  // column delta
       // the diagonal block is the only one that needs the causal mask
       const bool diag = p.causal && (t == blk);
       mbar_wait(t1_full, it & 1, p.status, SITE_BWD_S_FULL);
       tc_fence_after();
-      uint32_t pr[BLK];  // P as fp32 bits
+      uint32_t pr[HC];  // P as fp32 bits
 #pragma unroll
-      for (int c = 0; c < BLK; c += 32) tmem_ld32(tm_t1 + lane_addr + c, pr + c);
+      for (int c = 0; c < HC; c += 32) tmem_ld32(tm_t1 + lane_addr + half * HC + c, pr + c);
       tmem_ld_wait();
+      if (!DQ) asm volatile("bar.sync 1, 256;" ::: "memory");  // both halves hold their T1 columns in registers
 #pragma unroll
-      for (int c = 0; c < BLK; ++c) {
+      for (int c = 0; c < HC; ++c) {
         const float mm = DQ ? m_row : sm[c];
         float pv = ex2(fmaf(__uint_as_float(pr[c]), scale, -mm));
         // dK/dV kernel: row = kv, column = q, keep q >= kv.   dQ kernel: row = q, column = kv, keep kv <= q.
-        if (diag && (DQ ? (c > r) : (c < r))) pv = 0.f;
+        const int cc = half * HC + c;
+        if (diag && (DQ ? (cc > r) : (cc < r))) pv = 0.f;
         pr[c] = __float_as_uint(pv);
       }
       if (!DQ) {
 #pragma unroll
-        for (int c = 0; c < BLK; c += 32) {
+        for (int c = 0; c < HC; c += 32) {
           uint32_t w[16];
 #pragma unroll
           for (int k = 0; k < 16; ++k) w[k] = pack2<BF16>(__uint_as_float(pr[c + 2 * k]), __uint_as_float(pr[c + 2 * k + 1]));
-          tmem_st16(tm_t1 + lane_addr + (c >> 1), w);
+          tmem_st16(tm_t1 + lane_addr + ((half * HC + c) >> 1), w);
         }
         tmem_st_wait();
         tc_fence_before();
@@ -269,41 +277,41 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       }
       mbar_wait(t2_full, it & 1, p.status, SITE_BWD_DP_FULL);
       tc_fence_after();
+      uint32_t dsw[HC / 2];  // dS packed to 16 bit
 #pragma unroll
-      for (int c = 0; c < BLK; c += 32) {
+      for (int c = 0; c < HC; c += 32) {
         uint32_t dp[32];
-        tmem_ld32(tm_t2 + lane_addr + c, dp);
+        tmem_ld32(tm_t2 + lane_addr + half * HC + c, dp);
         tmem_ld_wait();
-        uint32_t w[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
           const float d0 = DQ ? d_row : sd[c + 2 * k];
           const float d1 = DQ ? d_row : sd[c + 2 * k + 1];
           const float ds0 = __uint_as_float(pr[c + 2 * k]) * (__uint_as_float(dp[2 * k]) - d0);
           const float ds1 = __uint_as_float(pr[c + 2 * k + 1]) * (__uint_as_float(dp[2 * k + 1]) - d1);
-          w[k] = pack2<BF16>(ds0, ds1);
+          dsw[(c >> 1) + k] = pack2<BF16>(ds0, ds1);
         }
-        // all 128 columns of T2 must be read before the packed dS overwrites its first 64 columns:
-        // chunk c writes columns [c/2, c/2+16), which chunk c' > c has not read only if c/2+16 > c' -> c' < 32
-        // i.e. only chunk 0's write (columns 0-15) could clobber unread data of chunk 0 itself (already read).
-        tmem_st16(tm_t2 + lane_addr + (c >> 1), w);
       }
+      asm volatile("bar.sync 2, 256;" ::: "memory");  // both halves have read all of T2
+#pragma unroll
+      for (int c = 0; c < HC / 2; c += 16) tmem_st16(tm_t2 + lane_addr + half * (HC / 2) + c, dsw + c);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(ds_full);
       if (++s == NST) s = 0;
     }
 
-    // epilogue
+    // epilogue: each thread stores its half of the accumulator columns
     mbar_wait(acc_full, 0, p.status, SITE_BWD_ACC_FULL);
     tc_fence_after();
     auto store_rows = [&](uint32_t tm_acc, void* out, long long sz, long long sh, long long sn, float mul) {
-      uint16_t* orow = reinterpret_cast<uint16_t*>(out) + (long long)z * sz + (long long)h * sh + (long long)grow * sn;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(out) + (long long)z * sz + (long long)h * sh + (long long)grow * sn +
+                       half * HD;
       const bool vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((sn & 7) == 0) && ((sh & 7) == 0) && ((sz & 7) == 0);
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
+      for (int c = 0; c < HD; c += 32) {
         uint32_t o[32];
-        tmem_ld32(tm_acc + lane_addr + c, o);
+        tmem_ld32(tm_acc + lane_addr + half * HD + c, o);
         tmem_ld_wait();
         uint32_t w[16];
 #pragma unroll
@@ -329,7 +337,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
