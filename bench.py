@@ -20,7 +20,6 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
 import threading
 import time
@@ -44,15 +43,21 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 20 ms; summarised over the
-    samples that fall inside the timed region (mark() brackets it)."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    """SM clock, power and throttle reasons of one GPU, read (never set) through NVML every few
+    milliseconds by a thread; summarised over the samples inside the timed region (mark() brackets it)."""
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
-        self.t0 = self.t1 = None
+        self.index, self.rows, self.t0, self.t1 = index, [], None, None
+        self.stop_flag = threading.Event()
+        self.thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.nv, self.err = None, repr(e)
 
     def mark(self):
         if self.t0 is None:
@@ -60,48 +65,44 @@ class ClockSampler:
         else:
             self.t1 = time.time()
 
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-            time.sleep(0.5)  # let the sampler come up before the GPU work starts
-        except OSError:
-            self.proc = None
+    def _poll(self):
+        nv = self.nv
+        while not self.stop_flag.is_set():
+            try:
+                sm = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                pw = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                try:
+                    rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    rs = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.rows.append((time.time(), sm, pw, rs))
+            except Exception:
+                pass
+            time.sleep(0.002)
 
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) >= 7:
-                self.rows.append((time.time(), parts))
+    def start(self):
+        if self.nv:
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
 
     def stop(self):
-        if not self.proc:
-            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, reasons, smax, power = [], set(), None, []
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        inside = [r for t, r in self.rows if self.t0 and self.t1 and self.t0 <= t <= self.t1 + 0.03]
-        rows = inside if inside else [r for _, r in self.rows]
+        if not self.nv:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["NVML unavailable: " + self.err])
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        nv = self.nv
+        inside = [r for r in self.rows if self.t0 and self.t1 and self.t0 <= r[0] <= self.t1]
+        rows = inside if inside else self.rows
+        bits = 0
         for r in rows:
-            try:
-                sm.append(float(r[0]))
-                smax = float(r[1])
-                power.append(float(r[2]))
-            except ValueError:
-                continue
-            for nm, v in zip(names, r[3:7]):
-                if v.lower().startswith("active"):
-                    reasons.add(nm)
-        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=smax,
-                    power_w_max=max(power) if power else None, samples=len(sm),
-                    window="timed region" if inside else "whole run", reasons=sorted(reasons))
+            bits |= r[3]
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40,
+                 "sw_thermal_slowdown": 0x20, "hw_power_brake_slowdown": 0x80}
+        reasons = sorted(k for k, v in names.items() if bits & v)
+        sm = [r[1] for r in rows]
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_min_mhz=min(sm) if sm else None,
+                    sm_max_mhz=self.max_sm, power_w_max=max(r[2] for r in rows) if rows else None,
+                    samples=len(rows), window="timed region" if inside else "whole run", reasons=reasons)
 
 
 def cpu_threads():
@@ -346,8 +347,9 @@ def run_ours(args, rank, local_rank, world):
         dist.destroy_process_group()
 
 
-# filled in from the ncu capture (bytes); None until a capture of the current kernel exists
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_kernel<256,256,3> launch on this workload
+# (879.5 MB + 120.1 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md); algorithmic: 402.7 MB
+TRAFFIC_BYTES_PER_LAUNCH = 999_603_200
 
 
 def main():
