@@ -133,9 +133,19 @@ def time_oracle(rows, reps=1):
     return 2.0 * rows * N * K / dt / 1e12, dt
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm is meant to use every core."""
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=os.cpu_count() or 1)
+    except Exception:
+        pass
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
+    use_all_host_threads()
     # size the per-step sample so that the whole run stays within a few minutes
     _, probe = time_oracle(128)
     budget = 150.0 / max(1, args.steps + args.warmup)
@@ -334,6 +344,7 @@ def run_ours(args, rank, local_rank, world):
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH},
         }
         if world == 1:
+            use_all_host_threads()
             rows = 2048
             v, dt = time_oracle(rows)
             line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
