@@ -373,6 +373,10 @@ def main():
     ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5"],
                     help="run three launches of one configuration and exit (for ncu captures)")
     args = ap.parse_args()
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm and the cpu_baseline leg are meant to
+    # use every host core, and BLAS reads the variable when numpy is first imported (below, lazily)
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = str(os.cpu_count() or 1)
     rank = int(os.environ.get("RANK", 0))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
