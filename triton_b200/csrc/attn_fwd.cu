@@ -22,14 +22,21 @@
 //                     O_i += P_i V_j (P from TMEM, V from shared memory, N-major).  MMAs of one
 //                     thread execute in issue order, which is what lets P alias S.
 //   warp 17           TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
+// The kernel is persistent: one CTA per SM takes work items (256 query rows of one head) from an
+// atomic counter, head-major and heavy-first, so a head's K/V stay in L2, causal work balances, and
+// the epilogue of one item overlaps the loads and first MMAs of the next.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_i = first 64 columns of S_i.
 #include <cmath>
 #include <cstdlib>
+#include <mutex>
 
 #include "common.cuh"
 #include "host.h"
 
 namespace tb {
+
+// work counters of the persistent forward kernel (see launch_attn_fwd)
+__device__ int g_fwd_sched[64];
 
 namespace {
 
@@ -45,6 +52,8 @@ struct FwdParams {
   int causal;
   float scale_log2;  // sm_scale * log2(e)
   int num_qb;        // 256-row query blocks per head
+  int total_items;   // num_qb * Z * H
+  int* sched_counter;  // work counter of this launch (zeroed before the launch)
   unsigned* status;
 };
 
@@ -53,7 +62,7 @@ struct FwdCfg {
   static constexpr int TILE_BYTES = BLK * D * 2;               // one Q tile or one K / V block
   static constexpr int KV_STAGES = (D == 128) ? 4 : 8;
   // tiles + barriers + TMEM slot + 3 x 512 floats of row statistics exchanged between column halves
-  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 10) * 8 + 16 + 3 * 512 * 4 + 1024;
+  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 16) * 8 + 16 + 3 * 512 * 4 + 1024;
 };
 
 template <int D>
@@ -66,6 +75,24 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, 
 __device__ __forceinline__ void tile_sync(int tile) {
   if (tile == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
   else asm volatile("bar.sync 2, 256;" ::: "memory");
+}
+
+// One work item = 256 query rows of one (batch, head).  Items are numbered head-major, heavy
+// (late, long) query blocks first inside a head, and handed out through an atomic counter.
+struct Item {
+  int qb, zh, z, h, n0, n1;
+};
+__device__ __forceinline__ Item decode_item(const FwdParams& p, int w) {
+  Item it;
+  it.zh = w / p.num_qb;
+  it.qb = p.num_qb - 1 - (w % p.num_qb);
+  it.z = it.zh / p.H;
+  it.h = it.zh % p.H;
+  const int nkv_all = (p.N + BLK - 1) / BLK;
+  // K/V blocks per tile: up to and including the block that holds the tile's diagonal when causal
+  it.n0 = p.causal ? min(2 * it.qb + 1, nkv_all) : nkv_all;
+  it.n1 = p.causal ? min(2 * it.qb + 2, nkv_all) : nkv_all;  // n0 <= n1 <= n0 + 1
+  return it;
 }
 
 template <int D, bool BF16>
@@ -84,24 +111,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* sq = smem;                // Q tiles 0, 1
   uint8_t* skv = smem + 2 * TILE;    // ring
   uint64_t* bars = reinterpret_cast<uint64_t*>(skv + NST * TILE);
-  uint64_t* q_full = bars;            // [2]
-  uint64_t* kv_full = bars + 2;       // [NST]
-  uint64_t* kv_empty = kv_full + NST; // [NST]
-  uint64_t* s_full = kv_empty + NST;  // [2] S_i(j) is in TMEM
-  uint64_t* p_full = s_full + 2;      // [2] P_i(j) is in TMEM (and O_i rescaled if it had to be)
-  uint64_t* o_full = p_full + 2;      // [2] last P V of tile i done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 2);
+  uint64_t* q_full = bars;             // [2]
+  uint64_t* kv_full = bars + 2;        // [NST]
+  uint64_t* kv_empty = kv_full + NST;  // [NST]
+  uint64_t* s_full = kv_empty + NST;   // [2] S_i(j) is in TMEM
+  uint64_t* p_full = s_full + 2;       // [2] P_i(j) is in TMEM (and O_i rescaled if it had to be)
+  uint64_t* o_full = p_full + 2;       // [2] last P V of tile i done
+  uint64_t* q_empty = o_full + 2;      // [1] every S MMA of the item has read the Q tiles
+  uint64_t* sched_full = q_empty + 1;  // [2] an item id was published
+  uint64_t* sched_empty = sched_full + 2;  // [2] all 17 readers have taken it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + 2);
+  volatile int* sched_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
   // row statistics exchanged between the two threads of a row: [buffer][tile][half][row]
   float* xchg = reinterpret_cast<float*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // heavy (late) query blocks first within a head
-  const int qb = p.num_qb - 1 - (int)blockIdx.x;
-  const int zh = blockIdx.y, z = zh / p.H, h = zh % p.H;
-  const int nkv_all = (p.N + BLK - 1) / BLK;
-  // K/V blocks per tile: up to and including the block that holds the tile's diagonal when causal
-  const int n0 = p.causal ? min(2 * qb + 1, nkv_all) : nkv_all;
-  const int n1 = p.causal ? min(2 * qb + 2, nkv_all) : nkv_all;  // n0 <= n1 <= n0 + 1
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -109,7 +133,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 256);
       mbar_init(&o_full[i], 1);
+      mbar_init(&sched_full[i], 1);
+      mbar_init(&sched_empty[i], 17);  // MMA thread + one lane of each softmax warp
     }
+    mbar_init(q_empty, 1);
     for (int s = 0; s < NST; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
@@ -131,19 +158,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tm_o[2] = {tmem_base + 256, tmem_base + 384};
 
   if (warp == TMA_WARP) {
-    // ------------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------------ scheduler + TMA producer
     if (lane == 0) {
-      for (int i = 0; i < 2; ++i) {
-        mbar_expect_tx(&q_full[i], TILE);
-        load_tile<D>(sq + i * TILE, &tm_q, &q_full[i], qb * 256 + i * BLK, h, z);
-      }
-      uint32_t s = 0, ph = 0;
-      for (int j = 0; j < n1; ++j) {
-        for (int kv = 0; kv < 2; ++kv) {  // K_j then V_j
-          mbar_wait(&kv_empty[s], ph ^ 1u, p.status, SITE_FWD_KV_EMPTY);
-          mbar_expect_tx(&kv_full[s], TILE);
-          load_tile<D>(skv + s * TILE, kv == 0 ? &tm_k : &tm_v, &kv_full[s], j * BLK, h, z);
-          if (++s == NST) { s = 0; ph ^= 1u; }
+      uint32_t s = 0, ph = 0;  // K/V ring position, runs on across items
+      for (uint32_t n = 0;; ++n) {
+        const int w = atomicAdd(p.sched_counter, 1);
+        const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
+        mbar_wait(&sched_empty[slot], sph ^ 1u, p.status, SITE_FWD_SCHED);
+        sched_item[slot] = w;
+        mbar_arrive(&sched_full[slot]);
+        if (w >= p.total_items) break;
+        const Item it = decode_item(p, w);
+        mbar_wait(q_empty, (n & 1u) ^ 1u, p.status, SITE_FWD_Q);  // previous item's S MMAs are done with Q
+        for (int i = 0; i < 2; ++i) {
+          mbar_expect_tx(&q_full[i], TILE);
+          load_tile<D>(sq + i * TILE, &tm_q, &q_full[i], it.qb * 256 + i * BLK, it.h, it.z);
+        }
+        for (int j = 0; j < it.n1; ++j) {
+          for (int kv = 0; kv < 2; ++kv) {  // K_j then V_j
+            mbar_wait(&kv_empty[s], ph ^ 1u, p.status, SITE_FWD_KV_EMPTY);
+            mbar_expect_tx(&kv_full[s], TILE);
+            load_tile<D>(skv + s * TILE, kv == 0 ? &tm_k : &tm_v, &kv_full[s], j * BLK, it.h, it.z);
+            if (++s == NST) { s = 0; ph ^= 1u; }
+          }
         }
       }
     }
@@ -159,7 +196,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint64_t dq0 = smem_desc_sw128(smem_u32(sq), 0, 1024);
       const uint64_t dk0 = smem_desc_sw128(smem_u32(skv), 0, 1024);
       const uint64_t dv0 = smem_desc_sw128(smem_u32(skv), BLK * 128, 1024);  // LBO: next 64-column box
-      uint32_t s = 0, ph = 0;  // ring position of the next unconsumed K / V block
+      uint32_t s = 0, ph = 0;        // ring position of the next unconsumed K / V block
+      uint32_t pcnt[2] = {0, 0};     // blocks of tile i whose P has been consumed (parity of p_full)
 
       auto issue_s = [&](int i, uint32_t stage) {  // S_i = Q_i K^T, D/16 MMAs
         const uint64_t dq = dq0 + i * (TILE >> 4), dk = dk0 + stage * (TILE >> 4);
@@ -178,40 +216,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       };
       auto advance = [&]() { if (++s == NST) { s = 0; ph ^= 1u; } };
 
-      // prologue: S_0(0), S_1(0) on K_0
-      mbar_wait(&kv_full[s], ph, p.status, SITE_FWD_KV_FULL);
-      mbar_wait(&q_full[0], 0, p.status, SITE_FWD_Q);
-      issue_s(0, s);
-      mbar_wait(&q_full[1], 0, p.status, SITE_FWD_Q);
-      issue_s(1, s);
-      tc_commit(&kv_empty[s]);
-      advance();
-      for (int j = 0; j < n1; ++j) {
-        const uint32_t vs = s, vph = ph;  // V_j
+      for (uint32_t n = 0;; ++n) {
+        const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
+        mbar_wait(&sched_full[slot], sph, p.status, SITE_FWD_SCHED);
+        const int w = sched_item[slot];
+        mbar_arrive(&sched_empty[slot]);
+        if (w >= p.total_items) break;
+        const Item it = decode_item(p, w);
+        const int n0 = it.n0, n1 = it.n1;
+
+        // prologue: S_0(0), S_1(0) on K_0
+        mbar_wait(&kv_full[s], ph, p.status, SITE_FWD_KV_FULL);
+        mbar_wait(&q_full[0], n & 1u, p.status, SITE_FWD_Q);
+        issue_s(0, s);
+        mbar_wait(&q_full[1], n & 1u, p.status, SITE_FWD_Q);
+        issue_s(1, s);
+        tc_commit(&kv_empty[s]);
+        if (n1 == 1) tc_commit(q_empty);
         advance();
-        const uint32_t ks = s, kph = ph;  // K_{j+1} (if any)
-        const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
-        mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
-        if (j < n0) {
-          mbar_wait(&p_full[0], j & 1, p.status, SITE_FWD_P_FULL);
-          tc_fence_after();
-          issue_pv(0, vs, j > 0);
-          if (j == n0 - 1) tc_commit(&o_full[0]);
-          if (more0) {
-            mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
-            issue_s(0, ks);
-          }
-        }
-        mbar_wait(&p_full[1], j & 1, p.status, SITE_FWD_P_FULL);
-        tc_fence_after();
-        issue_pv(1, vs, j > 0);
-        tc_commit(&kv_empty[vs]);
-        if (j == n1 - 1) tc_commit(&o_full[1]);
-        if (more1) {
-          mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
-          issue_s(1, ks);
-          tc_commit(&kv_empty[ks]);
+        for (int j = 0; j < n1; ++j) {
+          const uint32_t vs = s, vph = ph;  // V_j
           advance();
+          const uint32_t ks = s, kph = ph;  // K_{j+1} (if any)
+          const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
+          mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
+          if (j < n0) {
+            mbar_wait(&p_full[0], pcnt[0]++ & 1u, p.status, SITE_FWD_P_FULL);
+            tc_fence_after();
+            issue_pv(0, vs, j > 0);
+            if (j == n0 - 1) tc_commit(&o_full[0]);
+            if (more0) {
+              mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+              issue_s(0, ks);
+            }
+          }
+          mbar_wait(&p_full[1], pcnt[1]++ & 1u, p.status, SITE_FWD_P_FULL);
+          tc_fence_after();
+          issue_pv(1, vs, j > 0);
+          tc_commit(&kv_empty[vs]);
+          if (j == n1 - 1) tc_commit(&o_full[1]);
+          if (more1) {
+            mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+            issue_s(1, ks);
+            tc_commit(&kv_empty[ks]);
+            if (j + 2 == n1) tc_commit(q_empty);  // that was the item's last S: the Q tiles may be replaced
+            advance();
+          }
         }
       }
     }
@@ -223,119 +273,138 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const int half = (warp >> 2) & 1;        // column half of the scores / of the accumulator
     const uint32_t quarter = warp & 3u;      // TMEM lanes [32*quarter, +32)
     const int row_in_tile = quarter * 32 + lane;
-    const int row = qb * 256 + i * BLK + row_in_tile;  // query index
     const uint32_t lane_addr = (quarter * 32u) << 16;
-    const int nb = i ? n1 : n0;
     const float scale = p.scale_log2;
     float* x_mine = xchg + (i * 2 + half) * BLK + row_in_tile;        // + buffer * 512
     float* x_other = xchg + (i * 2 + (half ^ 1)) * BLK + row_in_tile;
-    float m_ref = -INFINITY, l = 0.f;  // l: this thread's half of the row sum
-
-    for (int j = 0; j < nb; ++j) {
-      mbar_wait(&s_full[i], j & 1, p.status, SITE_FWD_S_FULL);
-      tc_fence_after();
-      uint32_t r[HC];
-#pragma unroll
-      for (int c = 0; c < HC; c += 32) tmem_ld32(tm_s[i] + lane_addr + half * HC + c, r + c);
-      tmem_ld_wait();
-      const int col0 = j * BLK + half * HC;
-      const bool need_mask = (p.causal && j * BLK + BLK - 1 > qb * 256 + i * BLK) || (j * BLK + BLK > p.N);
-      if (need_mask) {
-#pragma unroll
-        for (int c = 0; c < HC; ++c) {
-          const int col = col0 + c;
-          const bool ok = (col < p.N) && (!p.causal || col <= row);
-          if (!ok) r[c] = __float_as_uint(-INFINITY);
-        }
-      }
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < HC; c += 8) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          mx4[u] = max3(mx4[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
-      }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // combine with the other half of the row (double-buffered by block parity)
-      x_mine[(j & 1) * 512] = mx;
-      tile_sync(i);
-      mx = fmaxf(mx, x_other[(j & 1) * 512]);
-      // mx is finite: every row sees at least one valid column in every block it visits
-      const float m_new = fmaxf(m_ref, mx * scale);
-      // lazy rescale of the accumulator (both threads of a row take the same decision; the ld/st
-      // below are warp collectives, so the warp rescales if any of its rows has to)
-      const bool grow = (m_new - m_ref) > kRescaleThreshold;  // true on the first block (m_ref = -inf)
-      if (__any_sync(0xffffffffu, grow)) {
-        const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
-        if (grow) { m_ref = m_new; l *= alpha; }
-        if (j > 0) {
-#pragma unroll 1
-          for (int c = 0; c < HD; c += 16) {
-            uint32_t o[16];
-            tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int k = 0; k < 16; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
-            tmem_st16(tm_o[i] + lane_addr + half * HD + c, o);
-          }
-        }
-      }
-      const float neg_m = -m_ref;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-      for (int c = 0; c < HC; c += 32) {
-        uint32_t w[16];
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const float p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
-          const float p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));
-          sum4[k & 3] += p0 + p1;
-          w[k] = pack2<BF16>(p0, p1);
-        }
-        tmem_st16(tm_s[i] + lane_addr + ((half * HC + c) >> 1), w);
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(&p_full[i]);
-    }
-
-    // epilogue: the row sum is the two halves' sums; O / l and M
-    x_mine[1024] = l;
-    tile_sync(i);
-    l += x_other[1024];
-    mbar_wait(&o_full[i], 0, p.status, SITE_FWD_O_FULL);
-    tc_fence_after();
-    const float inv_l = 1.f / l;
-    const bool valid = row < p.N;
-    uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)z * p.o_sz + (long long)h * p.o_sh +
-                     (long long)row * p.o_sn + half * HD;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.o) & 15) == 0) && ((p.o_sn & 7) == 0) && ((p.o_sh & 7) == 0) &&
                         ((p.o_sz & 7) == 0);
+    uint32_t scnt = 0;  // blocks of this tile seen so far, across items (parity of s_full, exchange buffer)
+
+    for (uint32_t n = 0;; ++n) {
+      const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
+      int w = 0;
+      if (lane == 0) {
+        mbar_wait(&sched_full[slot], sph, p.status, SITE_FWD_SCHED);
+        w = sched_item[slot];
+        mbar_arrive(&sched_empty[slot]);
+      }
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (w >= p.total_items) break;
+      const Item it = decode_item(p, w);
+      const int qb = it.qb;
+      const int row = qb * 256 + i * BLK + row_in_tile;  // query index
+      const int nb = i ? it.n1 : it.n0;
+      float m_ref = -INFINITY, l = 0.f;  // l: this thread's half of the row sum
+
+      for (int j = 0; j < nb; ++j, ++scnt) {
+        mbar_wait(&s_full[i], scnt & 1u, p.status, SITE_FWD_S_FULL);
+        tc_fence_after();
+        uint32_t r[HC];
+#pragma unroll
+        for (int c = 0; c < HC; c += 32) tmem_ld32(tm_s[i] + lane_addr + half * HC + c, r + c);
+        tmem_ld_wait();
+        const int col0 = j * BLK + half * HC;
+        const bool need_mask = (p.causal && j * BLK + BLK - 1 > qb * 256 + i * BLK) || (j * BLK + BLK > p.N);
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < HC; ++c) {
+            const int col = col0 + c;
+            const bool ok = (col < p.N) && (!p.causal || col <= row);
+            if (!ok) r[c] = __float_as_uint(-INFINITY);
+          }
+        }
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < HC; c += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx4[u] = max3(mx4[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+        }
+        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        // combine with the other half of the row (double-buffered by block parity)
+        x_mine[(scnt & 1u) * 512] = mx;
+        tile_sync(i);
+        mx = fmaxf(mx, x_other[(scnt & 1u) * 512]);
+        // mx is finite: every row sees at least one valid column in every block it visits
+        const float m_new = fmaxf(m_ref, mx * scale);
+        // lazy rescale of the accumulator (both threads of a row take the same decision; the ld/st
+        // below are warp collectives, so the warp rescales if any of its rows has to)
+        const bool grow = (m_new - m_ref) > kRescaleThreshold;  // true on the first block (m_ref = -inf)
+        if (__any_sync(0xffffffffu, grow)) {
+          const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
+          if (grow) { m_ref = m_new; l *= alpha; }
+          if (j > 0) {
 #pragma unroll 1
-    for (int c = 0; c < HD; c += 16) {
-      uint32_t o[16];
-      tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
-      tmem_ld_wait();
-      if (valid) {
-        uint32_t w[8];
+            for (int c = 0; c < HD; c += 16) {
+              uint32_t o[16];
+              tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
+              tmem_ld_wait();
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          w[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
-        if (vec_ok) {
+              for (int k = 0; k < 16; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+              tmem_st16(tm_o[i] + lane_addr + half * HD + c, o);
+            }
+          }
+        }
+        const float neg_m = -m_ref;
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int k = 0; k < 2; ++k)
-            reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
-        } else {
+        for (int c = 0; c < HC; c += 32) {
+          uint32_t wv[16];
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            orow[c + 2 * k] = (uint16_t)(w[k] & 0xFFFFu);
-            orow[c + 2 * k + 1] = (uint16_t)(w[k] >> 16);
+          for (int k = 0; k < 16; ++k) {
+            const float p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));
+            sum4[k & 3] += p0 + p1;
+            wv[k] = pack2<BF16>(p0, p1);
+          }
+          tmem_st16(tm_s[i] + lane_addr + ((half * HC + c) >> 1), wv);
+        }
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_full[i]);
+      }
+
+      // epilogue: the row sum is the two halves' sums; O / l and M.  It overlaps the next item's
+      // Q / K loads and first S MMAs; the next item's first P V (which overwrites O) needs this
+      // tile's next P, i.e. comes after these reads in program order.
+      x_mine[1024] = l;
+      tile_sync(i);
+      l += x_other[1024];
+      mbar_wait(&o_full[i], n & 1u, p.status, SITE_FWD_O_FULL);
+      tc_fence_after();
+      const float inv_l = 1.f / l;
+      const bool valid = row < p.N;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)it.z * p.o_sz + (long long)it.h * p.o_sh +
+                       (long long)row * p.o_sn + half * HD;
+#pragma unroll 1
+      for (int c = 0; c < HD; c += 16) {
+        uint32_t o[16];
+        tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
+        tmem_ld_wait();
+        if (valid) {
+          uint32_t wv[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            wv[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
+          if (vec_ok) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k)
+              reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(wv[4 * k], wv[4 * k + 1], wv[4 * k + 2], wv[4 * k + 3]);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              orow[c + 2 * k] = (uint16_t)(wv[k] & 0xFFFFu);
+              orow[c + 2 * k + 1] = (uint16_t)(wv[k] >> 16);
+            }
           }
         }
       }
+      if (valid && half == 0) p.m[(long long)it.zh * p.N + row] = m_ref + log2f(l);
+      // the other half must have read x_other[1024] before the next item's epilogue rewrites it:
+      // guaranteed by the tile_sync calls of the next item's blocks (every item has >= 1 block)
     }
-    if (valid && half == 0) p.m[(long long)zh * p.N + row] = m_ref + log2f(l);
   }
 
   if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
@@ -357,7 +426,7 @@ int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, con
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(attn fwd): %s", cudaGetErrorString(e));
     attr_done[ctx->device] = true;
   }
-  dim3 grid(p.num_qb, p.Z * p.H, 1);
+  const int grid = p.total_items < ctx->sm_count ? p.total_items : ctx->sm_count;
   attn_fwd_kernel<D, BF16><<<grid, FWD_THREADS, smem, stream>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn fwd launch: %s", cudaGetErrorString(e));
@@ -388,7 +457,25 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
   p.Z = Z; p.H = H; p.N = N; p.causal = causal;
   p.scale_log2 = sm_scale * 1.44269504f;  // the reference's constant (06-fused-attention.py:161)
   p.num_qb = (N + 255) / 256;
+  p.total_items = p.num_qb * Z * H;
   p.status = ctx->status;
+  // Work counter: one of a ring of 64 device words, so that launches in flight on different streams
+  // do not share one (more than 64 forward launches in flight at once would).
+  {
+    static std::mutex mu;
+    static int* base[64] = {};
+    static unsigned next[64] = {};
+    std::lock_guard<std::mutex> lk(mu);
+    if (!base[ctx->device]) {
+      void* ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_fwd_sched);
+      if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaGetSymbolAddress(scheduler): %s", cudaGetErrorString(e));
+      base[ctx->device] = static_cast<int*>(ptr);
+    }
+    p.sched_counter = base[ctx->device] + (next[ctx->device]++ % 64);
+  }
+  cudaError_t me = cudaMemsetAsync(p.sched_counter, 0, sizeof(int), stream);
+  if (me != cudaSuccess) return fail(B200_ERR_CUDA, "scheduler reset: %s", cudaGetErrorString(me));
   const bool bf16 = dtype == B200_BF16;
   if (D == 128) return bf16 ? launch_fwd_t<128, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<128, false>(ctx, stream, tq, tk, tv, p);
   if (D == 64) return bf16 ? launch_fwd_t<64, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<64, false>(ctx, stream, tq, tk, tv, p);
