@@ -43,6 +43,8 @@ struct BwdParams {
   int causal;
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
+  int total_items;     // (N / 128) * Z * H
+  int* sched_counter;  // work counter of this launch (zeroed before the launch)
   unsigned* status;
 };
 
@@ -51,7 +53,7 @@ struct BwdCfg {
   static constexpr int TILE = BLK * D * 2;
   static constexpr int NST = (D == 128) ? 2 : 3;
   static constexpr int STAGE = 2 * TILE + 1024;  // U1, U2, column statistics (M, delta of the streamed rows)
-  static constexpr size_t SMEM = 2 * TILE + (size_t)NST * STAGE + (2 * NST + 8) * 8 + 16 + 1024;
+  static constexpr size_t SMEM = 2 * TILE + (size_t)NST * STAGE + (2 * NST + 14) * 8 + 32 + 1024;
 };
 
 template <int D>
@@ -69,6 +71,24 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
 
 // DQ = false: block = K/V block, R1 = K, R2 = V, stream (Q_i, dO_i), outputs dK (A), dV (B)
 // DQ = true : block = Q block,  R1 = Q, R2 = dO, stream (K_j, V_j), output dQ (A)
+// Persistent: one CTA per SM takes (block, head) items from an atomic counter, head-major and
+// heavy-first; the epilogue of an item overlaps the loads and first MMAs of the next one.
+template <bool DQ>
+struct BwdItem {
+  int blk, zh, z, h, t_lo, t_hi;
+  __device__ BwdItem(const BwdParams& p, int w) {
+    const int nblk = p.N / BLK;
+    zh = w / nblk;
+    const int pos = w % nblk;
+    // the dK/dV kernel's early K/V blocks and the dQ kernel's late Q blocks see the most steps
+    blk = DQ ? (nblk - 1 - pos) : pos;
+    z = zh / p.H;
+    h = zh % p.H;
+    t_lo = DQ ? 0 : (p.causal ? blk : 0);        // streamed block range [t_lo, t_hi)
+    t_hi = DQ ? (p.causal ? blk + 1 : nblk) : nblk;
+  }
+};
+
 template <int D, bool BF16, bool DQ>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
@@ -76,6 +96,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
                 const BwdParams p) {
   using Cfg = BwdCfg<D>;
   constexpr int TILE = Cfg::TILE, NST = Cfg::NST, STAGE = Cfg::STAGE;
+  constexpr int MMA_WARP = 8, TMA_WARP = 9;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
@@ -83,27 +104,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   uint8_t* sres = smem;                 // R1, R2
   uint8_t* sring = smem + 2 * TILE;     // stages
   uint64_t* bars = reinterpret_cast<uint64_t*>(sring + NST * STAGE);
-  uint64_t* r_full = bars;              // [1] resident tiles loaded
-  uint64_t* full = bars + 1;            // [NST]
+  uint64_t* r_full = bars;              // resident tiles of the item loaded
+  uint64_t* r_empty = bars + 1;         // every T MMA of the item has read them
+  uint64_t* full = bars + 2;            // [NST]
   uint64_t* empty = full + NST;         // [NST]
   uint64_t* t1_full = empty + NST;      // T1(t) in TMEM
   uint64_t* t2_full = t1_full + 1;      // T2(t) in TMEM
   uint64_t* p_full = t2_full + 1;       // P(t) written (dK/dV kernel)
   uint64_t* ds_full = p_full + 1;       // dS(t) written
-  uint64_t* acc_full = ds_full + 1;     // accumulators final
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = ds_full + 1;     // accumulators of the item final
+  uint64_t* sched_full = acc_full + 1;  // [2] an item id was published
+  uint64_t* sched_empty = sched_full + 2;  // [2] all 9 readers have taken it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + 2);
+  volatile int* sched_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nblk = p.N / BLK;
-  // heavy blocks first: the dK/dV kernel's early K/V blocks and the dQ kernel's late Q blocks see most steps
-  const int blk = DQ ? (nblk - 1 - (int)blockIdx.x) : (int)blockIdx.x;
-  const int zh = blockIdx.y, z = zh / p.H, h = zh % p.H;
-  // streamed range [t_lo, t_hi)
-  const int t_lo = DQ ? 0 : (p.causal ? blk : 0);
-  const int t_hi = DQ ? (p.causal ? blk + 1 : nblk) : nblk;
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
+    mbar_init(r_empty, 1);
     for (int s = 0; s < NST; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -113,13 +132,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     mbar_init(p_full, 256);
     mbar_init(ds_full, 256);
     mbar_init(acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sched_full[i], 1);
+      mbar_init(&sched_empty[i], 9);  // MMA thread + one lane of each compute warp
+    }
     fence_barrier_init();
     tma_prefetch_desc(&tm_r1);
     tma_prefetch_desc(&tm_r2);
     tma_prefetch_desc(&tm_u1);
     tma_prefetch_desc(&tm_u2);
   }
-  if (warp == 8) {
+  if (warp == MMA_WARP) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -129,28 +152,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const uint32_t tm_t1 = tmem_base, tm_t2 = tmem_base + 128, tm_a = tmem_base + 256, tm_b = tmem_base + 256 + D;
 
-  if (warp == 9) {
-    // ------------------------------------------------------------------ TMA producer
+  if (warp == TMA_WARP) {
+    // ------------------------------------------------------------------ scheduler + TMA producer
     if (lane == 0) {
-      mbar_expect_tx(r_full, 2 * TILE);
-      load_tile_b<D>(sres, &tm_r1, r_full, blk * BLK, h, z);
-      load_tile_b<D>(sres + TILE, &tm_r2, r_full, blk * BLK, h, z);
-      uint32_t s = 0, ph = 0;
-      for (int t = t_lo; t < t_hi; ++t) {
-        mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_BWD_LOAD_EMPTY);
-        uint8_t* st = sring + s * STAGE;
-        mbar_expect_tx(&full[s], 2 * TILE + (DQ ? 0 : 1024));
-        load_tile_b<D>(st, &tm_u1, &full[s], t * BLK, h, z);
-        load_tile_b<D>(st + TILE, &tm_u2, &full[s], t * BLK, h, z);
-        if (!DQ) {  // statistics of the streamed Q rows: M then delta, 128 floats each
-          bulk_load(st + 2 * TILE, p.m + (long long)zh * p.N + t * BLK, 512, &full[s]);
-          bulk_load(st + 2 * TILE + 512, p.delta + (long long)zh * p.N + t * BLK, 512, &full[s]);
+      uint32_t s = 0, ph = 0;  // ring position, runs on across items
+      for (uint32_t n = 0;; ++n) {
+        const int w = atomicAdd(p.sched_counter, 1);
+        const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
+        mbar_wait(&sched_empty[slot], sph ^ 1u, p.status, SITE_BWD_SCHED);
+        sched_item[slot] = w;
+        mbar_arrive(&sched_full[slot]);
+        if (w >= p.total_items) break;
+        const BwdItem<DQ> it(p, w);
+        mbar_wait(r_empty, (n & 1u) ^ 1u, p.status, SITE_BWD_KV);  // the previous item no longer reads R1, R2
+        mbar_expect_tx(r_full, 2 * TILE);
+        load_tile_b<D>(sres, &tm_r1, r_full, it.blk * BLK, it.h, it.z);
+        load_tile_b<D>(sres + TILE, &tm_r2, r_full, it.blk * BLK, it.h, it.z);
+        for (int t = it.t_lo; t < it.t_hi; ++t) {
+          mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_BWD_LOAD_EMPTY);
+          uint8_t* st = sring + s * STAGE;
+          mbar_expect_tx(&full[s], 2 * TILE + (DQ ? 0 : 1024));
+          load_tile_b<D>(st, &tm_u1, &full[s], t * BLK, it.h, it.z);
+          load_tile_b<D>(st + TILE, &tm_u2, &full[s], t * BLK, it.h, it.z);
+          if (!DQ) {  // statistics of the streamed Q rows: M then delta, 128 floats each
+            bulk_load(st + 2 * TILE, p.m + (long long)it.zh * p.N + t * BLK, 512, &full[s]);
+            bulk_load(st + 2 * TILE + 512, p.delta + (long long)it.zh * p.N + t * BLK, 512, &full[s]);
+          }
+          if (++s == NST) { s = 0; ph ^= 1u; }
         }
-        if (++s == NST) { s = 0; ph ^= 1u; }
       }
     }
     __syncwarp();
-  } else if (warp == 8) {
+  } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr int FMT = BF16 ? 1 : 0;
@@ -173,52 +206,59 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
           umma_ts_f16(tm_acc, tm_opnd + kk * 8, dun + kk * ((16 * 128) >> 4), IDESC_ACC, (accum | kk) != 0);
       };
 
-      mbar_wait(r_full, 0, p.status, SITE_BWD_KV);
-      const int steps = t_hi - t_lo;
-      uint32_t s = 0, ph = 0;
-      if (steps > 0) {
-        mbar_wait(&full[0], 0, p.status, SITE_BWD_LOAD_FULL);
-        issue_t(tm_t1, dr0, du0);
+      uint32_t s = 0, ph = 0;  // ring position
+      uint32_t cnt = 0;        // steps done so far, across items (parity of p_full / ds_full)
+      for (uint32_t n = 0;; ++n) {
+        const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
+        mbar_wait(&sched_full[slot], sph, p.status, SITE_BWD_SCHED);
+        const int w = sched_item[slot];
+        mbar_arrive(&sched_empty[slot]);
+        if (w >= p.total_items) break;
+        const BwdItem<DQ> item(p, w);
+        const int steps = item.t_hi - item.t_lo;  // >= 1
+
+        mbar_wait(r_full, n & 1u, p.status, SITE_BWD_KV);
+        mbar_wait(&full[s], ph, p.status, SITE_BWD_LOAD_FULL);
+        issue_t(tm_t1, dr0, du0 + s * (STAGE >> 4));
         tc_commit(t1_full);
-        issue_t(tm_t2, dr0 + (TILE >> 4), du0 + (TILE >> 4));
+        issue_t(tm_t2, dr0 + (TILE >> 4), du0 + s * (STAGE >> 4) + (TILE >> 4));
         tc_commit(t2_full);
-      }
-      for (int it = 0; it < steps; ++it) {
-        const uint32_t cs = s;
-        uint32_t ns = s + 1, nph = ph;
-        if (ns == NST) { ns = 0; nph ^= 1u; }
-        const uint64_t dun1 = dun0 + cs * (STAGE >> 4), dun2 = dun1 + (TILE >> 4);
-        const bool more = it + 1 < steps;
-        if (!DQ) {
-          mbar_wait(p_full, it & 1, p.status, SITE_BWD_P_FULL);
+        if (steps == 1) tc_commit(r_empty);
+        for (int it = 0; it < steps; ++it, ++cnt) {
+          const uint32_t cs = s;
+          uint32_t ns = s + 1, nph = ph;
+          if (ns == NST) { ns = 0; nph ^= 1u; }
+          const uint64_t dun1 = dun0 + cs * (STAGE >> 4), dun2 = dun1 + (TILE >> 4);
+          const bool more = it + 1 < steps;
+          if (!DQ) {
+            mbar_wait(p_full, cnt & 1u, p.status, SITE_BWD_P_FULL);
+            tc_fence_after();
+            issue_acc(tm_b, tm_t1, dun2, it > 0);  // dV += P^T dO
+          }
+          if (more) {
+            mbar_wait(&full[ns], nph, p.status, SITE_BWD_LOAD_FULL);
+            if (!DQ) {  // T1 of the next step may start as soon as P was consumed (in-order pipe)
+              issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
+              tc_commit(t1_full);
+            }
+          }
+          mbar_wait(ds_full, cnt & 1u, p.status, SITE_BWD_DS_FULL);
           tc_fence_after();
-          issue_acc(tm_b, tm_t1, dun2, it > 0);  // dV += P^T dO
-        }
-        if (more) {  // T1 of the next step may start as soon as P was consumed (in-order pipe)
-          mbar_wait(&full[ns], nph, p.status, SITE_BWD_LOAD_FULL);
-          if (DQ) {
-            // the dQ kernel has no consumer of P in TMEM: T1 is free once the compute warps have read it,
-            // which ds_full(it) implies; wait for it below before reusing T1
-          } else {
-            issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
-            tc_commit(t1_full);
+          issue_acc(tm_a, tm_t2, dun1, it > 0);  // dK += dS^T Q   /   dQ += dS K
+          tc_commit(&empty[cs]);
+          if (more) {
+            if (DQ) {  // no MMA consumes P here: T1 is free once the compute warps have read it (ds_full)
+              issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
+              tc_commit(t1_full);
+            }
+            issue_t(tm_t2, dr0 + (TILE >> 4), du0 + ns * (STAGE >> 4) + (TILE >> 4));
+            tc_commit(t2_full);
+            if (it + 2 == steps) tc_commit(r_empty);  // those were the item's last reads of R1, R2
           }
+          s = ns; ph = nph;
         }
-        mbar_wait(ds_full, it & 1, p.status, SITE_BWD_DS_FULL);
-        tc_fence_after();
-        issue_acc(tm_a, tm_t2, dun1, it > 0);  // dK += dS^T Q   /   dQ += dS K
-        tc_commit(&empty[cs]);
-        if (more) {
-          if (DQ) {
-            issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
-            tc_commit(t1_full);
-          }
-          issue_t(tm_t2, dr0 + (TILE >> 4), du0 + ns * (STAGE >> 4) + (TILE >> 4));
-          tc_commit(t2_full);
-        }
-        s = ns; ph = nph;
+        tc_commit(acc_full);
       }
-      tc_commit(acc_full);
     }
     __syncwarp();
   } else {
@@ -231,113 +271,129 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     const int half = warp >> 2;
     constexpr int HC = BLK / 2, HD = D / 2;
     const int r = quarter * 32 + lane;       // row inside the block
-    const int grow = blk * BLK + r;          // kv index (dK/dV kernel) or q index (dQ kernel)
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const float scale = p.scale_log2;
-    float m_row = 0.f, d_row = 0.f;
-    if (DQ) {
-      m_row = p.m[(long long)zh * p.N + grow];
-      d_row = p.delta[(long long)zh * p.N + grow];
-    }
-    const int steps = t_hi - t_lo;
-    uint32_t s = 0;
-    for (int it = 0; it < steps; ++it) {
-      const int t = t_lo + it;
-      const float* sm = reinterpret_cast<const float*>(sring + s * STAGE + 2 * TILE) + half * HC;  // column M
-      const float* sd = sm + 128;                                                                  // column delta
-      // the diagonal block is the only one that needs the causal mask
-      const bool diag = p.causal && (t == blk);
-      mbar_wait(t1_full, it & 1, p.status, SITE_BWD_S_FULL);
-      tc_fence_after();
-      uint32_t pr[HC];  // P as fp32 bits
-#pragma unroll
-      for (int c = 0; c < HC; c += 32) tmem_ld32(tm_t1 + lane_addr + half * HC + c, pr + c);
-      tmem_ld_wait();
-      if (!DQ) asm volatile("bar.sync 1, 256;" ::: "memory");  // both halves hold their T1 columns in registers
-#pragma unroll
-      for (int c = 0; c < HC; ++c) {
-        const float mm = DQ ? m_row : sm[c];
-        float pv = ex2(fmaf(__uint_as_float(pr[c]), scale, -mm));
-        // dK/dV kernel: row = kv, column = q, keep q >= kv.   dQ kernel: row = q, column = kv, keep kv <= q.
-        const int cc = half * HC + c;
-        if (diag && (DQ ? (cc > r) : (cc < r))) pv = 0.f;
-        pr[c] = __float_as_uint(pv);
+    uint32_t s = 0;    // ring position
+    uint32_t cnt = 0;  // steps done so far, across items (parity of t1_full / t2_full)
+
+    for (uint32_t n = 0;; ++n) {
+      const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
+      int w = 0;
+      if (lane == 0) {
+        mbar_wait(&sched_full[slot], sph, p.status, SITE_BWD_SCHED);
+        w = sched_item[slot];
+        mbar_arrive(&sched_empty[slot]);
       }
-      if (!DQ) {
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (w >= p.total_items) break;
+      const BwdItem<DQ> item(p, w);
+      const int blk = item.blk, zh = item.zh;
+      const int grow = blk * BLK + r;  // kv index (dK/dV kernel) or q index (dQ kernel)
+      float m_row = 0.f, d_row = 0.f;
+      if (DQ) {
+        m_row = p.m[(long long)zh * p.N + grow];
+        d_row = p.delta[(long long)zh * p.N + grow];
+      }
+      const int steps = item.t_hi - item.t_lo;
+      for (int it = 0; it < steps; ++it, ++cnt) {
+        const int t = item.t_lo + it;
+        const float* sm = reinterpret_cast<const float*>(sring + s * STAGE + 2 * TILE) + half * HC;  // column M
+        const float* sd = sm + 128;                                                                  // column delta
+        // the diagonal block is the only one that needs the causal mask
+        const bool diag = p.causal && (t == blk);
+        mbar_wait(t1_full, cnt & 1u, p.status, SITE_BWD_S_FULL);
+        tc_fence_after();
+        uint32_t pr[HC];  // P as fp32 bits
+#pragma unroll
+        for (int c = 0; c < HC; c += 32) tmem_ld32(tm_t1 + lane_addr + half * HC + c, pr + c);
+        tmem_ld_wait();
+        if (!DQ) asm volatile("bar.sync 1, 256;" ::: "memory");  // both halves hold their T1 columns in registers
+#pragma unroll
+        for (int c = 0; c < HC; ++c) {
+          const float mm = DQ ? m_row : sm[c];
+          float pv = ex2(fmaf(__uint_as_float(pr[c]), scale, -mm));
+          // dK/dV kernel: row = kv, column = q, keep q >= kv.   dQ kernel: row = q, column = kv, keep kv <= q.
+          const int cc = half * HC + c;
+          if (diag && (DQ ? (cc > r) : (cc < r))) pv = 0.f;
+          pr[c] = __float_as_uint(pv);
+        }
+        if (!DQ) {
+#pragma unroll
+          for (int c = 0; c < HC; c += 32) {
+            uint32_t wv[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) wv[k] = pack2<BF16>(__uint_as_float(pr[c + 2 * k]), __uint_as_float(pr[c + 2 * k + 1]));
+            tmem_st16(tm_t1 + lane_addr + ((half * HC + c) >> 1), wv);
+          }
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(p_full);
+        }
+        mbar_wait(t2_full, cnt & 1u, p.status, SITE_BWD_DP_FULL);
+        tc_fence_after();
+        uint32_t dsw[HC / 2];  // dS packed to 16 bit
 #pragma unroll
         for (int c = 0; c < HC; c += 32) {
-          uint32_t w[16];
-#pragma unroll
-          for (int k = 0; k < 16; ++k) w[k] = pack2<BF16>(__uint_as_float(pr[c + 2 * k]), __uint_as_float(pr[c + 2 * k + 1]));
-          tmem_st16(tm_t1 + lane_addr + ((half * HC + c) >> 1), w);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(p_full);
-      }
-      mbar_wait(t2_full, it & 1, p.status, SITE_BWD_DP_FULL);
-      tc_fence_after();
-      uint32_t dsw[HC / 2];  // dS packed to 16 bit
-#pragma unroll
-      for (int c = 0; c < HC; c += 32) {
-        uint32_t dp[32];
-        tmem_ld32(tm_t2 + lane_addr + half * HC + c, dp);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          const float d0 = DQ ? d_row : sd[c + 2 * k];
-          const float d1 = DQ ? d_row : sd[c + 2 * k + 1];
-          const float ds0 = __uint_as_float(pr[c + 2 * k]) * (__uint_as_float(dp[2 * k]) - d0);
-          const float ds1 = __uint_as_float(pr[c + 2 * k + 1]) * (__uint_as_float(dp[2 * k + 1]) - d1);
-          dsw[(c >> 1) + k] = pack2<BF16>(ds0, ds1);
-        }
-      }
-      asm volatile("bar.sync 2, 256;" ::: "memory");  // both halves have read all of T2
-#pragma unroll
-      for (int c = 0; c < HC / 2; c += 16) tmem_st16(tm_t2 + lane_addr + half * (HC / 2) + c, dsw + c);
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(ds_full);
-      if (++s == NST) s = 0;
-    }
-
-    // epilogue: each thread stores its half of the accumulator columns
-    mbar_wait(acc_full, 0, p.status, SITE_BWD_ACC_FULL);
-    tc_fence_after();
-    auto store_rows = [&](uint32_t tm_acc, void* out, long long sz, long long sh, long long sn, float mul) {
-      uint16_t* orow = reinterpret_cast<uint16_t*>(out) + (long long)z * sz + (long long)h * sh + (long long)grow * sn +
-                       half * HD;
-      const bool vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((sn & 7) == 0) && ((sh & 7) == 0) && ((sz & 7) == 0);
-#pragma unroll 1
-      for (int c = 0; c < HD; c += 32) {
-        uint32_t o[32];
-        tmem_ld32(tm_acc + lane_addr + half * HD + c, o);
-        tmem_ld_wait();
-        uint32_t w[16];
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-          w[k] = (steps > 0) ? pack2<BF16>(__uint_as_float(o[2 * k]) * mul, __uint_as_float(o[2 * k + 1]) * mul) : 0u;
-        if (vec_ok) {
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
-        } else {
+          uint32_t dp[32];
+          tmem_ld32(tm_t2 + lane_addr + half * HC + c, dp);
+          tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
-            orow[c + 2 * k] = (uint16_t)(w[k] & 0xFFFFu);
-            orow[c + 2 * k + 1] = (uint16_t)(w[k] >> 16);
+            const float d0 = DQ ? d_row : sd[c + 2 * k];
+            const float d1 = DQ ? d_row : sd[c + 2 * k + 1];
+            const float ds0 = __uint_as_float(pr[c + 2 * k]) * (__uint_as_float(dp[2 * k]) - d0);
+            const float ds1 = __uint_as_float(pr[c + 2 * k + 1]) * (__uint_as_float(dp[2 * k + 1]) - d1);
+            dsw[(c >> 1) + k] = pack2<BF16>(ds0, ds1);
           }
         }
+        asm volatile("bar.sync 2, 256;" ::: "memory");  // both halves have read all of T2
+#pragma unroll
+        for (int c = 0; c < HC / 2; c += 16) tmem_st16(tm_t2 + lane_addr + half * (HC / 2) + c, dsw + c);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(ds_full);
+        if (++s == NST) s = 0;
       }
-    };
-    store_rows(tm_a, p.out_a, p.oa_sz, p.oa_sh, p.oa_sn, p.sm_scale);  // dK or dQ carry sm_scale
-    if (!DQ) store_rows(tm_b, p.out_b, p.ob_sz, p.ob_sh, p.ob_sn, 1.0f);
+
+      // epilogue: each thread stores its half of the accumulator columns.  It overlaps the next
+      // item's loads and first T MMAs; the next item's first accumulate MMA needs this warp's next
+      // P / dS, i.e. comes after these reads in program order.
+      mbar_wait(acc_full, n & 1u, p.status, SITE_BWD_ACC_FULL);
+      tc_fence_after();
+      auto store_rows = [&](uint32_t tm_acc, void* out, long long sz, long long sh, long long sn, float mul) {
+        uint16_t* orow = reinterpret_cast<uint16_t*>(out) + (long long)item.z * sz + (long long)item.h * sh +
+                         (long long)grow * sn + half * HD;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((sn & 7) == 0) && ((sh & 7) == 0) && ((sz & 7) == 0);
+#pragma unroll 1
+        for (int c = 0; c < HD; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tm_acc + lane_addr + half * HD + c, o);
+          tmem_ld_wait();
+          uint32_t wv[16];
+#pragma unroll
+          for (int k = 0; k < 16; ++k) wv[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * mul, __uint_as_float(o[2 * k + 1]) * mul);
+          if (vec_ok) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(wv[4 * k], wv[4 * k + 1], wv[4 * k + 2], wv[4 * k + 3]);
+          } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              orow[c + 2 * k] = (uint16_t)(wv[k] & 0xFFFFu);
+              orow[c + 2 * k + 1] = (uint16_t)(wv[k] >> 16);
+            }
+          }
+        }
+      };
+      store_rows(tm_a, p.out_a, p.oa_sz, p.oa_sh, p.oa_sn, p.sm_scale);  // dK or dQ carry sm_scale
+      if (!DQ) store_rows(tm_b, p.out_b, p.ob_sz, p.ob_sh, p.ob_sn, 1.0f);
+    }
   }
 
   if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == MMA_WARP) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -394,8 +450,12 @@ int launch_bwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& r1, con
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(attn bwd): %s", cudaGetErrorString(e));
     attr_done[ctx->device] = true;
   }
-  dim3 grid(p.N / BLK, p.Z * p.H, 1);
-  attn_bwd_kernel<D, BF16, DQ><<<grid, BWD_THREADS, smem, stream>>>(r1, r2, u1, u2, p);
+  BwdParams q = p;
+  q.total_items = (p.N / BLK) * p.Z * p.H;
+  q.sched_counter = next_sched_counter(ctx, stream);
+  if (!q.sched_counter) return B200_ERR_CUDA;
+  const int grid = q.total_items < ctx->sm_count ? q.total_items : ctx->sm_count;
+  attn_bwd_kernel<D, BF16, DQ><<<grid, BWD_THREADS, smem, stream>>>(r1, r2, u1, u2, q);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd launch: %s", cudaGetErrorString(e));
   return B200_OK;

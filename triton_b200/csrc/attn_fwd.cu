@@ -28,15 +28,11 @@
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_i = first 64 columns of S_i.
 #include <cmath>
 #include <cstdlib>
-#include <mutex>
 
 #include "common.cuh"
 #include "host.h"
 
 namespace tb {
-
-// work counters of the persistent forward kernel (see launch_attn_fwd)
-__device__ int g_fwd_sched[64];
 
 namespace {
 
@@ -459,23 +455,8 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
   p.num_qb = (N + 255) / 256;
   p.total_items = p.num_qb * Z * H;
   p.status = ctx->status;
-  // Work counter: one of a ring of 64 device words, so that launches in flight on different streams
-  // do not share one (more than 64 forward launches in flight at once would).
-  {
-    static std::mutex mu;
-    static int* base[64] = {};
-    static unsigned next[64] = {};
-    std::lock_guard<std::mutex> lk(mu);
-    if (!base[ctx->device]) {
-      void* ptr = nullptr;
-      cudaError_t e = cudaGetSymbolAddress(&ptr, g_fwd_sched);
-      if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaGetSymbolAddress(scheduler): %s", cudaGetErrorString(e));
-      base[ctx->device] = static_cast<int*>(ptr);
-    }
-    p.sched_counter = base[ctx->device] + (next[ctx->device]++ % 64);
-  }
-  cudaError_t me = cudaMemsetAsync(p.sched_counter, 0, sizeof(int), stream);
-  if (me != cudaSuccess) return fail(B200_ERR_CUDA, "scheduler reset: %s", cudaGetErrorString(me));
+  p.sched_counter = next_sched_counter(ctx, stream);
+  if (!p.sched_counter) return B200_ERR_CUDA;
   const bool bf16 = dtype == B200_BF16;
   if (D == 128) return bf16 ? launch_fwd_t<128, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<128, false>(ctx, stream, tq, tk, tv, p);
   if (D == 64) return bf16 ? launch_fwd_t<64, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<64, false>(ctx, stream, tq, tk, tv, p);

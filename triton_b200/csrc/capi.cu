@@ -11,6 +11,10 @@ namespace tb {
 
 // Status word read by b200_status(); kernels receive its device address as a parameter.
 __device__ unsigned g_status_word[4];
+// Work counters of the persistent attention kernels: each launch takes the next word of this ring
+// and zeroes it on its stream, so launches in flight on different streams do not share one (more
+// than 256 attention launches in flight at once would).
+__device__ int g_sched_ring[256];
 
 namespace {
 thread_local char g_err[512] = "";
@@ -82,6 +86,31 @@ DeviceCtx* current_ctx() {
   c.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
   c.device = dev;
   return &c;
+}
+
+int* next_sched_counter(DeviceCtx* ctx, cudaStream_t stream) {
+  static int* base[64] = {};
+  static unsigned next[64] = {};
+  int* slot = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!base[ctx->device]) {
+      void* ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_sched_ring);
+      if (e != cudaSuccess) {
+        fail(B200_ERR_CUDA, "cudaGetSymbolAddress(scheduler ring): %s", cudaGetErrorString(e));
+        return nullptr;
+      }
+      base[ctx->device] = static_cast<int*>(ptr);
+    }
+    slot = base[ctx->device] + (next[ctx->device]++ % 256);
+  }
+  cudaError_t e = cudaMemsetAsync(slot, 0, sizeof(int), stream);
+  if (e != cudaSuccess) {
+    fail(B200_ERR_CUDA, "scheduler counter reset: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  return slot;
 }
 
 bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,

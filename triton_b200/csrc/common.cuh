@@ -22,7 +22,7 @@ enum WaitSite : unsigned {
   SITE_FWD_Q = 10, SITE_FWD_KV_EMPTY = 11, SITE_FWD_KV_FULL = 12, SITE_FWD_S_FULL = 13, SITE_FWD_P_FULL = 14,
   SITE_FWD_O_FULL = 15, SITE_FWD_S_EMPTY = 16, SITE_FWD_O_READY = 17, SITE_FWD_SCHED = 18,
   SITE_BWD_LOAD_EMPTY = 20, SITE_BWD_LOAD_FULL = 21, SITE_BWD_S_FULL = 22, SITE_BWD_P_FULL = 23,
-  SITE_BWD_DP_FULL = 24, SITE_BWD_DS_FULL = 25, SITE_BWD_ACC_FULL = 26, SITE_BWD_FREE = 27, SITE_BWD_KV = 28,
+  SITE_BWD_DP_FULL = 24, SITE_BWD_DS_FULL = 25, SITE_BWD_ACC_FULL = 26, SITE_BWD_FREE = 27, SITE_BWD_KV = 28, SITE_BWD_SCHED = 29,
 };
 
 __device__ __forceinline__ unsigned long long gtimer_ns() {

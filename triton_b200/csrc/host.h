@@ -20,6 +20,9 @@ struct DeviceCtx {
 // string) when no usable sm_100 device is current.
 DeviceCtx* current_ctx();
 
+// A zeroed work counter for one launch of a persistent kernel on `stream` (nullptr + error string on failure).
+int* next_sched_counter(DeviceCtx* ctx, cudaStream_t stream);
+
 // Record an error message for b200_last_error() and return `code`.
 int fail(int code, const char* fmt, ...);
 
