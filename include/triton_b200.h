@@ -57,8 +57,9 @@ B200_API int b200_status(unsigned* value, int clear);
  * B200_E4M3.  scale_a / scale_b are optional DEVICE pointers to one fp32 each: the epilogue
  * multiplies the accumulator by (*scale_a) * (*scale_b) before the activation and the single
  * rounding to out_dtype (per-tensor fp8 scaling; pass NULL for 1.0).
- * A and B may each be row- or column-major (one of the two strides must be 1); C must have
- * stride_cn == 1.  Base addresses and the non-unit strides must be multiples of 16 bytes.
+ * A and B may have any strides; C must have stride_cn == 1.  The tensor-core path needs one unit
+ * stride per operand, 16-byte aligned base addresses and non-unit strides that are multiples of
+ * 16 bytes (what TMA can address); other layouts run on a plain CUDA-core kernel, correct but slow.
  * in_dtype: F16, BF16 or E4M3 (both operands); out_dtype: F16, BF16 or F32. */
 B200_API int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                 int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,

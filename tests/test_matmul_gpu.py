@@ -81,12 +81,39 @@ def test_empty_and_degenerate():
     b = torch.ones(0, 8, dtype=torch.float16, device=DEV)
     c = triton_b200.matmul(a, b)
     assert c.shape == (5, 8) and float(c.abs().sum()) == 0.0  # empty sum
-    # a stride the TMA path cannot address is an error, not a silent fallback
-    a = torch.ones(8, 12, dtype=torch.float16, device=DEV)
-    b = torch.ones(12, 6, dtype=torch.float16, device=DEV)
-    with pytest.raises(RuntimeError, match="16 bytes"):
-        triton_b200.matmul(a, b)
     status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float8_e4m3fn])
+@pytest.mark.parametrize("shape", [(8, 6, 12), (129, 257, 70), (300, 77, 513)])
+def test_layouts_tma_cannot_address(dtype, shape):
+    """Row strides that are not multiples of 16 bytes, and operands with no unit stride at all, are legal
+    for the reference kernel (it takes arbitrary strides); they run on the plain CUDA-core kernel."""
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(K, N, generator=g).to(dtype)
+    af, bf = a.float().numpy(), b.float().numpy()
+    out = "fp16" if dtype == torch.float16 else "bf16"
+    want = R.matmul(af, bf, out=out)
+    got = triton_b200.matmul(a.to(DEV), b.to(DEV))
+    np.testing.assert_allclose(f32(got), want, rtol=2e-2, atol=2e-2)
+    # B with no unit stride: every second column of a wider matrix
+    wide = torch.zeros(K, 2 * N, dtype=dtype, device=DEV)
+    wide[:, ::2] = b.to(DEV)
+    got2 = triton_b200.matmul(a.to(DEV), wide[:, ::2])
+    assert torch.equal(got2, got)
+    status_ok()
+
+
+def test_plain_kernel_matches_tensor_core_kernel(monkeypatch):
+    g = torch.Generator().manual_seed(99)
+    a = torch.randn(320, 256, generator=g).half().to(DEV)
+    b = torch.randn(256, 192, generator=g).half().to(DEV)
+    fast = triton_b200.matmul(a, b, activation="leaky_relu")
+    monkeypatch.setenv("B200_GEMM_PLAIN", "1")
+    plain = triton_b200.matmul(a, b, activation="leaky_relu")
+    np.testing.assert_allclose(f32(plain), f32(fast), rtol=2e-3, atol=2e-3)
 
 
 @pytest.mark.parametrize("name", list(cases.FP8_CASES))

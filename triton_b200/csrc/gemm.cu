@@ -403,6 +403,69 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   }
 }
 
+// ------------------------------------------------------------------------ layouts TMA cannot address
+// A base address that is not 16-byte aligned or a row stride that is not a multiple of 16 bytes
+// (N = 257 fp16 columns, say) cannot be described by a tensor map.  The reference accepts any
+// strides, so such calls take this plain CUDA-core kernel: same arithmetic (fp32 accumulation in
+// K order per 16-wide slab, scale, activation, one rounding), no tensor cores, no speed claim.
+__device__ __forceinline__ float load_elem(const void* base, long long idx, int dtype) {
+  if (dtype == B200_F16) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+  if (dtype == B200_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+  // e4m3: sign, 4 exponent bits (bias 7), 3 mantissa bits; 0x7f / 0xff are NaN
+  const uint32_t b = reinterpret_cast<const uint8_t*>(base)[idx];
+  const uint32_t e = (b >> 3) & 0xFu, m = b & 7u;
+  float v;
+  if (e == 0) v = (float)m * 0.001953125f;                       // m / 8 * 2^-6
+  else if (e == 15 && m == 7) v = __int_as_float(0x7fc00000);
+  else v = __int_as_float(((e + 120u) << 23) | (m << 20));        // (1 + m/8) * 2^(e-7)
+  return (b & 0x80u) ? -v : v;
+}
+
+__global__ void __launch_bounds__(256)
+gemm_plain_kernel(const void* a, const void* b, GemmParams p, long long sam, long long sak, long long sbk,
+                  long long sbn, int in_dtype) {
+  __shared__ float sa[16][64 + 1], sb[16][64 + 1];
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < p.K; k0 += 16) {
+    for (int i = threadIdx.x; i < 16 * 64; i += 256) {
+      const int kk = i & 15, mn = i >> 4;
+      const int gm = m0 + mn, gn = n0 + mn, gk = k0 + kk;
+      sa[kk][mn] = (gm < p.M && gk < p.K) ? load_elem(a, gm * sam + gk * sak, in_dtype) : 0.f;
+      sb[kk][mn] = (gn < p.N && gk < p.K) ? load_elem(b, gk * sbk + gn * sbn, in_dtype) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < 16; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { av[i] = sa[kk][ty * 4 + i]; bv[i] = sb[kk][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  float scale = 1.f;
+  if (p.scale_a) scale *= __ldg(p.scale_a);
+  if (p.scale_b) scale *= __ldg(p.scale_b);
+  for (int i = 0; i < 4; ++i) {
+    const int gm = m0 + ty * 4 + i;
+    if (gm >= p.M) continue;
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tx * 4 + j;
+      if (gn >= p.N) continue;
+      const float v = apply_act(acc[i][j] * scale, p.activation);
+      const long long o = (long long)gm * p.ldc + gn;
+      if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
+      else if (p.out_dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
+      else reinterpret_cast<__half*>(p.c)[o] = __float2half_rn(v);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------- host
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
@@ -490,8 +553,24 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   const int bk_elems = KBYTES / elt;
   const bool a_mn = !(sak == 1 || K == 1);  // K contiguous preferred
   const bool b_mn = !(sbk == 1 || K == 1);
-  if (a_mn && sam != 1 && M != 1) return fail(B200_ERR_UNSUPPORTED, "A must have a unit stride in M or K");
-  if (b_mn && sbn != 1 && N != 1) return fail(B200_ERR_UNSUPPORTED, "B must have a unit stride in K or N");
+
+  // Can TMA address A and B?  (C is written with plain stores and has no such limit.)
+  auto tma_ok = [&](const void* base, int64_t row_stride) {
+    return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ((row_stride * elt) & 15) == 0;
+  };
+  const bool a_ok = tma_ok(a, a_mn ? sak : sam) || (a_mn ? K : M) == 1;
+  const bool b_ok = tma_ok(b, b_mn ? sbk : sbn) || (b_mn ? K : N) == 1;
+  if (!a_ok || !b_ok || (a_mn && sam != 1) || (b_mn && sbn != 1) || env_int("B200_GEMM_PLAIN", 0)) {
+    GemmParams q{};
+    q.c = c; q.M = M; q.N = N; q.K = K; q.ldc = scm;
+    q.out_dtype = out_dtype; q.activation = activation;
+    q.scale_a = scale_a; q.scale_b = scale_b;
+    dim3 grid((N + 63) / 64, (M + 63) / 64, 1);
+    gemm_plain_kernel<<<grid, 256, 0, stream>>>(a, b, q, sam, sak, sbk, sbn, in_dtype);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "plain gemm launch: %s", cudaGetErrorString(e));
+    return B200_OK;
+  }
 
   // Tile shape.  B200_GEMM_TILE forces one: 128064, 128128, 128256, 256256, or 2256 for the CTA pair.
   auto tiles = [&](int bm_, int bn_) { return (long long)((M + bm_ - 1) / bm_) * ((N + bn_ - 1) / bn_); };
