@@ -62,15 +62,28 @@ def test_matmul_shapes_layouts(dtype, shape, b_layout):
     np.testing.assert_allclose(f32(got), want, rtol=tol, atol=tol)
 
 
-@pytest.mark.parametrize("tile", ["128064", "128128", "128256", "256256", "2256"])
+@pytest.mark.parametrize("tile", ["128064", "128128", "128256", "256256", "2256", "2512"])
 def test_every_tile_shape(monkeypatch, tile):
     monkeypatch.setenv("B200_GEMM_TILE", tile)
     g = torch.Generator().manual_seed(11)
     a = torch.randn(600, 328, generator=g).half()
     b = torch.randn(328, 712, generator=g).half()
+    want = R.matmul(f32(a), f32(b))
     got = triton_b200.matmul(a.to(DEV), b.to(DEV))
     status_ok()
-    np.testing.assert_allclose(f32(got), R.matmul(f32(a), f32(b)), rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(f32(got), want, rtol=1e-2, atol=1e-2)
+    # the direct-store epilogue (used for fp32 outputs and for a C that TMA cannot address) gives the same bits
+    monkeypatch.setenv("B200_GEMM_DIRECT_STORE", "1")
+    direct = triton_b200.matmul(a.to(DEV), b.to(DEV))
+    assert torch.equal(direct, got)
+    # C as a column slice of a wider matrix (row stride 1424 bytes, still TMA-addressable) and fp32 output
+    monkeypatch.delenv("B200_GEMM_DIRECT_STORE")
+    wide = torch.zeros(600, 1424, dtype=torch.float16, device=DEV)
+    triton_b200.matmul(a.to(DEV), b.to(DEV), out=wide[:, 8:720], out_dtype=torch.float16)
+    assert torch.equal(wide[:, 8:720], got) and float(wide[:, :8].abs().sum()) == 0 and float(wide[:, 720:].abs().sum()) == 0
+    acc = triton_b200.matmul(a.to(DEV), b.to(DEV), out_dtype=torch.float32)
+    np.testing.assert_allclose(f32(acc), f32(a) @ f32(b), rtol=1e-3, atol=1e-3)
+    status_ok()
 
 
 def test_empty_and_degenerate():

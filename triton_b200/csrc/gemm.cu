@@ -11,11 +11,11 @@
 //   128 x {64,128,256}   one CTA, two TMEM accumulators: the epilogue of tile i overlaps the main
 //                        loop of tile i+1
 //   256 x 256            one CTA, two 128-row MMAs per K step sharing the B stage, one accumulator
-//                        set; a third less shared-memory fill traffic per flop
-//   256 x 256 (pair)     two CTAs of a cluster (cta_group::2): each stages 128 rows of A and 128
-//                        columns of B, the leader issues 256 x 256 MMAs that read both CTAs'
-//                        shared memory; same fill traffic per flop as above, a deeper ring and
-//                        two accumulators
+//                        set; a third less shared-memory fill traffic per flop (the default for
+//                        large problems)
+//   256 x 256 / 256 x 512 (pair)  two CTAs of a cluster (cta_group::2): each stages 128 rows of A
+//                        and 128 columns of B per 256-column MMA, the leader issues 256 x 256 MMAs
+//                        that read both CTAs' shared memory; selectable with B200_GEMM_TILE
 // What bounds the big shapes is the L2 -> shared-memory fill (bytes per flop), not the tensor
 // pipe, hence the preference for 256-row tiles when the problem has enough of them.
 //
@@ -60,6 +60,7 @@ struct GemmParams {
   unsigned* status;
   int num_pid_m, num_pid_n, num_tiles, num_k, bk_elems;
   int group_m;  // tile rows per rasterisation group (the reference's GROUP_SIZE_M)
+  int c_tma;    // C is written through shared-memory staging + TMA stores (16-bit outputs TMA can address)
   uint32_t idesc;
   OperandGeom ga, gb;
 };
@@ -114,6 +115,63 @@ __device__ __forceinline__ void store_chunk32(const GemmParams& p, int row, int 
   }
 }
 
+
+constexpr int STG_BYTES = 32 * 128;  // staging of one epilogue warp: 32 rows x 64 columns of 16 bit
+constexpr int kMaxSmem = 232448;     // dynamic shared memory one CTA can opt in to on sm_100
+// epilogue staging buffers of the pair kernel: only where they fit beside the stages (the 7-stage
+// 256 x 256 configuration keeps direct stores; its two accumulators hide the epilogue anyway)
+constexpr int pair_staging_warps(int stages, int nb) {
+  return (stages * (128 + 128 * nb) * 128 + 4 * STG_BYTES + 2048 <= kMaxSmem) ? 4 : 0;
+}
+
+// One epilogue warp drains `ncols` accumulator columns of its 32 TMEM lanes (rows row0 .. row0+31 of C,
+// columns col0 ..).  Fast path: 64 columns at a time are converted, written to the warp's swizzled
+// staging buffer and stored by TMA (full 128-byte lines, clipped at the matrix edge by the hardware);
+// a warp-wide store of one row each would touch 32 separate lines per instruction and made the
+// epilogue cost 9 % of a 256 x 256 tile.  Other outputs (fp32, or a C that TMA cannot address) take
+// direct stores.
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tma_c, uint8_t* stg,
+                                                  uint32_t taddr, int ncols, int row0, int col0, int lane,
+                                                  float scale, bool vec_ok) {
+  if (p.c_tma) {
+#pragma unroll 1
+    for (int c0 = 0; c0 < ncols; c0 += 64) {
+      uint32_t r[64];
+      tmem_ld32(taddr + c0, r);
+      tmem_ld32(taddr + c0 + 32, r + 32);
+      tmem_ld_wait();
+      if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging buffer
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float v0 = apply_act(__uint_as_float(r[8 * c + 2 * j]) * scale, p.activation);
+          const float v1 = apply_act(__uint_as_float(r[8 * c + 2 * j + 1]) * scale, p.activation);
+          w[j] = (p.out_dtype == B200_BF16) ? pack2<true>(v0, v1) : pack2<false>(v0, v1);
+        }
+        *reinterpret_cast<uint4*>(stg + sw128_offset(lane, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && row0 < p.M && col0 + c0 < p.N) {
+        tma_store_2d(tma_c, stg, col0 + c0, row0);
+        tma_store_commit();
+      }
+    }
+  } else {
+    const int row = row0 + lane;
+#pragma unroll 1
+    for (int c0 = 0; c0 < ncols; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(taddr + c0, r);
+      tmem_ld_wait();
+      if (row < p.M) store_chunk32(p, row, col0 + c0, r, scale, vec_ok);
+    }
+  }
+}
+
 // TMA boxes of one operand stage (2-D maps: K-major {k, row}; MN-major {row, k} in 128-byte column blocks)
 template <bool PAIR>
 __device__ __forceinline__ void load_operand(const OperandGeom& g, const CUtensorMap* map, uint8_t* dst, uint64_t* bar,
@@ -133,7 +191,7 @@ __device__ __forceinline__ void load_operand(const OperandGeom& g, const CUtenso
 template <int BM, int BN, int STAGES>
 __global__ void __launch_bounds__(64 + BM, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   constexpr uint32_t A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
   constexpr int MH = BM / 128;                  // 128-row MMAs per K step
@@ -142,7 +200,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;  // one 4 KiB buffer per epilogue warp
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + (BM / 32) * STG_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -159,6 +218,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       mbar_init(&tmem_full[i], 1);
       mbar_init(&tmem_empty[i], BM);
     }
+    if (p.c_tma) tma_prefetch_desc(&tma_c);
     fence_barrier_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
@@ -244,18 +304,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const uint32_t acc = ti % NACC;
       mbar_wait(&tmem_full[acc], (ti / NACC) & 1u, p.status, SITE_GEMM_TMEM_FULL);
       tc_fence_after();
-      const int row = pid_m * BM + half * 128 + quarter * 32 + lane;
-      const int n0 = pid_n * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN + c0, r);
-        tmem_ld_wait();
-        if (row < p.M) store_chunk32(p, row, n0 + c0, r, scale, vec_ok);
-      }
+      drain_accumulator(p, &tma_c, staging + (warp - 2) * STG_BYTES,
+                        tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
+                        pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
     }
+    if (p.c_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
   }
 
   // teardown: after a recorded failure give copies in flight time to land before the CTA exits
@@ -272,18 +327,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 // Barriers: both producers credit the LEADER's full[s] (the peer through the leader's cluster
 // address); the leader's tcgen05.commit is multicast to both CTAs' empty[s] / tmem_full[acc];
 // the peer's epilogue warps arrive remotely on the leader's tmem_empty[acc].
-template <int STAGES>
+template <int STAGES, int NB>
 __global__ void __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                 const GemmParams p) {
-  constexpr int BN = 256, HALF_N = 128;
-  constexpr uint32_t A_BYTES = 128 * KBYTES, B_BYTES = HALF_N * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+                 const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
+  // The pair's tile is 256 x (256 * NB).  Per K block each CTA stages its 128 rows of A and, for
+  // each of the NB 256-column MMAs, its 128 columns of B.  NB = 2 needs a quarter less fill
+  // traffic per flop and amortises the per-stage bookkeeping over eight MMAs, but its
+  // accumulators fill TMEM, so the epilogue is not overlapped with the next tile.
+  constexpr int BN = 256 * NB, HALF_N = 128;
+  constexpr uint32_t A_BYTES = 128 * KBYTES, B_BYTES = NB * HALF_N * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t NACC = (NB == 1) ? 2 : 1;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;  // one 4 KiB buffer per epilogue warp
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + pair_staging_warps(STAGES, NB) * STG_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -305,6 +366,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     fence_barrier_init();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
+    if (p.c_tma) tma_prefetch_desc(&tma_c);
   }
   if (warp == 1) {
     tmem_alloc_pair(tmem_slot, TMEM_COLS);
@@ -327,7 +389,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           load_operand<true>(p.ga, &tma_a, a_dst, &full[s], kb * p.bk_elems, m0);
-          load_operand<true>(p.gb, &tma_b, a_dst + A_BYTES, &full[s], kb * p.bk_elems, n0);
+#pragma unroll
+          for (int j = 0; j < NB; ++j)  // this CTA's 128 columns of the j-th 256-column MMA
+            load_operand<true>(p.gb, &tma_b, a_dst + A_BYTES + j * (HALF_N * KBYTES), &full[s], kb * p.bk_elems,
+                               n0 + j * 256);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
       }
@@ -342,20 +407,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const bool fp8 = p.fp8 != 0;
       uint32_t s = 0, ph = 0, ti = 0;
       for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++ti) {
-        const uint32_t acc = ti & 1u;
-        mbar_wait(&tmem_empty[acc], ((ti >> 1) & 1u) ^ 1u, p.status, SITE_GEMM_TMEM_EMPTY);
+        const uint32_t acc = ti % NACC;
+        mbar_wait(&tmem_empty[acc], ((ti / NACC) & 1u) ^ 1u, p.status, SITE_GEMM_TMEM_EMPTY);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * 256;
         uint32_t accum = 0;
         for (int kb = 0; kb < p.num_k; ++kb) {
           mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);
           const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < KBYTES / 32; ++k) {
-            if (fp8)
-              umma_ss_pair<true>(d_tmem, das + k * ka, dbs + k * kb16, idesc, accum);
-            else
-              umma_ss_pair<false>(d_tmem, das + k * ka, dbs + k * kb16, idesc, accum);
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+              const uint64_t db = dbs + (j * ((HALF_N * KBYTES) >> 4) + k * kb16);
+              if (fp8)
+                umma_ss_pair<true>(d_tmem + j * 256, das + k * ka, db, idesc, accum);
+              else
+                umma_ss_pair<false>(d_tmem + j * 256, das + k * ka, db, idesc, accum);
+            }
             accum = 1;
           }
           tc_commit_pair(&empty[s]);
@@ -376,22 +445,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++ti) {
       int pid_m, pid_n;
       tile_coords(p, tile, pid_m, pid_n);
-      const uint32_t acc = ti & 1u;
-      mbar_wait(&tmem_full[acc], (ti >> 1) & 1u, p.status, SITE_GEMM_TMEM_FULL);
+      const uint32_t acc = ti % NACC;
+      mbar_wait(&tmem_full[acc], (ti / NACC) & 1u, p.status, SITE_GEMM_TMEM_FULL);
       tc_fence_after();
-      const int row = pid_m * 256 + rank * 128 + quarter * 32 + lane;
-      const int n0 = pid_n * BN;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((quarter * 32u) << 16) + acc * BN + c0, r);
-        tmem_ld_wait();
-        if (row < p.M) store_chunk32(p, row, n0 + c0, r, scale, vec_ok);
-      }
+      drain_accumulator(p, &tma_c, staging + (warp - 2) * STG_BYTES,
+                        tmem_base + ((quarter * 32u) << 16) + acc * 256, BN,
+                        pid_m * 256 + rank * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(&tmem_empty[acc], 0);  // the leader's barrier
     }
+    if (p.c_tma && lane == 0) tma_store_wait_all<0>();
   }
 
   if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
@@ -493,14 +557,15 @@ OperandGeom make_geom(bool mn_major, int rows, int elt, int bk_elems) {
   return g;
 }
 
-constexpr size_t smem_bytes(int stages, int stage_bytes) {
-  return (size_t)stages * stage_bytes + (2 * stages + 4) * 8 + 16 + 1024;
+constexpr size_t smem_bytes(int stages, int stage_bytes, int epilogue_warps) {
+  return (size_t)stages * stage_bytes + (size_t)epilogue_warps * STG_BYTES + (2 * stages + 4) * 8 + 16 + 1024;
 }
 
 template <int BM, int BN, int STAGES>
-int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, GemmParams& p) {
+int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
+                GemmParams& p) {
   static bool attr_done[64] = {};
-  constexpr size_t smem = smem_bytes(STAGES, (BM + BN) * KBYTES);
+  constexpr size_t smem = smem_bytes(STAGES, (BM + BN) * KBYTES, BM / 32);
   if (!attr_done[ctx->device]) {
     cudaError_t e =
         cudaFuncSetAttribute(gemm_kernel<BM, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -508,19 +573,20 @@ int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, cons
     attr_done[ctx->device] = true;
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
-  gemm_kernel<BM, BN, STAGES><<<grid, 64 + BM, smem, stream>>>(ta, tb_, p);
+  gemm_kernel<BM, BN, STAGES><<<grid, 64 + BM, smem, stream>>>(ta, tb_, tc, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
 
-constexpr int PAIR_STAGES = 7;
-
-int launch_pair(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, GemmParams& p) {
+template <int STAGES, int NB>
+int launch_pair(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
+                GemmParams& p) {
   static bool attr_done[64] = {};
-  constexpr size_t smem = smem_bytes(PAIR_STAGES, 256 * KBYTES);
+  constexpr size_t smem = smem_bytes(STAGES, (128 + 128 * NB) * KBYTES, pair_staging_warps(STAGES, NB));
+  if (pair_staging_warps(STAGES, NB) == 0) p.c_tma = 0;
   if (!attr_done[ctx->device]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<PAIR_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<STAGES, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(gemm pair): %s", cudaGetErrorString(e));
     attr_done[ctx->device] = true;
@@ -539,7 +605,7 @@ int launch_pair(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<PAIR_STAGES>, ta, tb_, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<STAGES, NB>, ta, tb_, tc, p);
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "gemm pair launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
@@ -572,28 +638,32 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     return B200_OK;
   }
 
-  // Tile shape.  B200_GEMM_TILE forces one: 128064, 128128, 128256, 256256, or 2256 for the CTA pair.
+  // Tile shape.  B200_GEMM_TILE forces one: 128064, 128128, 128256, 256256, or 2256 / 2512 for the CTA pair
+  // (256 x 256 / 256 x 512).
   auto tiles = [&](int bm_, int bn_) { return (long long)((M + bm_ - 1) / bm_) * ((N + bn_ - 1) / bn_); };
   int bm = 128, bn = 64;
   bool pair = false;
   const int force = env_int("B200_GEMM_TILE", 0);
-  if (force == 2256) {
+  int pair_nb = 1;  // 256-column MMAs per pair tile
+  if (force == 2256 || force == 2512) {
     pair = true;
+    pair_nb = force == 2512 ? 2 : 1;
   } else if (force) {
     bm = force / 1000;
     bn = force % 1000;
   } else if (tiles(256, 256) >= ctx->sm_count) {
-    // enough 256 x 256 tiles for every SM: fp8 runs best on the pair, 16-bit types on one CTA
-    if (elt == 1) pair = true;
-    else { bm = 256; bn = 256; }
+    // enough 256 x 256 tiles for every SM.  The single-CTA shape measured fastest for every dtype
+    // (fp16 1.37 vs 1.27 PFLOP/s, e4m3 2.71 vs 2.66 for the 256 x 256 pair on the same GPU); the
+    // pair shapes stay selectable through B200_GEMM_TILE.
+    bm = 256; bn = 256;
   } else {
     for (int cand : {256, 128}) {
       if (tiles(128, cand) >= ctx->sm_count) { bn = cand; break; }
     }
   }
-  if (pair) { bm = 256; bn = 256; }
+  if (pair) { bm = 256; bn = 256 * pair_nb; }
   if (elt == 1 && b_mn && bn < 128) bn = 128;  // an MN-major box is 128 columns of 1-byte elements
-  if (!((bm == 128 && (bn == 64 || bn == 128 || bn == 256)) || (bm == 256 && bn == 256)))
+  if (!pair && !((bm == 128 && (bn == 64 || bn == 128 || bn == 256)) || (bm == 256 && bn == 256)))
     return fail(B200_ERR_ARG, "B200_GEMM_TILE=%d is not a tile shape of this library", force);
   const int a_rows = pair ? 128 : bm;  // rows of A / columns of B that one CTA stages
   const int b_rows = pair ? 128 : bn;
@@ -609,7 +679,7 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   p.group_m = env_int("B200_GEMM_GROUP_M", 8);
   if (p.group_m < 1) p.group_m = 1;
   const int fmt = (in_dtype == B200_BF16) ? 1 : 0;  // kind::f16: f16 = 0, bf16 = 1; kind::f8f6f4: e4m3 = 0
-  p.idesc = make_idesc(fmt, fmt, a_mn, b_mn, pair ? 256 : 128, bn);
+  p.idesc = make_idesc(fmt, fmt, a_mn, b_mn, pair ? 256 : 128, pair ? 256 : bn);
   p.ga = make_geom(a_mn, a_rows, elt, bk_elems);
   p.gb = make_geom(b_mn, b_rows, elt, bk_elems);
 
@@ -624,13 +694,22 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     else       { dims[0] = N; dims[1] = K; strides[0] = (uint64_t)sbk * elt; box[0] = p.gb.box_mn; box[1] = bk_elems; }
     if (!encode_tmap(&tbm, in_dtype, 2, b, dims, strides, box, true)) return B200_ERR_UNSUPPORTED;
   }
-  if (pair) return launch_pair(ctx, stream, ta, tbm, p);
+  // C through TMA stores when it is a 16-bit output that a tensor map can describe
+  CUtensorMap tcm = ta;  // a valid map even when unused
+  p.c_tma = 0;
+  if (out_dtype != B200_F32 && (reinterpret_cast<uintptr_t>(c) & 15) == 0 && ((scm * 2) & 15) == 0 &&
+      !env_int("B200_GEMM_DIRECT_STORE", 0)) {
+    uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)scm * 2};
+    uint32_t box[2] = {64, 32};
+    if (encode_tmap(&tcm, out_dtype, 2, c, dims, strides, box, true)) p.c_tma = 1;
+  }
+  if (pair) return pair_nb == 2 ? launch_pair<4, 2>(ctx, stream, ta, tbm, tcm, p) : launch_pair<7, 1>(ctx, stream, ta, tbm, tcm, p);
   switch (bn) {
     case 256:
-      if (bm == 256) return launch_tile<256, 256, 3>(ctx, stream, ta, tbm, p);
-      return launch_tile<128, 256, 4>(ctx, stream, ta, tbm, p);
-    case 128: return launch_tile<128, 128, 6>(ctx, stream, ta, tbm, p);
-    default: return launch_tile<128, 64, 8>(ctx, stream, ta, tbm, p);
+      if (bm == 256) return launch_tile<256, 256, 3>(ctx, stream, ta, tbm, tcm, p);
+      return launch_tile<128, 256, 4>(ctx, stream, ta, tbm, tcm, p);
+    case 128: return launch_tile<128, 128, 6>(ctx, stream, ta, tbm, tcm, p);
+    default: return launch_tile<128, 64, 7>(ctx, stream, ta, tbm, tcm, p);
   }
 }
 
