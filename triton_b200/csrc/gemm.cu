@@ -19,12 +19,13 @@
 // What bounds the big shapes is the L2 -> shared-memory fill (bytes per flop), not the tensor
 // pipe, hence the preference for 256-row tiles when the problem has enough of them.
 //
-// Structure of one CTA (64 + 128 threads per 128 tile rows):
+// Structure of one CTA (64 + 128 threads per 128 tile rows, plus one warp for the 256-row tile):
 //   warp 0      TMA producer: fills a ring of shared-memory stages (128-byte swizzle) and signals
 //               `full[s]` through the copy's byte count
 //   warp 1      MMA issuer: one thread issues tcgen05.mma (32 bytes of K per instruction) into a
 //               TMEM accumulator; tcgen05.commit releases the stage (`empty[s]`) and, after the
-//               last K block, publishes the accumulator (`tmem_full[acc]`)
+//               last K block, publishes the accumulator (`tmem_full[acc]`).  The 256-row tile has
+//               a second issuing thread (last warp) for its lower 128 rows
 //   warps 2..   epilogue: tcgen05.ld the accumulator (each warp owns 32 TMEM lanes = 32 rows),
 //               scale / activation / convert, store C, then hand the accumulator back
 //               (`tmem_empty[acc]`)
@@ -189,7 +190,7 @@ __device__ __forceinline__ void load_operand(const OperandGeom& g, const CUtenso
 
 // ------------------------------------------------------------------------------- single CTA
 template <int BM, int BN, int STAGES>
-__global__ void __launch_bounds__(64 + BM, 1)
+__global__ void __launch_bounds__(64 + BM + (BM == 256 ? 32 : 0), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
             const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   constexpr uint32_t A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -212,10 +213,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 1);
+      mbar_init(&empty[s], MH);  // one commit per issuing thread
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_full[i], MH);
       mbar_init(&tmem_empty[i], BM);
     }
     if (p.c_tma) tma_prefetch_desc(&tma_c);
@@ -250,7 +251,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 || (MH == 2 && warp == 2 + BM / 32)) {
+    // One issuing thread per 128-row half of the tile (warp 1: rows 0-127, the last warp: rows
+    // 128-255).  The halves have separate accumulators and share the B stage; while one thread
+    // does its per-stage bookkeeping the other keeps the pipe fed (+3 % fp16, +4 % fp8 measured).
+    const int h = (warp == 1) ? 0 : 1;
     if (lane == 0) {
       // The issue loop is kept lean (the tensor pipe queues only about one MMA ahead of the
       // issuing thread): a descriptor is a constant plus (address >> 4) in its low bits, and
@@ -272,14 +277,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < KBYTES / 32; ++k) {
-#pragma unroll
-            for (int h = 0; h < MH; ++h) {  // rows [128h, 128h+128) of the A stage, 16 KiB apart
-              const uint64_t da = das + (h * ((128 * KBYTES) >> 4) + k * ka);
-              if (fp8)
-                umma_ss<true>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
-              else
-                umma_ss<false>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
-            }
+            const uint64_t da = das + (h * ((128 * KBYTES) >> 4) + k * ka);  // rows [128h, 128h+128): 16 KiB apart
+            if (fp8)
+              umma_ss<true>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
+            else
+              umma_ss<false>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
             accum = 1;
           }
           tc_commit(&empty[s]);
@@ -573,7 +575,7 @@ int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, cons
     attr_done[ctx->device] = true;
   }
   const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
-  gemm_kernel<BM, BN, STAGES><<<grid, 64 + BM, smem, stream>>>(ta, tb_, tc, p);
+  gemm_kernel<BM, BN, STAGES><<<grid, 64 + BM + (BM == 256 ? 32 : 0), smem, stream>>>(ta, tb_, tc, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
   return B200_OK;
