@@ -653,14 +653,21 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   } else if (force) {
     bm = force / 1000;
     bn = force % 1000;
-  } else if (tiles(256, 256) >= ctx->sm_count) {
-    // enough 256 x 256 tiles for every SM.  The single-CTA shape measured fastest for every dtype
-    // (fp16 1.37 vs 1.27 PFLOP/s, e4m3 2.71 vs 2.66 for the 256 x 256 pair on the same GPU); the
-    // pair shapes stay selectable through B200_GEMM_TILE.
-    bm = 256; bn = 256;
   } else {
-    for (int cand : {256, 128}) {
-      if (tiles(128, cand) >= ctx->sm_count) { bn = cand; break; }
+    // Pick the shape with the smallest estimated time: waves x (tile time + fixed cost).  Per-SM
+    // rates relative to the 256 x 256 tile (measured on multi-wave problems: 1.17, 1.02, 0.70,
+    // 0.37 PFLOP/s at 4096^3) and about 4 us of prologue / epilogue per tile.  On large problems
+    // the single-CTA 256 x 256 shape also beat the pair shapes for every dtype (fp16 1.41 vs 1.27
+    // PFLOP/s, e4m3 2.85 vs 2.66 on the same GPU); those stay selectable through B200_GEMM_TILE.
+    struct Cand { int bm, bn; double rate; };
+    const Cand cands[4] = {{256, 256, 1.0}, {128, 256, 0.88}, {128, 128, 0.60}, {128, 64, 0.32}};
+    double best = 1e300;
+    for (const Cand& cd : cands) {
+      const long long t = tiles(cd.bm, cd.bn);
+      const long long waves = (t + ctx->sm_count - 1) / ctx->sm_count;
+      const double tile_us = 2.0 * cd.bm * cd.bn * (double)K / (7.9e6 * cd.rate) + 4.0;
+      const double est = (double)waves * tile_us;
+      if (est < best) { best = est; bm = cd.bm; bn = cd.bn; }
     }
   }
   if (pair) { bm = 256; bn = 256 * pair_nb; }
