@@ -16,6 +16,7 @@
 #ifndef TRITON_B200_H_
 #define TRITON_B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -65,6 +66,20 @@ B200_API int b200_matmul(b200_stream_t stream, const void* a, const void* b, voi
                 int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
                 int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
                 const float* scale_a, const float* scale_b);
+
+/* Split-K variant for skinny problems (few output tiles, long K; the tall-skinny shapes of
+ * python/test/regression/test_performance.py:36-46).  b200_matmul_plan says how many K splits pay
+ * off for a shape on the current device and how large the fp32 workspace must be (0 when splits
+ * is 1); b200_matmul_splitk computes exactly what b200_matmul computes, with the K range cut in
+ * `splits` parts whose fp32 partial tiles go to `workspace` ([splits][M][N] floats, caller's
+ * scratch) and are summed in a fixed order by a second kernel (deterministic).  splits == 1 is
+ * b200_matmul.  The reference has no counterpart (its kernels do not split K); the library still
+ * allocates nothing. */
+B200_API int b200_matmul_plan(int M, int N, int K, int in_dtype, int* splits, size_t* workspace_bytes);
+B200_API int b200_matmul_splitk(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
+                                int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
+                                int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
+                                const float* scale_a, const float* scale_b, int splits, float* workspace);
 
 /* Flash-attention forward: O = softmax(Q K^T * sm_scale, causal mask optional) V, and per-row
  * statistics M[Z,H,N] (fp32) = base-2 log-sum-exp of the scores scaled by sm_scale * log2(e)

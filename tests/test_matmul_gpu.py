@@ -129,6 +129,83 @@ def test_plain_kernel_matches_tensor_core_kernel(monkeypatch):
     np.testing.assert_allclose(f32(plain), f32(fast), rtol=2e-3, atol=2e-3)
 
 
+def _raw_matmul_splitk(a, b, splits, out_dtype=None, activation="", scales=(None, None)):
+    """Calls b200_matmul_splitk with an explicit split count (the wrapper only picks the planned one)."""
+    from triton_b200.ops import _ACT, _DT, _stream
+    M, K = a.shape
+    N = b.shape[1]
+    out_dtype = out_dtype or a.dtype
+    c = torch.empty(M, N, device=a.device, dtype=out_dtype)
+    ws = torch.empty(max(splits, 1) * M * N, device=a.device, dtype=torch.float32)
+    sa, sb = scales
+    code = _lib.lib().b200_matmul_splitk(
+        _stream(a), a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K, a.stride(0), a.stride(1), b.stride(0),
+        b.stride(1), c.stride(0), c.stride(1), _DT[a.dtype], _DT[out_dtype], _ACT[activation],
+        sa.data_ptr() if sa is not None else None, sb.data_ptr() if sb is not None else None, splits,
+        ws.data_ptr() if splits > 1 else None)
+    _lib.check(code, "matmul_splitk")
+    return c
+
+
+@pytest.mark.parametrize("shape", [(16, 4096, 4096), (64, 4096, 4096), (8192, 64, 8192), (130, 72, 2056)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_skinny_shapes_take_split_k(shape, dtype):
+    """Few tiles and a long K: the plan cuts K, the wrapper supplies the workspace, the result is the
+    oracle's (fp32 partial sums, one rounding at the end)."""
+    import ctypes
+    M, N, K = shape
+    splits, ws_bytes = ctypes.c_int(0), ctypes.c_size_t(0)
+    _lib.check(_lib.lib().b200_matmul_plan(M, N, K, 0, ctypes.byref(splits), ctypes.byref(ws_bytes)), "plan")
+    assert splits.value > 1 and ws_bytes.value == splits.value * M * N * 4
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g).to(dtype)
+    b = torch.randn(K, N, generator=g).to(dtype)
+    got = triton_b200.matmul(a.to(DEV), b.to(DEV), activation="leaky_relu")
+    status_ok()
+    want = R.matmul(f32(a), f32(b), activation="leaky_relu", out="fp16" if dtype == torch.float16 else "bf16")
+    np.testing.assert_allclose(f32(got), want, rtol=1e-2, atol=1e-2)
+    # large problems are never split
+    _lib.check(_lib.lib().b200_matmul_plan(4096, 4096, 4096, 0, ctypes.byref(splits), ctypes.byref(ws_bytes)), "plan")
+    assert splits.value == 1 and ws_bytes.value == 0
+
+
+@pytest.mark.parametrize("splits", [1, 2, 3, 7, 16, 64])
+def test_split_k_any_split_count(splits):
+    """Any split count gives the unsplit result up to the fp32 summation order; more splits than
+    K blocks are clipped; fp32 output, scales and fp8 operands take the same path."""
+    M, N, K = 200, 136, 1544  # ragged in every dimension: 25 K blocks, the last one partial
+    g = torch.Generator().manual_seed(splits)
+    a = torch.randn(M, K, generator=g).half().to(DEV)
+    b = torch.randn(K, N, generator=g).half().to(DEV)
+    base = _raw_matmul_splitk(a, b, 1, out_dtype=torch.float32)
+    got = _raw_matmul_splitk(a, b, splits, out_dtype=torch.float32)
+    status_ok()
+    want = f32(a).astype(np.float64) @ f32(b).astype(np.float64)
+    np.testing.assert_allclose(f32(got), want, rtol=1e-4, atol=1e-3)
+    np.testing.assert_allclose(f32(got), f32(base), rtol=1e-4, atol=1e-3)
+    again = _raw_matmul_splitk(a, b, splits, out_dtype=torch.float32)
+    assert torch.equal(got, again), "the reduction order is fixed: two runs are bit-identical"
+    # fp8 with per-tensor scales and bf16 output
+    a8, sa = triton_b200.quantize_e4m3(a.float())
+    b8, sb = triton_b200.quantize_e4m3(b.float())
+    c1 = _raw_matmul_splitk(a8, b8, 1, out_dtype=torch.bfloat16, scales=(sa, sb))
+    cs = _raw_matmul_splitk(a8, b8, splits, out_dtype=torch.bfloat16, scales=(sa, sb))
+    status_ok()
+    np.testing.assert_allclose(f32(cs), f32(c1), rtol=1e-2, atol=1e-2)
+
+
+def test_split_k_argument_errors():
+    a = torch.zeros(16, 4096, device=DEV, dtype=torch.float16)
+    b = torch.zeros(4096, 64, device=DEV, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="splits"):
+        _raw_matmul_splitk(a, b, 65)
+    from triton_b200.ops import _stream
+    c = torch.empty(16, 64, device=DEV, dtype=torch.float16)
+    code = _lib.lib().b200_matmul_splitk(_stream(a), a.data_ptr(), b.data_ptr(), c.data_ptr(), 16, 64, 4096, 4096, 1,
+                                         64, 1, 64, 1, 0, 0, 0, None, None, 4, None)
+    assert code == 1 and b"workspace" in _lib.lib().b200_last_error()
+
+
 @pytest.mark.parametrize("name", list(cases.FP8_CASES))
 def test_fp8_accumulator_matches_golden(golden, name):
     c = cases.FP8_CASES[name]

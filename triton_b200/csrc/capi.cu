@@ -191,6 +191,28 @@ int b200_status(unsigned* value, int clear) {
 int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K, int64_t stride_am,
                 int64_t stride_ak, int64_t stride_bk, int64_t stride_bn, int64_t stride_cm, int64_t stride_cn,
                 int in_dtype, int out_dtype, int activation, const float* scale_a, const float* scale_b) {
+  return b200_matmul_splitk(stream, a, b, c, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn,
+                            in_dtype, out_dtype, activation, scale_a, scale_b, 1, nullptr);
+}
+
+int b200_matmul_plan(int M, int N, int K, int in_dtype, int* splits, size_t* workspace_bytes) {
+  if (M < 0 || N < 0 || K < 0 || !splits || !workspace_bytes) return fail(B200_ERR_ARG, "bad argument");
+  if (in_dtype != B200_F16 && in_dtype != B200_BF16 && in_dtype != B200_E4M3)
+    return fail(B200_ERR_ARG, "in_dtype must be F16, BF16 or E4M3");
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  *splits = (M == 0 || N == 0 || K == 0) ? 1 : gemm_plan_splits(ctx, M, N, K, in_dtype);
+  *workspace_bytes = *splits > 1 ? (size_t)*splits * M * N * sizeof(float) : 0;
+  return B200_OK;
+}
+
+int b200_matmul_splitk(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
+                       int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn, int64_t stride_cm,
+                       int64_t stride_cn, int in_dtype, int out_dtype, int activation, const float* scale_a,
+                       const float* scale_b, int splits, float* workspace) {
+  if (splits < 1 || splits > 64) return fail(B200_ERR_ARG, "splits must be in [1, 64]");
+  if (splits > 1 && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15)))
+    return fail(B200_ERR_ARG, "split-K needs a 16-byte aligned workspace of splits * M * N floats");
   if (M < 0 || N < 0 || K < 0) return fail(B200_ERR_ARG, "negative dimension");
   if (in_dtype != B200_F16 && in_dtype != B200_BF16 && in_dtype != B200_E4M3)
     return fail(B200_ERR_ARG, "in_dtype must be F16, BF16 or E4M3");
@@ -211,7 +233,7 @@ int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int
     return B200_OK;
   }
   return launch_gemm(ctx, reinterpret_cast<cudaStream_t>(stream), a, b, c, M, N, K, stride_am, stride_ak, stride_bk,
-                     stride_bn, stride_cm, in_dtype, out_dtype, activation, scale_a, scale_b);
+                     stride_bn, stride_cm, in_dtype, out_dtype, activation, scale_a, scale_b, splits, workspace);
 }
 
 int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m, int Z,

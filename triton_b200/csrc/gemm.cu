@@ -62,6 +62,9 @@ struct GemmParams {
   int num_pid_m, num_pid_n, num_tiles, num_k, bk_elems;
   int group_m;  // tile rows per rasterisation group (the reference's GROUP_SIZE_M)
   int c_tma;    // C is written through shared-memory staging + TMA stores (16-bit outputs TMA can address)
+  int splits;   // split-K: work items = tiles x splits, each writes an fp32 partial tile to `ws`
+  int kb_per_split;
+  float* ws;    // [splits][M][N] fp32 partial sums (caller's workspace), reduced by splitk_reduce_kernel
   uint32_t idesc;
   OperandGeom ga, gb;
 };
@@ -173,6 +176,30 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
   }
 }
 
+// split-K: one epilogue warp writes its 32 rows of raw fp32 partial sums to a dense [M][N] slice
+__device__ __forceinline__ void drain_partial(float* ws, int M, int N, uint32_t taddr, int ncols, int row0, int col0,
+                                              int lane) {
+  const int row = row0 + lane;
+  const bool vec_ok = (N & 3) == 0;  // the slice base is 16-byte aligned (checked on the host)
+#pragma unroll 1
+  for (int c0 = 0; c0 < ncols; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld32(taddr + c0, r);
+    tmem_ld_wait();
+    if (row >= M) continue;
+    const int col = col0 + c0;
+    float* dst = ws + (long long)row * N + col;
+    if (vec_ok && col + 32 <= N) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        reinterpret_cast<uint4*>(dst)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col + j < N) dst[j] = __uint_as_float(r[j]);
+    }
+  }
+}
+
 // TMA boxes of one operand stage (2-D maps: K-major {k, row}; MN-major {row, k} in 128-byte column blocks)
 template <bool PAIR>
 __device__ __forceinline__ void load_operand(const OperandGeom& g, const CUtensorMap* map, uint8_t* dst, uint64_t* bar,
@@ -236,11 +263,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   if (warp == 0) {
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      for (int work = blockIdx.x; work < p.num_tiles * p.splits; work += gridDim.x) {
+        const int tile = work % p.num_tiles, split = work / p.num_tiles;
         int pid_m, pid_n;
         tile_coords(p, tile, pid_m, pid_n);
         const int m0 = pid_m * BM, n0 = pid_n * BN;
-        for (int kb = 0; kb < p.num_k; ++kb) {
+        const int kb_end = min(p.num_k, (split + 1) * p.kb_per_split);
+        for (int kb = split * p.kb_per_split; kb < kb_end; ++kb) {
           mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
           mbar_expect_tx(&full[s], STAGE_BYTES);
           uint8_t* a_dst = smem + s * STAGE_BYTES;
@@ -266,13 +295,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const uint32_t idesc = p.idesc;
       const bool fp8 = p.fp8 != 0;
       uint32_t s = 0, ph = 0, ti = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
+      for (int work = blockIdx.x; work < p.num_tiles * p.splits; work += gridDim.x, ++ti) {
+        const int split = work / p.num_tiles;
+        const int kb_cnt = min(p.num_k, (split + 1) * p.kb_per_split) - split * p.kb_per_split;
         const uint32_t acc = ti % NACC;
         mbar_wait(&tmem_empty[acc], ((ti / NACC) & 1u) ^ 1u, p.status, SITE_GEMM_TMEM_EMPTY);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         uint32_t accum = 0;
-        for (int kb = 0; kb < p.num_k; ++kb) {
+        for (int kb = 0; kb < kb_cnt; ++kb) {
           mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);  // TMA bytes landed
           const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
@@ -300,12 +331,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     const int esize = (p.out_dtype == B200_F32) ? 4 : 2;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (((p.ldc * esize) & 15) == 0);
     uint32_t ti = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++ti) {
+    for (int work = blockIdx.x; work < p.num_tiles * p.splits; work += gridDim.x, ++ti) {
+      const int tile = work % p.num_tiles, split = work / p.num_tiles;
       int pid_m, pid_n;
       tile_coords(p, tile, pid_m, pid_n);
       const uint32_t acc = ti % NACC;
       mbar_wait(&tmem_full[acc], (ti / NACC) & 1u, p.status, SITE_GEMM_TMEM_FULL);
       tc_fence_after();
+      if (p.splits > 1) {
+        // split-K: the raw fp32 partial sums go to this split's slice of the workspace
+        drain_partial(p.ws + (long long)split * p.M * p.N, p.M, p.N,
+                      tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
+                      pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane);
+      } else
       drain_accumulator(p, &tma_c, staging + (warp - 2) * STG_BYTES,
                         tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
                         pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
@@ -532,6 +570,24 @@ gemm_plain_kernel(const void* a, const void* b, GemmParams p, long long sam, lon
   }
 }
 
+// split-K second pass: C = act(scale * sum over splits of the fp32 partial tiles), one rounding
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(GemmParams p) {
+  const long long total = (long long)p.M * p.N;
+  float scale = 1.f;
+  if (p.scale_a) scale *= __ldg(p.scale_a);
+  if (p.scale_b) scale *= __ldg(p.scale_b);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float v = 0.f;
+    for (int sp = 0; sp < p.splits; ++sp) v += p.ws[(long long)sp * total + i];  // fixed order: deterministic
+    v = apply_act(v * scale, p.activation);
+    const long long o = (i / p.N) * p.ldc + (i % p.N);
+    if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
+    else if (p.out_dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
+    else reinterpret_cast<__half*>(p.c)[o] = __float2half_rn(v);
+  }
+}
+
 // ------------------------------------------------------------------------------------- host
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
@@ -574,7 +630,8 @@ int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, cons
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
     attr_done[ctx->device] = true;
   }
-  const int grid = p.num_tiles < ctx->sm_count ? p.num_tiles : ctx->sm_count;
+  const int work = p.num_tiles * p.splits;
+  const int grid = work < ctx->sm_count ? work : ctx->sm_count;
   gemm_kernel<BM, BN, STAGES><<<grid, 64 + BM + (BM == 256 ? 32 : 0), smem, stream>>>(ta, tb_, tc, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
@@ -614,9 +671,25 @@ int launch_pair(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, cons
 
 }  // namespace
 
+// Split-K plan for skinny problems: when the chosen tile shape gives fewer than half as many tiles as
+// there are SMs and K is long, the K range is cut so that about one wave of work items exists.
+int gemm_plan_splits(DeviceCtx* ctx, int M, int N, int K, int in_dtype) {
+  const int forced = env_int("B200_GEMM_SPLITK", -1);  // 0 or 1: never split; n > 1: that many splits
+  if (forced >= 0) return forced < 1 ? 1 : (forced > 64 ? 64 : forced);
+  const int bk_elems = KBYTES / dtype_bytes(in_dtype);
+  const int num_k = (K + bk_elems - 1) / bk_elems;
+  // skinny problems always end up on the 128 x 64 tile (most tiles)
+  const long long tiles = (long long)((M + 127) / 128) * ((N + 63) / 64);
+  if (tiles * 2 > ctx->sm_count || num_k < 8) return 1;
+  long long s = ctx->sm_count / tiles;
+  if (s > num_k / 4) s = num_k / 4;
+  if (s > 16) s = 16;
+  return s < 1 ? 1 : (int)s;
+}
+
 int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                 int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t scm, int in_dtype, int out_dtype,
-                int activation, const float* scale_a, const float* scale_b) {
+                int activation, const float* scale_a, const float* scale_b, int splits, float* ws) {
   const int elt = dtype_bytes(in_dtype);
   const int bk_elems = KBYTES / elt;
   const bool a_mn = !(sak == 1 || K == 1);  // K contiguous preferred
@@ -647,7 +720,9 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   bool pair = false;
   const int force = env_int("B200_GEMM_TILE", 0);
   int pair_nb = 1;  // 256-column MMAs per pair tile
-  if (force == 2256 || force == 2512) {
+  if (splits > 1) {
+    bm = 128; bn = 64;  // split-K serves skinny problems: the shape with the most tiles
+  } else if (force == 2256 || force == 2512) {
     pair = true;
     pair_nb = force == 2512 ? 2 : 1;
   } else if (force) {
@@ -685,6 +760,9 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   p.num_tiles = p.num_pid_m * p.num_pid_n;
   p.num_k = (K + bk_elems - 1) / bk_elems;
   p.bk_elems = bk_elems;
+  p.kb_per_split = (p.num_k + splits - 1) / splits;
+  p.splits = (p.num_k + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  p.ws = ws;
   p.group_m = env_int("B200_GEMM_GROUP_M", 8);
   if (p.group_m < 1) p.group_m = 1;
   const int fmt = (in_dtype == B200_BF16) ? 1 : 0;  // kind::f16: f16 = 0, bf16 = 1; kind::f8f6f4: e4m3 = 0
@@ -713,13 +791,23 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     if (encode_tmap(&tcm, out_dtype, 2, c, dims, strides, box, true)) p.c_tma = 1;
   }
   if (pair) return pair_nb == 2 ? launch_pair<4, 2>(ctx, stream, ta, tbm, tcm, p) : launch_pair<7, 1>(ctx, stream, ta, tbm, tcm, p);
+  int rc;
   switch (bn) {
     case 256:
-      if (bm == 256) return launch_tile<256, 256, 3>(ctx, stream, ta, tbm, tcm, p);
-      return launch_tile<128, 256, 4>(ctx, stream, ta, tbm, tcm, p);
-    case 128: return launch_tile<128, 128, 6>(ctx, stream, ta, tbm, tcm, p);
-    default: return launch_tile<128, 64, 7>(ctx, stream, ta, tbm, tcm, p);
+      rc = (bm == 256) ? launch_tile<256, 256, 3>(ctx, stream, ta, tbm, tcm, p)
+                       : launch_tile<128, 256, 4>(ctx, stream, ta, tbm, tcm, p);
+      break;
+    case 128: rc = launch_tile<128, 128, 6>(ctx, stream, ta, tbm, tcm, p); break;
+    default: rc = launch_tile<128, 64, 7>(ctx, stream, ta, tbm, tcm, p); break;
   }
+  if (rc || p.splits == 1) return rc;
+  const long long total = (long long)M * N;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
+  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "split-K reduce launch: %s", cudaGetErrorString(e));
+  return B200_OK;
 }
 
 }  // namespace tb

@@ -9,6 +9,8 @@
 Tensors are torch CUDA tensors (torch supplies device memory, streams and autograd
 plumbing); the arithmetic is done by the library's sm_100a kernels through the C ABI.
 """
+import ctypes
+
 import torch
 
 from . import _lib
@@ -68,10 +70,16 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
 
         pa, keep_a = scale_ptr(scale_a)
         pb, keep_b = scale_ptr(scale_b)
-        code = _lib.lib().b200_matmul(
+        # skinny problems (few tiles, long K) are split along K; the fp32 partial tiles need scratch
+        splits, ws_bytes = ctypes.c_int(1), ctypes.c_size_t(0)
+        _lib.check(_lib.lib().b200_matmul_plan(M, N, K, _DT[a.dtype], ctypes.byref(splits), ctypes.byref(ws_bytes)),
+                   "matmul_plan")
+        ws = torch.empty(ws_bytes.value // 4, device=dev, dtype=torch.float32) if splits.value > 1 else None
+        code = _lib.lib().b200_matmul_splitk(
             _stream(a), a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K,
             a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
-            _DT[a.dtype], _DT[out_dtype], _ACT[activation], pa, pb)
+            _DT[a.dtype], _DT[out_dtype], _ACT[activation], pa, pb, splits.value,
+            ws.data_ptr() if ws is not None else None)
         _lib.check(code, "matmul")
     return c
 
