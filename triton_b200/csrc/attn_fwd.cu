@@ -91,6 +91,20 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int w) {
   return it;
 }
 
+#ifdef FWD_TRACE
+__device__ unsigned g_trace[3][8192][2];
+#define TRACE(region, tag)                                                        \
+  do {                                                                            \
+    if (blockIdx.x == 0 && trace_n < 8192) {                                      \
+      g_trace[region][trace_n][0] = (tag);                                        \
+      g_trace[region][trace_n][1] = (unsigned)clock64();                          \
+      ++trace_n;                                                                  \
+    }                                                                             \
+  } while (0)
+#else
+#define TRACE(region, tag)
+#endif
+
 template <int D, bool BF16>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -122,6 +136,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   float* xchg = reinterpret_cast<float*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef FWD_TRACE
+  unsigned trace_n = 0;
+#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -183,9 +200,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
-    // One thread issues for both tiles.  (Two issuing threads, one per tile, were measured 20 %
-    // slower: MMAs of different threads interleave in the pipe at a cost.)
-    if (lane == 0) {
+    // The warp stays converged and an elected lane issues, for both tiles.  (Two issuing threads,
+    // one per tile, were measured 20 % slower: MMAs of different threads interleave in the pipe
+    // at a cost.)
+    {
       constexpr int FMT = BF16 ? 1 : 0;
       constexpr uint32_t IDESC_S = make_idesc(FMT, FMT, 0, 0, 128, BLK);  // Q (K-major) x K (K-major)
       constexpr uint32_t IDESC_O = make_idesc(FMT, FMT, 0, 1, 128, D);    // P (TMEM) x V (N-major)
@@ -200,15 +218,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * ((BLK * 128) >> 4) + (kk & 3) * 2;  // 64-col box, 32 B per step
-          umma_ss<false>(tm_s[i], dq + off, dk + off, IDESC_S, kk != 0);
+          umma_ss_elect<false>(tm_s[i], dq + off, dk + off, IDESC_S, kk != 0);
         }
-        tc_commit(&s_full[i]);
+        tc_commit_elect(&s_full[i]);
       };
       auto issue_pv = [&](int i, uint32_t stage, uint32_t accum) {  // O_i (+)= P_i V, 8 MMAs of 16 kv rows
         const uint64_t dv = dv0 + stage * (TILE >> 4);
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts_f16(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
+          umma_ts_f16_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
       };
       auto advance = [&]() { if (++s == NST) { s = 0; ph ^= 1u; } };
 
@@ -216,7 +234,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
         mbar_wait(&sched_full[slot], sph, p.status, SITE_FWD_SCHED);
         const int w = sched_item[slot];
-        mbar_arrive(&sched_empty[slot]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sched_empty[slot]);
         if (w >= p.total_items) break;
         const Item it = decode_item(p, w);
         const int n0 = it.n0, n1 = it.n1;
@@ -227,8 +246,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         issue_s(0, s);
         mbar_wait(&q_full[1], n & 1u, p.status, SITE_FWD_Q);
         issue_s(1, s);
-        tc_commit(&kv_empty[s]);
-        if (n1 == 1) tc_commit(q_empty);
+        tc_commit_elect(&kv_empty[s]);
+        if (n1 == 1) tc_commit_elect(q_empty);
         advance();
         for (int j = 0; j < n1; ++j) {
           const uint32_t vs = s, vph = ph;  // V_j
@@ -237,25 +256,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
           mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
           if (j < n0) {
+            TRACE(2, 0x00);
             mbar_wait(&p_full[0], pcnt[0]++ & 1u, p.status, SITE_FWD_P_FULL);
+            TRACE(2, 0x01);
             tc_fence_after();
             issue_pv(0, vs, j > 0);
-            if (j == n0 - 1) tc_commit(&o_full[0]);
+            TRACE(2, 0x02);
+            if (j == n0 - 1) tc_commit_elect(&o_full[0]);
             if (more0) {
               mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
               issue_s(0, ks);
+              TRACE(2, 0x03);
             }
           }
+          TRACE(2, 0x10);
           mbar_wait(&p_full[1], pcnt[1]++ & 1u, p.status, SITE_FWD_P_FULL);
+          TRACE(2, 0x11);
           tc_fence_after();
           issue_pv(1, vs, j > 0);
-          tc_commit(&kv_empty[vs]);
-          if (j == n1 - 1) tc_commit(&o_full[1]);
+          TRACE(2, 0x12);
+          tc_commit_elect(&kv_empty[vs]);
+          if (j == n1 - 1) tc_commit_elect(&o_full[1]);
           if (more1) {
             mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
             issue_s(1, ks);
-            tc_commit(&kv_empty[ks]);
-            if (j + 2 == n1) tc_commit(q_empty);  // that was the item's last S: the Q tiles may be replaced
+            TRACE(2, 0x13);
+            tc_commit_elect(&kv_empty[ks]);
+            if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
             advance();
           }
         }
@@ -294,12 +321,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       float m_ref = -INFINITY, l = 0.f;  // l: this thread's half of the row sum
 
       for (int j = 0; j < nb; ++j, ++scnt) {
+        if ((warp & 7) == 0 && lane == 0) TRACE(i, 0);
         mbar_wait(&s_full[i], scnt & 1u, p.status, SITE_FWD_S_FULL);
+        if ((warp & 7) == 0 && lane == 0) TRACE(i, 1);
         tc_fence_after();
         uint32_t r[HC];
 #pragma unroll
         for (int c = 0; c < HC; c += 32) tmem_ld32(tm_s[i] + lane_addr + half * HC + c, r + c);
         tmem_ld_wait();
+        if ((warp & 7) == 0 && lane == 0) TRACE(i, 2);
         const int col0 = j * BLK + half * HC;
         const bool need_mask = (p.causal && j * BLK + BLK - 1 > qb * 256 + i * BLK) || (j * BLK + BLK > p.N);
         if (need_mask) {
@@ -342,6 +372,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
           }
         }
+        if ((warp & 7) == 0 && lane == 0) TRACE(i, 3);
         const float neg_m = -m_ref;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -357,9 +388,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_st16(tm_s[i] + lane_addr + ((half * HC + c) >> 1), wv);
         }
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if ((warp & 7) == 0 && lane == 0) TRACE(i, 4);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_full[i]);
+        if ((warp & 7) == 0 && lane == 0) TRACE(i, 5);
       }
 
       // epilogue: the row sum is the two halves' sums; O / l and M.  It overlaps the next item's
@@ -430,6 +463,12 @@ int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, con
 }
 
 }  // namespace
+
+#ifdef FWD_TRACE
+extern "C" __attribute__((visibility("default"))) int b200_debug_fwd_trace(void* dst) {
+  return (int)cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace));
+}
+#endif
 
 // 4-D map over [Z, H, N, D] (D contiguous) with boxes of 64 columns x 128 rows
 bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
