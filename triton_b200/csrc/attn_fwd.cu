@@ -8,20 +8,17 @@
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong so that the
 // tensor pipe works on one tile while the other tile's softmax runs.
-//   warps 0-7 / 8-15  softmax of tile 0 / 1: two threads per row (warps w and w+4 own the same TMEM
-//                     lanes and split the 128 columns; row max and row sum are exchanged through
-//                     shared memory), so the softmax of a block takes about half the time of a
-//                     one-thread-per-row layout - it sits on the S -> P -> PV dependency chain.
+//   warps 0-3 / 4-7   softmax of tile 0 / 1, one thread per query row (no cross-thread reduction):
 //                     tcgen05.ld S, running max and sum, exp2, P packed to 16 bit and written back over S in TMEM
 //                     (tcgen05.st) as the A operand of the second MMA.  The accumulator O is
 //                     rescaled lazily: only when the running max grew by more than 2^8 does the
 //                     warp multiply its O rows in TMEM (the reference rescales every step; the
 //                     result is the same up to fp32 rounding since P and l carry the same factor).
 //                     At the end: O / l -> storage type -> global, M -> global.
-//   warp 16           MMA issuer (one thread): S_i = Q_i K_j^T (operands in shared memory) and
+//   warp 8            MMA issuer (one elected lane): S_i = Q_i K_j^T (operands in shared memory) and
 //                     O_i += P_i V_j (P from TMEM, V from shared memory, N-major).  MMAs of one
 //                     thread execute in issue order, which is what lets P alias S.
-//   warp 17           TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
+//   warp 9            TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
 // The kernel is persistent: one CTA per SM takes work items (256 query rows of one head) from an
 // atomic counter, head-major and heavy-first, so a head's K/V stay in L2, causal work balances, and
 // the epilogue of one item overlaps the loads and first MMAs of the next.
@@ -37,7 +34,7 @@ namespace tb {
 namespace {
 
 constexpr int BLK = 128;           // rows of a Q tile and of a K/V block
-constexpr int FWD_THREADS = 576;   // 16 softmax warps + MMA warp + TMA warp
+constexpr int FWD_THREADS = 320;   // 8 softmax warps + MMA warp + TMA warp
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdParams {
@@ -57,20 +54,14 @@ template <int D>
 struct FwdCfg {
   static constexpr int TILE_BYTES = BLK * D * 2;               // one Q tile or one K / V block
   static constexpr int KV_STAGES = (D == 128) ? 4 : 8;
-  // tiles + barriers + TMEM slot + 3 x 512 floats of row statistics exchanged between column halves
-  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 16) * 8 + 16 + 3 * 512 * 4 + 1024;
+  // tiles + barriers + TMEM slot + scheduler slots + alignment slack
+  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 18) * 8 + 32 + 1024;
 };
 
 template <int D>
 __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int z) {
 #pragma unroll
   for (int b = 0; b < D / 64; ++b) tma_load_4d(dst + b * (BLK * 128), map, bar, b * 64, row0, h, z);
-}
-
-// named barrier over the 256 softmax threads of one tile (ids 1 and 2; 0 is __syncthreads)
-__device__ __forceinline__ void tile_sync(int tile) {
-  if (tile == 0) asm volatile("bar.sync 1, 256;" ::: "memory");
-  else asm volatile("bar.sync 2, 256;" ::: "memory");
 }
 
 // One work item = 256 query rows of one (batch, head).  Items are numbered head-major, heavy
@@ -91,29 +82,13 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int w) {
   return it;
 }
 
-#ifdef FWD_TRACE
-__device__ unsigned g_trace[3][8192][2];
-#define TRACE(region, tag)                                                        \
-  do {                                                                            \
-    if (blockIdx.x == 0 && trace_n < 8192) {                                      \
-      g_trace[region][trace_n][0] = (tag);                                        \
-      g_trace[region][trace_n][1] = (unsigned)clock64();                          \
-      ++trace_n;                                                                  \
-    }                                                                             \
-  } while (0)
-#else
-#define TRACE(region, tag)
-#endif
-
 template <int D, bool BF16>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using Cfg = FwdCfg<D>;
   constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES;
-  constexpr int MMA_WARP = 16, TMA_WARP = 17;
-  constexpr int HC = BLK / 2;  // score columns per softmax thread
-  constexpr int HD = D / 2;    // accumulator columns per softmax thread
+  constexpr int MMA_WARP = 8, TMA_WARP = 9;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
@@ -125,29 +100,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* kv_full = bars + 2;        // [NST]
   uint64_t* kv_empty = kv_full + NST;  // [NST]
   uint64_t* s_full = kv_empty + NST;   // [2] S_i(j) is in TMEM
-  uint64_t* p_full = s_full + 2;       // [2] P_i(j) is in TMEM (and O_i rescaled if it had to be)
-  uint64_t* o_full = p_full + 2;       // [2] last P V of tile i done
+  uint64_t* p_full = s_full + 2;       // [2 tiles][2 halves] columns [64h, 64h+64) of P_i(j) are in TMEM (and O_i rescaled if it had to be)
+  uint64_t* o_full = p_full + 4;       // [2] last P V of tile i done
   uint64_t* q_empty = o_full + 2;      // [1] every S MMA of the item has read the Q tiles
   uint64_t* sched_full = q_empty + 1;  // [2] an item id was published
-  uint64_t* sched_empty = sched_full + 2;  // [2] all 17 readers have taken it
+  uint64_t* sched_empty = sched_full + 2;  // [2] all 9 readers have taken it
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + 2);
   volatile int* sched_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
-  // row statistics exchanged between the two threads of a row: [buffer][tile][half][row]
-  float* xchg = reinterpret_cast<float*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef FWD_TRACE
-  unsigned trace_n = 0;
-#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 256);
+      mbar_init(&p_full[2 * i], 128);
+      mbar_init(&p_full[2 * i + 1], 128);
       mbar_init(&o_full[i], 1);
       mbar_init(&sched_full[i], 1);
-      mbar_init(&sched_empty[i], 17);  // MMA thread + one lane of each softmax warp
+      mbar_init(&sched_empty[i], 9);  // MMA warp + one lane of each softmax warp
     }
     mbar_init(q_empty, 1);
     for (int s = 0; s < NST; ++s) {
@@ -222,11 +193,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         tc_commit_elect(&s_full[i]);
       };
-      auto issue_pv = [&](int i, uint32_t stage, uint32_t accum) {  // O_i (+)= P_i V, 8 MMAs of 16 kv rows
+      // O_i (+)= P_i V: 8 MMAs of 16 kv rows; the second four wait for the second half of P
+      auto issue_pv = [&](int i, uint32_t stage, uint32_t accum, uint32_t parity) {
         const uint64_t dv = dv0 + stage * (TILE >> 4);
 #pragma unroll
-        for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts_f16_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
+        for (int h = 0; h < 2; ++h) {
+          mbar_wait(&p_full[2 * i + h], parity, p.status, SITE_FWD_P_FULL);
+          tc_fence_after();
+#pragma unroll
+          for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
+            umma_ts_f16_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
+        }
       };
       auto advance = [&]() { if (++s == NST) { s = 0; ph ^= 1u; } };
 
@@ -256,31 +233,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
           mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
           if (j < n0) {
-            TRACE(2, 0x00);
-            mbar_wait(&p_full[0], pcnt[0]++ & 1u, p.status, SITE_FWD_P_FULL);
-            TRACE(2, 0x01);
-            tc_fence_after();
-            issue_pv(0, vs, j > 0);
-            TRACE(2, 0x02);
+            issue_pv(0, vs, j > 0, pcnt[0]++ & 1u);
             if (j == n0 - 1) tc_commit_elect(&o_full[0]);
             if (more0) {
               mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
               issue_s(0, ks);
-              TRACE(2, 0x03);
             }
           }
-          TRACE(2, 0x10);
-          mbar_wait(&p_full[1], pcnt[1]++ & 1u, p.status, SITE_FWD_P_FULL);
-          TRACE(2, 0x11);
-          tc_fence_after();
-          issue_pv(1, vs, j > 0);
-          TRACE(2, 0x12);
+          issue_pv(1, vs, j > 0, pcnt[1]++ & 1u);
           tc_commit_elect(&kv_empty[vs]);
           if (j == n1 - 1) tc_commit_elect(&o_full[1]);
           if (more1) {
             mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
             issue_s(1, ks);
-            TRACE(2, 0x13);
             tc_commit_elect(&kv_empty[ks]);
             if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
             advance();
@@ -291,18 +256,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    // 8 warps per tile: warps w and w+4 share TMEM lanes (rows) and split the columns in halves.
-    const int i = warp >> 3;                 // tile
-    const int half = (warp >> 2) & 1;        // column half of the scores / of the accumulator
+    // 4 warps per tile, one thread per query row.
+    const int i = warp >> 2;                 // tile
     const uint32_t quarter = warp & 3u;      // TMEM lanes [32*quarter, +32)
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const float scale = p.scale_log2;
-    float* x_mine = xchg + (i * 2 + half) * BLK + row_in_tile;        // + buffer * 512
-    float* x_other = xchg + (i * 2 + (half ^ 1)) * BLK + row_in_tile;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.o) & 15) == 0) && ((p.o_sn & 7) == 0) && ((p.o_sh & 7) == 0) &&
                         ((p.o_sz & 7) == 0);
-    uint32_t scnt = 0;  // blocks of this tile seen so far, across items (parity of s_full, exchange buffer)
+    uint32_t scnt = 0;  // blocks of this tile seen so far, across items (parity of s_full)
 
     for (uint32_t n = 0;; ++n) {
       const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
@@ -318,65 +280,63 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int qb = it.qb;
       const int row = qb * 256 + i * BLK + row_in_tile;  // query index
       const int nb = i ? it.n1 : it.n0;
-      float m_ref = -INFINITY, l = 0.f;  // l: this thread's half of the row sum
+      float m_ref = -INFINITY, l = 0.f;
 
       for (int j = 0; j < nb; ++j, ++scnt) {
-        if ((warp & 7) == 0 && lane == 0) TRACE(i, 0);
         mbar_wait(&s_full[i], scnt & 1u, p.status, SITE_FWD_S_FULL);
-        if ((warp & 7) == 0 && lane == 0) TRACE(i, 1);
         tc_fence_after();
-        uint32_t r[HC];
+        const int col0 = j * BLK;
+        const bool need_mask = (p.causal && col0 + BLK - 1 > qb * 256 + i * BLK) || (col0 + BLK > p.N);
+        // load 32 columns at a time; the row maximum of a chunk is taken while the next chunk loads
+        uint32_t r[BLK];
+        float mx4[16];
 #pragma unroll
-        for (int c = 0; c < HC; c += 32) tmem_ld32(tm_s[i] + lane_addr + half * HC + c, r + c);
-        tmem_ld_wait();
-        if ((warp & 7) == 0 && lane == 0) TRACE(i, 2);
-        const int col0 = j * BLK + half * HC;
-        const bool need_mask = (p.causal && j * BLK + BLK - 1 > qb * 256 + i * BLK) || (j * BLK + BLK > p.N);
-        if (need_mask) {
+        for (int u = 0; u < 16; ++u) mx4[u] = -INFINITY;
+        tmem_ld32(tm_s[i] + lane_addr, r);
+        tmem_ld_wait32(r);
 #pragma unroll
-          for (int c = 0; c < HC; ++c) {
-            const int col = col0 + c;
-            const bool ok = (col < p.N) && (!p.causal || col <= row);
-            if (!ok) r[c] = __float_as_uint(-INFINITY);
+        for (int c = 0; c < BLK; c += 32) {
+          if (c + 32 < BLK) tmem_ld32(tm_s[i] + lane_addr + c + 32, r + c + 32);
+          if (need_mask) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+              const int col = col0 + c + k;
+              const bool ok = (col < p.N) && (!p.causal || col <= row);
+              if (!ok) r[c + k] = __float_as_uint(-INFINITY);
+            }
           }
-        }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < HC; c += 8) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            mx4[u] = max3(mx4[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
+          for (int u = 0; u < 16; ++u)
+            mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1])));
+          if (c + 32 < BLK) tmem_ld_wait32(r + c + 32);
         }
-        float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        // combine with the other half of the row (double-buffered by block parity)
-        x_mine[(scnt & 1u) * 512] = mx;
-        tile_sync(i);
-        mx = fmaxf(mx, x_other[(scnt & 1u) * 512]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(max3(mx4[u], mx4[u + 4], mx4[u + 8]), mx4[u + 12]);
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
         // mx is finite: every row sees at least one valid column in every block it visits
         const float m_new = fmaxf(m_ref, mx * scale);
-        // lazy rescale of the accumulator (both threads of a row take the same decision; the ld/st
-        // below are warp collectives, so the warp rescales if any of its rows has to)
+        // lazy rescale of the accumulator (the ld/st below are warp collectives, so the warp
+        // rescales if any of its rows has to)
         const bool grow = (m_new - m_ref) > kRescaleThreshold;  // true on the first block (m_ref = -inf)
         if (__any_sync(0xffffffffu, grow)) {
           const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
           if (grow) { m_ref = m_new; l *= alpha; }
           if (j > 0) {
 #pragma unroll 1
-            for (int c = 0; c < HD; c += 16) {
-              uint32_t o[16];
-              tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
+            for (int c = 0; c < D; c += 32) {
+              uint32_t o[32];
+              tmem_ld32(tm_o[i] + lane_addr + c, o);
               tmem_ld_wait();
 #pragma unroll
-              for (int k = 0; k < 16; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
-              tmem_st16(tm_o[i] + lane_addr + half * HD + c, o);
+              for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * alpha);
+              tmem_st32(tm_o[i] + lane_addr + c, o);
             }
           }
         }
-        if ((warp & 7) == 0 && lane == 0) TRACE(i, 3);
         const float neg_m = -m_ref;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < HC; c += 32) {
+        for (int c = 0; c < BLK; c += 32) {
           uint32_t wv[16];
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
@@ -385,54 +345,49 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             sum4[k & 3] += p0 + p1;
             wv[k] = pack2<BF16>(p0, p1);
           }
-          tmem_st16(tm_s[i] + lane_addr + ((half * HC + c) >> 1), wv);
+          tmem_st16(tm_s[i] + lane_addr + (c >> 1), wv);
+          if (c == 32 || c == 96) {  // a half of P is complete: its four P V MMAs may start
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_full[2 * i + (c >> 6)]);
+          }
         }
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-        if ((warp & 7) == 0 && lane == 0) TRACE(i, 4);
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&p_full[i]);
-        if ((warp & 7) == 0 && lane == 0) TRACE(i, 5);
       }
 
-      // epilogue: the row sum is the two halves' sums; O / l and M.  It overlaps the next item's
-      // Q / K loads and first S MMAs; the next item's first P V (which overwrites O) needs this
-      // tile's next P, i.e. comes after these reads in program order.
-      x_mine[1024] = l;
-      tile_sync(i);
-      l += x_other[1024];
+      // epilogue: O / l and M.  It overlaps the next item's Q / K loads and first S MMAs; the next
+      // item's first P V (which overwrites O) needs this tile's next P, i.e. comes after these
+      // reads in program order.
       mbar_wait(&o_full[i], n & 1u, p.status, SITE_FWD_O_FULL);
       tc_fence_after();
       const float inv_l = 1.f / l;
       const bool valid = row < p.N;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)it.z * p.o_sz + (long long)it.h * p.o_sh +
-                       (long long)row * p.o_sn + half * HD;
+                       (long long)row * p.o_sn;
 #pragma unroll 1
-      for (int c = 0; c < HD; c += 16) {
-        uint32_t o[16];
-        tmem_ld16(tm_o[i] + lane_addr + half * HD + c, o);
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(tm_o[i] + lane_addr + c, o);
         tmem_ld_wait();
         if (valid) {
-          uint32_t wv[8];
+          uint32_t wv[16];
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
+          for (int k = 0; k < 16; ++k)
             wv[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
           if (vec_ok) {
 #pragma unroll
-            for (int k = 0; k < 2; ++k)
+            for (int k = 0; k < 4; ++k)
               reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(wv[4 * k], wv[4 * k + 1], wv[4 * k + 2], wv[4 * k + 3]);
           } else {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
+            for (int k = 0; k < 16; ++k) {
               orow[c + 2 * k] = (uint16_t)(wv[k] & 0xFFFFu);
               orow[c + 2 * k + 1] = (uint16_t)(wv[k] >> 16);
             }
           }
         }
       }
-      if (valid && half == 0) p.m[(long long)it.zh * p.N + row] = m_ref + log2f(l);
-      // the other half must have read x_other[1024] before the next item's epilogue rewrites it:
-      // guaranteed by the tile_sync calls of the next item's blocks (every item has >= 1 block)
+      if (valid) p.m[(long long)it.zh * p.N + row] = m_ref + log2f(l);
     }
   }
 
@@ -463,12 +418,6 @@ int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, con
 }
 
 }  // namespace
-
-#ifdef FWD_TRACE
-extern "C" __attribute__((visibility("default"))) int b200_debug_fwd_trace(void* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, g_trace, sizeof(g_trace));
-}
-#endif
 
 // 4-D map over [Z, H, N, D] (D contiguous) with boxes of 64 columns x 128 rows
 bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
