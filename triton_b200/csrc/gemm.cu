@@ -284,11 +284,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     // One issuing thread per 128-row half of the tile (warp 1: rows 0-127, the last warp: rows
     // 128-255).  The halves have separate accumulators and share the B stage; while one thread
     // does its per-stage bookkeeping the other keeps the pipe fed (+3 % fp16, +4 % fp8 measured).
-    const int h = (warp == 1) ? 0 : 1;
-    if (lane == 0) {
+    const int h = (__shfl_sync(0xffffffffu, warp, 0) == 1) ? 0 : 1;  // warp-uniform for the compiler too
+    {
       // The issue loop is kept lean (the tensor pipe queues only about one MMA ahead of the
-      // issuing thread): a descriptor is a constant plus (address >> 4) in its low bits, and
-      // stage / phase are running counters.
+      // issuer): the warp stays converged and an elected lane issues, so the descriptor
+      // arithmetic is warp-uniform; a descriptor is a constant plus (address >> 4) in its low
+      // bits, and stage / phase are running counters.
       const uint64_t da0 = smem_desc_sw128(smem_u32(smem), p.ga.lbo, p.ga.sbo);
       const uint64_t db0 = smem_desc_sw128(smem_u32(smem) + A_BYTES, p.gb.lbo, p.gb.sbo);
       const uint32_t ka = p.ga.kstep_bytes >> 4, kb16 = p.gb.kstep_bytes >> 4;
@@ -310,15 +311,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           for (int k = 0; k < KBYTES / 32; ++k) {
             const uint64_t da = das + (h * ((128 * KBYTES) >> 4) + k * ka);  // rows [128h, 128h+128): 16 KiB apart
             if (fp8)
-              umma_ss<true>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
+              umma_ss_elect<true>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
             else
-              umma_ss<false>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
+              umma_ss_elect<false>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
             accum = 1;
           }
-          tc_commit(&empty[s]);
+          tc_commit_elect(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        tc_commit(&tmem_full[acc]);
+        tc_commit_elect(&tmem_full[acc]);
       }
     }
     __syncwarp();
