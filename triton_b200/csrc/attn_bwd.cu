@@ -185,7 +185,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
     __syncwarp();
   } else if (warp == MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    {  // the warp stays converged; an elected lane issues (descriptor arithmetic stays warp-uniform)
       constexpr int FMT = BF16 ? 1 : 0;
       constexpr uint32_t IDESC_T = make_idesc(FMT, FMT, 0, 0, 128, BLK);  // R (K-major) x U (K-major)
       constexpr uint32_t IDESC_ACC = make_idesc(FMT, FMT, 0, 1, 128, D);  // P/dS (TMEM) x U (N-major)
@@ -197,13 +197,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * ((BLK * 128) >> 4) + (kk & 3) * 2;
-          umma_ss<false>(tm, dr + off, du + off, IDESC_T, kk != 0);
+          umma_ss_elect<false>(tm, dr + off, du + off, IDESC_T, kk != 0);
         }
       };
       auto issue_acc = [&](uint32_t tm_acc, uint32_t tm_opnd, uint64_t dun, uint32_t accum) {  // acc (+)= X U, 8 MMAs
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts_f16(tm_acc, tm_opnd + kk * 8, dun + kk * ((16 * 128) >> 4), IDESC_ACC, (accum | kk) != 0);
+          umma_ts_f16_elect(tm_acc, tm_opnd + kk * 8, dun + kk * ((16 * 128) >> 4), IDESC_ACC, (accum | kk) != 0);
       };
 
       uint32_t s = 0, ph = 0;  // ring position
@@ -212,7 +212,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
         mbar_wait(&sched_full[slot], sph, p.status, SITE_BWD_SCHED);
         const int w = sched_item[slot];
-        mbar_arrive(&sched_empty[slot]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sched_empty[slot]);
         if (w >= p.total_items) break;
         const BwdItem<DQ> item(p, w);
         const int steps = item.t_hi - item.t_lo;  // >= 1
@@ -220,10 +221,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         mbar_wait(r_full, n & 1u, p.status, SITE_BWD_KV);
         mbar_wait(&full[s], ph, p.status, SITE_BWD_LOAD_FULL);
         issue_t(tm_t1, dr0, du0 + s * (STAGE >> 4));
-        tc_commit(t1_full);
+        tc_commit_elect(t1_full);
         issue_t(tm_t2, dr0 + (TILE >> 4), du0 + s * (STAGE >> 4) + (TILE >> 4));
-        tc_commit(t2_full);
-        if (steps == 1) tc_commit(r_empty);
+        tc_commit_elect(t2_full);
+        if (steps == 1) tc_commit_elect(r_empty);
         for (int it = 0; it < steps; ++it, ++cnt) {
           const uint32_t cs = s;
           uint32_t ns = s + 1, nph = ph;
@@ -239,25 +240,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
             mbar_wait(&full[ns], nph, p.status, SITE_BWD_LOAD_FULL);
             if (!DQ) {  // T1 of the next step may start as soon as P was consumed (in-order pipe)
               issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
-              tc_commit(t1_full);
+              tc_commit_elect(t1_full);
             }
           }
           mbar_wait(ds_full, cnt & 1u, p.status, SITE_BWD_DS_FULL);
           tc_fence_after();
           issue_acc(tm_a, tm_t2, dun1, it > 0);  // dK += dS^T Q   /   dQ += dS K
-          tc_commit(&empty[cs]);
+          tc_commit_elect(&empty[cs]);
           if (more) {
             if (DQ) {  // no MMA consumes P here: T1 is free once the compute warps have read it (ds_full)
               issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
-              tc_commit(t1_full);
+              tc_commit_elect(t1_full);
             }
             issue_t(tm_t2, dr0 + (TILE >> 4), du0 + ns * (STAGE >> 4) + (TILE >> 4));
-            tc_commit(t2_full);
-            if (it + 2 == steps) tc_commit(r_empty);  // those were the item's last reads of R1, R2
+            tc_commit_elect(t2_full);
+            if (it + 2 == steps) tc_commit_elect(r_empty);  // those were the item's last reads of R1, R2
           }
           s = ns; ph = nph;
         }
-        tc_commit(acc_full);
+        tc_commit_elect(acc_full);
       }
     }
     __syncwarp();

@@ -440,7 +440,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {  // the leader CTA's warp issues for the pair: converged, one elected lane
       const uint64_t da0 = smem_desc_sw128(smem_u32(smem), p.ga.lbo, p.ga.sbo);
       const uint64_t db0 = smem_desc_sw128(smem_u32(smem) + A_BYTES, p.gb.lbo, p.gb.sbo);
       const uint32_t ka = p.ga.kstep_bytes >> 4, kb16 = p.gb.kstep_bytes >> 4;
@@ -462,16 +462,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int j = 0; j < NB; ++j) {
               const uint64_t db = dbs + (j * ((HALF_N * KBYTES) >> 4) + k * kb16);
               if (fp8)
-                umma_ss_pair<true>(d_tmem + j * 256, das + k * ka, db, idesc, accum);
+                umma_ss_pair_elect<true>(d_tmem + j * 256, das + k * ka, db, idesc, accum);
               else
-                umma_ss_pair<false>(d_tmem + j * 256, das + k * ka, db, idesc, accum);
+                umma_ss_pair_elect<false>(d_tmem + j * 256, das + k * ka, db, idesc, accum);
             }
             accum = 1;
           }
-          tc_commit_pair(&empty[s]);
+          tc_commit_pair_elect(&empty[s]);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        tc_commit_pair(&tmem_full[acc]);
+        tc_commit_pair_elect(&tmem_full[acc]);
       }
     }
     __syncwarp();
