@@ -359,15 +359,15 @@ def run_ours(args, rank, local_rank, world):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemm_kernel<256,256,3> launch on this workload
-# (877.9 MB + 119.6 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md); algorithmic: 402.7 MB
-TRAFFIC_BYTES_PER_LAUNCH = 997_483_008
+# (877.3 MB + 119.7 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md); algorithmic: 402.7 MB
+TRAFFIC_BYTES_PER_LAUNCH = 997_027_584
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the short timings of configs 1, 3, 4, 5")
     ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5"],

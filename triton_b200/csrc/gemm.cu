@@ -681,9 +681,10 @@ int gemm_plan_splits(DeviceCtx* ctx, int M, int N, int K, int in_dtype) {
   const int num_k = (K + bk_elems - 1) / bk_elems;
   // skinny problems always end up on the 128 x 64 tile (most tiles)
   const long long tiles = (long long)((M + 127) / 128) * ((N + 63) / 64);
-  if (tiles * 2 > ctx->sm_count || num_k < 8) return 1;
+  // a second kernel and the workspace round trip cost a few microseconds: only long K loops pay
+  if (tiles * 2 > ctx->sm_count || num_k < 32) return 1;
   long long s = ctx->sm_count / tiles;
-  if (s > num_k / 4) s = num_k / 4;
+  if (s > num_k / 8) s = num_k / 8;
   if (s > 16) s = 16;
   return s < 1 ? 1 : (int)s;
 }
