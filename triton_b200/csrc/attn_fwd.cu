@@ -47,6 +47,7 @@ struct FwdParams {
   int num_qb;        // 256-row query blocks per head
   int total_items;   // num_qb * Z * H
   int* sched_counter;  // work counter of this launch (zeroed before the launch)
+  int o_tma;           // O is written through shared-memory staging and TMA stores
   unsigned* status;
 };
 
@@ -55,7 +56,8 @@ struct FwdCfg {
   static constexpr int TILE_BYTES = BLK * D * 2;               // one Q tile or one K / V block
   static constexpr int KV_STAGES = (D == 128) ? 4 : 8;
   // tiles + barriers + TMEM slot + scheduler slots + alignment slack
-  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + (2 * KV_STAGES + 18) * 8 + 32 + 1024;
+  static constexpr int STG_BYTES = 32 * 128;  // epilogue staging of one softmax warp: 32 rows x 64 columns
+  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + 8 * STG_BYTES + (2 * KV_STAGES + 18) * 8 + 32 + 1024;
 };
 
 template <int D>
@@ -85,7 +87,8 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int w) {
 template <int D, bool BF16>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o_map,
+                const FwdParams p) {
   using Cfg = FwdCfg<D>;
   constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES;
   constexpr int MMA_WARP = 8, TMA_WARP = 9;
@@ -95,7 +98,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint8_t* smem = smem_raw + pad;
   uint8_t* sq = smem;                // Q tiles 0, 1
   uint8_t* skv = smem + 2 * TILE;    // ring
-  uint64_t* bars = reinterpret_cast<uint64_t*>(skv + NST * TILE);
+  uint8_t* sstage = skv + NST * TILE;  // 8 x 4 KiB, 128-byte swizzled
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sstage + 8 * Cfg::STG_BYTES);
   uint64_t* q_full = bars;             // [2]
   uint64_t* kv_full = bars + 2;        // [NST]
   uint64_t* kv_empty = kv_full + NST;  // [NST]
@@ -129,6 +133,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
+    tma_prefetch_desc(&tm_o_map);
   }
   if (warp == MMA_WARP) {
     tmem_alloc(tmem_slot, 512);
@@ -364,31 +369,64 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool valid = row < p.N;
       uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + (long long)it.z * p.o_sz + (long long)it.h * p.o_sh +
                        (long long)row * p.o_sn;
+      if (p.o_tma) {
+        // 64 columns at a time: scaled, packed, written to this warp's swizzled staging buffer and
+        // stored by TMA (full 128-byte lines; rows past N are clipped by the hardware).  A warp-wide
+        // store of one row per lane touches 32 lines per instruction and made this epilogue cost
+        // 5200 clk per item at D = 128.
+        uint8_t* stg = sstage + warp * Cfg::STG_BYTES;
+        const int warp_row0 = qb * 256 + i * BLK + quarter * 32;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        uint32_t o[32];
-        tmem_ld32(tm_o[i] + lane_addr + c, o);
-        tmem_ld_wait();
-        if (valid) {
-          uint32_t wv[16];
+        for (int c = 0; c < D; c += 64) {
+          uint32_t o[64];
+          tmem_ld32(tm_o[i] + lane_addr + c, o);
+          tmem_ld32(tm_o[i] + lane_addr + c + 32, o + 32);
+          tmem_ld_wait();
+          if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging buffer
+          __syncwarp();
 #pragma unroll
-          for (int k = 0; k < 16; ++k)
-            wv[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
-          if (vec_ok) {
+          for (int ch = 0; ch < 8; ++ch) {
+            uint32_t wv[4];
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(wv[4 * k], wv[4 * k + 1], wv[4 * k + 2], wv[4 * k + 3]);
-          } else {
+              wv[k] = pack2<BF16>(__uint_as_float(o[8 * ch + 2 * k]) * inv_l, __uint_as_float(o[8 * ch + 2 * k + 1]) * inv_l);
+            *reinterpret_cast<uint4*>(stg + sw128_offset(lane, ch)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && warp_row0 < p.N) {
+            tma_store_4d(&tm_o_map, stg, c, warp_row0, it.h, it.z);
+            tma_store_commit();
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(tm_o[i] + lane_addr + c, o);
+          tmem_ld_wait();
+          if (valid) {
+            uint32_t wv[16];
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-              orow[c + 2 * k] = (uint16_t)(wv[k] & 0xFFFFu);
-              orow[c + 2 * k + 1] = (uint16_t)(wv[k] >> 16);
+            for (int k = 0; k < 16; ++k)
+              wv[k] = pack2<BF16>(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
+            if (vec_ok) {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                reinterpret_cast<uint4*>(orow + c)[k] = make_uint4(wv[4 * k], wv[4 * k + 1], wv[4 * k + 2], wv[4 * k + 3]);
+            } else {
+#pragma unroll
+              for (int k = 0; k < 16; ++k) {
+                orow[c + 2 * k] = (uint16_t)(wv[k] & 0xFFFFu);
+                orow[c + 2 * k + 1] = (uint16_t)(wv[k] >> 16);
+              }
             }
           }
         }
       }
       if (valid) p.m[(long long)it.zh * p.N + row] = m_ref + log2f(l);
     }
+    if (p.o_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
   }
 
   if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
@@ -402,7 +440,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
 template <int D, bool BF16>
 int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, const CUtensorMap& tk,
-                 const CUtensorMap& tv, const FwdParams& p) {
+                 const CUtensorMap& tv, const CUtensorMap& to, const FwdParams& p) {
   static bool attr_done[64] = {};
   constexpr size_t smem = FwdCfg<D>::SMEM;
   if (!attr_done[ctx->device]) {
@@ -411,7 +449,7 @@ int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, con
     attr_done[ctx->device] = true;
   }
   const int grid = p.total_items < ctx->sm_count ? p.total_items : ctx->sm_count;
-  attn_fwd_kernel<D, BF16><<<grid, FWD_THREADS, smem, stream>>>(tq, tk, tv, p);
+  attn_fwd_kernel<D, BF16><<<grid, FWD_THREADS, smem, stream>>>(tq, tk, tv, to, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn fwd launch: %s", cudaGetErrorString(e));
   return B200_OK;
@@ -435,7 +473,11 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
   if (!encode_qkv_map(&tq, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], BLK)) return B200_ERR_UNSUPPORTED;
   if (!encode_qkv_map(&tk, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], BLK)) return B200_ERR_UNSUPPORTED;
   if (!encode_qkv_map(&tv, dtype, v, Z, H, N, D, sv[0], sv[1], sv[2], BLK)) return B200_ERR_UNSUPPORTED;
+  CUtensorMap to;
   FwdParams p{};
+  // O through TMA stores (boxes of 32 rows x 64 columns) when its layout allows, else direct stores
+  p.o_tma = encode_qkv_map(&to, dtype, o, Z, H, N, D, so[0], so[1], so[2], 32) ? 1 : 0;
+  if (!p.o_tma) to = tq;
   p.o = o; p.m = m;
   p.o_sz = so[0]; p.o_sh = so[1]; p.o_sn = so[2];
   p.Z = Z; p.H = H; p.N = N; p.causal = causal;
@@ -446,8 +488,8 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
   p.sched_counter = next_sched_counter(ctx, stream);
   if (!p.sched_counter) return B200_ERR_CUDA;
   const bool bf16 = dtype == B200_BF16;
-  if (D == 128) return bf16 ? launch_fwd_t<128, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<128, false>(ctx, stream, tq, tk, tv, p);
-  if (D == 64) return bf16 ? launch_fwd_t<64, true>(ctx, stream, tq, tk, tv, p) : launch_fwd_t<64, false>(ctx, stream, tq, tk, tv, p);
+  if (D == 128) return bf16 ? launch_fwd_t<128, true>(ctx, stream, tq, tk, tv, to, p) : launch_fwd_t<128, false>(ctx, stream, tq, tk, tv, to, p);
+  if (D == 64) return bf16 ? launch_fwd_t<64, true>(ctx, stream, tq, tk, tv, to, p) : launch_fwd_t<64, false>(ctx, stream, tq, tk, tv, to, p);
   return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
 }
 
