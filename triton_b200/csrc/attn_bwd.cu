@@ -45,6 +45,7 @@ struct BwdParams {
   float sm_scale;
   int total_items;     // (N / 128) * Z * H
   int* sched_counter;  // work counter of this launch (zeroed before the launch)
+  int out_tma;         // gradients are written through shared-memory staging and TMA stores
   unsigned* status;
 };
 
@@ -53,7 +54,8 @@ struct BwdCfg {
   static constexpr int TILE = BLK * D * 2;
   static constexpr int NST = (D == 128) ? 2 : 3;
   static constexpr int STAGE = 2 * TILE + 1024;  // U1, U2, column statistics (M, delta of the streamed rows)
-  static constexpr size_t SMEM = 2 * TILE + (size_t)NST * STAGE + (2 * NST + 14) * 8 + 32 + 1024;
+  static constexpr int STG_BYTES = 32 * 64;  // epilogue staging of one compute warp: 32 rows x 32 columns
+  static constexpr size_t SMEM = 2 * TILE + (size_t)NST * STAGE + 8 * STG_BYTES + (2 * NST + 14) * 8 + 32 + 1024;
 };
 
 template <int D>
@@ -93,6 +95,7 @@ template <int D, bool BF16, bool DQ>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant__ CUtensorMap tm_r2,
                 const __grid_constant__ CUtensorMap tm_u1, const __grid_constant__ CUtensorMap tm_u2,
+                const __grid_constant__ CUtensorMap tm_oa, const __grid_constant__ CUtensorMap tm_ob,
                 const BwdParams p) {
   using Cfg = BwdCfg<D>;
   constexpr int TILE = Cfg::TILE, NST = Cfg::NST, STAGE = Cfg::STAGE;
@@ -103,7 +106,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   uint8_t* smem = smem_raw + pad;
   uint8_t* sres = smem;                 // R1, R2
   uint8_t* sring = smem + 2 * TILE;     // stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sring + NST * STAGE);
+  uint8_t* sstage = sring + NST * STAGE;  // 8 x 2 KiB epilogue staging, rows of 64 bytes, not swizzled
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sstage + 8 * Cfg::STG_BYTES);
   uint64_t* r_full = bars;              // resident tiles of the item loaded
   uint64_t* r_empty = bars + 1;         // every T MMA of the item has read them
   uint64_t* full = bars + 2;            // [NST]
@@ -361,7 +365,37 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       // P / dS, i.e. comes after these reads in program order.
       mbar_wait(acc_full, n & 1u, p.status, SITE_BWD_ACC_FULL);
       tc_fence_after();
-      auto store_rows = [&](uint32_t tm_acc, void* out, long long sz, long long sh, long long sn, float mul) {
+      auto store_rows = [&](uint32_t tm_acc, const CUtensorMap* map, void* out, long long sz, long long sh,
+                            long long sn, float mul) {
+        if (p.out_tma) {
+          // 32 columns at a time through this warp's staging buffer and a TMA store (a warp-wide
+          // store of one row per lane touches 32 lines per instruction); rows past N are clipped
+          uint8_t* stg = sstage + warp * Cfg::STG_BYTES;
+          const int warp_row0 = blk * BLK + quarter * 32;
+#pragma unroll 1
+          for (int c = 0; c < HD; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(tm_acc + lane_addr + half * HD + c, o);
+            tmem_ld_wait();
+            if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging buffer
+            __syncwarp();
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              uint32_t wv[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                wv[k] = pack2<BF16>(__uint_as_float(o[8 * ch + 2 * k]) * mul, __uint_as_float(o[8 * ch + 2 * k + 1]) * mul);
+              *reinterpret_cast<uint4*>(stg + lane * 64 + ch * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && warp_row0 < p.N) {
+              tma_store_4d(map, stg, half * HD + c, warp_row0, item.h, item.z);
+              tma_store_commit();
+            }
+          }
+          return;
+        }
         uint16_t* orow = reinterpret_cast<uint16_t*>(out) + (long long)item.z * sz + (long long)item.h * sh +
                          (long long)grow * sn + half * HD;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((sn & 7) == 0) && ((sh & 7) == 0) && ((sz & 7) == 0);
@@ -386,9 +420,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
           }
         }
       };
-      store_rows(tm_a, p.out_a, p.oa_sz, p.oa_sh, p.oa_sn, p.sm_scale);  // dK or dQ carry sm_scale
-      if (!DQ) store_rows(tm_b, p.out_b, p.ob_sz, p.ob_sh, p.ob_sn, 1.0f);
+      store_rows(tm_a, &tm_oa, p.out_a, p.oa_sz, p.oa_sh, p.oa_sn, p.sm_scale);  // dK or dQ carry sm_scale
+      if (!DQ) store_rows(tm_b, &tm_ob, p.out_b, p.ob_sz, p.ob_sh, p.ob_sn, 1.0f);
     }
+    if (p.out_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
   }
 
   if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
@@ -442,7 +477,8 @@ attn_bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict
 
 template <int D, bool BF16, bool DQ>
 int launch_bwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& r1, const CUtensorMap& r2,
-                 const CUtensorMap& u1, const CUtensorMap& u2, const BwdParams& p) {
+                 const CUtensorMap& u1, const CUtensorMap& u2, const CUtensorMap& oa, const CUtensorMap& ob,
+                 const BwdParams& p) {
   static bool attr_done[64] = {};
   constexpr size_t smem = BwdCfg<D>::SMEM;
   if (!attr_done[ctx->device]) {
@@ -456,7 +492,7 @@ int launch_bwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& r1, con
   q.sched_counter = next_sched_counter(ctx, stream);
   if (!q.sched_counter) return B200_ERR_CUDA;
   const int grid = q.total_items < ctx->sm_count ? q.total_items : ctx->sm_count;
-  attn_bwd_kernel<D, BF16, DQ><<<grid, BWD_THREADS, smem, stream>>>(r1, r2, u1, u2, q);
+  attn_bwd_kernel<D, BF16, DQ><<<grid, BWD_THREADS, smem, stream>>>(r1, r2, u1, u2, oa, ob, q);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd launch: %s", cudaGetErrorString(e));
   return B200_OK;
@@ -475,15 +511,22 @@ int launch_bwd_all(DeviceCtx* ctx, cudaStream_t stream, const void* o, const voi
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd delta launch: %s", cudaGetErrorString(e));
   p.delta = delta;
+  // gradients through TMA stores (boxes of 32 rows x 32 columns) when all three layouts allow
+  CUtensorMap mdq, mdk, mdv;
+  const int dt = BF16 ? B200_BF16 : B200_F16;
+  p.out_tma = encode_rows_map(&mdq, dt, dq, p.Z, p.H, p.N, D, sdq[0], sdq[1], sdq[2], 32, 32, false) &&
+              encode_rows_map(&mdk, dt, dk, p.Z, p.H, p.N, D, sdk[0], sdk[1], sdk[2], 32, 32, false) &&
+              encode_rows_map(&mdv, dt, dv, p.Z, p.H, p.N, D, sdv[0], sdv[1], sdv[2], 32, 32, false);
+  if (!p.out_tma) mdq = mdk = mdv = tq;
   // dK, dV: resident (K, V), streamed (Q, dO)
   p.out_a = dk; p.oa_sz = sdk[0]; p.oa_sh = sdk[1]; p.oa_sn = sdk[2];
   p.out_b = dv; p.ob_sz = sdv[0]; p.ob_sh = sdv[1]; p.ob_sn = sdv[2];
-  int rc = launch_bwd_t<D, BF16, false>(ctx, stream, tk, tv, tq, tdo, p);
+  int rc = launch_bwd_t<D, BF16, false>(ctx, stream, tk, tv, tq, tdo, mdk, mdv, p);
   if (rc) return rc;
   // dQ: resident (Q, dO), streamed (K, V)
   p.out_a = dq; p.oa_sz = sdq[0]; p.oa_sh = sdq[1]; p.oa_sn = sdq[2];
   p.out_b = nullptr;
-  return launch_bwd_t<D, BF16, true>(ctx, stream, tq, tdo, tk, tv, p);
+  return launch_bwd_t<D, BF16, true>(ctx, stream, tq, tdo, tk, tv, mdq, mdq, p);
 }
 
 }  // namespace

@@ -457,13 +457,18 @@ int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, con
 
 }  // namespace
 
-// 4-D map over [Z, H, N, D] (D contiguous) with boxes of 64 columns x 128 rows
-bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
-                    int64_t sn, int box_rows) {
+bool encode_rows_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
+                     int64_t sn, int box_cols, int box_rows, bool swizzle128) {
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)N, (uint64_t)H, (uint64_t)Z};
   uint64_t strides[3] = {(uint64_t)sn * 2, (uint64_t)sh * 2, (uint64_t)sz * 2};
-  uint32_t box[4] = {64, (uint32_t)box_rows, 1, 1};
-  return encode_tmap(out, dtype, 4, base, dims, strides, box, true);
+  uint32_t box[4] = {(uint32_t)box_cols, (uint32_t)box_rows, 1, 1};
+  return encode_tmap(out, dtype, 4, base, dims, strides, box, swizzle128);
+}
+
+// the operand maps: boxes of 64 columns (128 bytes, swizzled) x box_rows rows
+bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
+                    int64_t sn, int box_rows) {
+  return encode_rows_map(out, dtype, base, Z, H, N, D, sz, sh, sn, 64, box_rows, true);
 }
 
 int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,

@@ -62,6 +62,9 @@ long long attn_bwd_scratch_capacity();
 float* attn_bwd_scratch(DeviceCtx* ctx);
 
 // 4-D tensor map over [Z, H, N, D] (D contiguous): boxes of 64 columns x box_rows rows, 128-byte swizzle
+// 4-D map over a [Z, H, N, D] tensor (D contiguous) with boxes of box_cols x box_rows elements
+bool encode_rows_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
+                     int64_t sn, int box_cols, int box_rows, bool swizzle128);
 bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
                     int64_t sn, int box_rows);
 
