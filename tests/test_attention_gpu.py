@@ -113,6 +113,41 @@ def test_strided_inputs_and_errors():
     status_ok()
 
 
+@pytest.mark.parametrize("pad", [4, 8])
+def test_outputs_tma_cannot_address(pad):
+    """O, dQ, dK, dV whose row pitch is not a multiple of 16 bytes (pad = 4 elements) cannot be
+    written by TMA stores: the kernels fall back to direct stores and give the same bits as the
+    TMA path; pad = 8 keeps the TMA path on a padded layout."""
+    from triton_b200.ops import _DT, _stream
+    Z, H, N, D = 1, 2, 256, 64
+    g = torch.Generator().manual_seed(11 + pad)
+    q, k, v, do = ((torch.randn(Z, H, N, D, generator=g) * 0.5).to(torch.bfloat16).to(DEV) for _ in range(4))
+    o_ref, M_ref = triton_b200.attention_forward(q, k, v, True, 0.125)
+    dq_ref, dk_ref, dv_ref = triton_b200.attention_backward(q, k, v, o_ref, M_ref, do, True, 0.125)
+
+    def padded():
+        buf = torch.zeros(Z, H, N, D + pad, dtype=torch.bfloat16, device=DEV)
+        return buf, buf[..., :D]
+    (ob, o), (dqb, dq), (dkb, dk), (dvb, dv) = padded(), padded(), padded(), padded()
+    M = torch.empty(Z, H, N, device=DEV, dtype=torch.float32)
+    delta = torch.empty_like(M)
+    L = _lib.lib()
+    _lib.check(L.b200_attention_fwd(_stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), M.data_ptr(),
+                                    Z, H, N, D, _lib.strides4(q), _lib.strides4(k), _lib.strides4(v), _lib.strides4(o),
+                                    0.125, 1, _DT[q.dtype]), "fwd")
+    assert torch.equal(o, o_ref) and torch.equal(M, M_ref)
+    assert float(ob[..., D:].abs().max()) == 0.0, "the padding was written"
+    _lib.check(L.b200_attention_bwd(_stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o_ref.data_ptr(),
+                                    do.data_ptr(), M.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(),
+                                    dv.data_ptr(), Z, H, N, D, _lib.strides4(q), _lib.strides4(k), _lib.strides4(v),
+                                    _lib.strides4(o_ref), _lib.strides4(do), _lib.strides4(dq), _lib.strides4(dk),
+                                    _lib.strides4(dv), 0.125, 1, _DT[q.dtype]), "bwd")
+    assert torch.equal(dq, dq_ref) and torch.equal(dk, dk_ref) and torch.equal(dv, dv_ref)
+    for b in (dqb, dkb, dvb):
+        assert float(b[..., D:].abs().max()) == 0.0, "the padding was written"
+    status_ok()
+
+
 def _check_heads(q, k, v, do, got, heads, causal, sm_scale, dtype, bwd):
     for (z, h) in heads:
         sl = (slice(z, z + 1), slice(h, h + 1))

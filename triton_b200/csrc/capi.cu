@@ -250,7 +250,7 @@ int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const
   if (!ctx) return B200_ERR_DEVICE;
   if (Z == 0 || H == 0 || N == 0) return B200_OK;
   if (!q || !k || !v || !o || !m) return fail(B200_ERR_ARG, "null pointer");
-  if ((long long)Z * H > 65535) return fail(B200_ERR_UNSUPPORTED, "Z*H exceeds 65535");
+  if ((long long)Z * H * ((N + 127) / 128) > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "too many work items");
   return launch_attn_fwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, m, Z, H, N, D, stride_q, stride_k,
                          stride_v, stride_o, sm_scale, causal, dtype);
 }
@@ -274,7 +274,7 @@ int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const
   if (!ctx) return B200_ERR_DEVICE;
   if (Z == 0 || H == 0 || N == 0) return B200_OK;
   if (!q || !k || !v || !o || !d_o || !m || !delta || !dq || !dk || !dv) return fail(B200_ERR_ARG, "null pointer");
-  if ((long long)Z * H > 65535) return fail(B200_ERR_UNSUPPORTED, "Z*H exceeds 65535");
+  if ((long long)Z * H * ((N + 127) / 128) > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "too many work items");
   if ((reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(delta) & 15))
     return fail(B200_ERR_UNSUPPORTED, "m and delta must be 16-byte aligned");
   return launch_attn_bwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, d_o, m, delta, dq, dk, dv, Z, H, N, D,
