@@ -290,3 +290,20 @@ def test_full_size_fp8_properties():
     want = (a8[rows].double().numpy() @ b8[:, cols].double().numpy()) * (sa * sb)
     g = got[rows][:, cols].float().cpu().numpy()
     assert np.linalg.norm(g - want) / np.linalg.norm(want) < 2e-2
+
+
+def test_host_matmul_pipeline_matches_device_matmul():
+    """HostMatmul (pinned host operands, row blocks pipelined over two copy streams) gives the
+    device-resident matmul's result, also for a row count that the blocks do not divide."""
+    M, N, K = 1000, 520, 264
+    g = torch.Generator().manual_seed(5)
+    a_h = torch.randn(M, K, generator=g).half().pin_memory()
+    b_h = torch.randn(K, N, generator=g).half().pin_memory()
+    c_h = torch.empty(M, N, dtype=torch.float16).pin_memory()
+    hm = triton_b200.HostMatmul(M, N, K, torch.float16, DEV, blocks=3)
+    for _ in range(2):  # the second run reuses the device buffers while nothing of the first is pending
+        hm.run(a_h, b_h, c_h, activation="leaky_relu")
+        torch.cuda.synchronize()
+        want = triton_b200.matmul(a_h.to(DEV), b_h.to(DEV), activation="leaky_relu")
+        np.testing.assert_allclose(f32(c_h), f32(want), rtol=1e-2, atol=1e-2)
+    status_ok()

@@ -84,6 +84,46 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
     return c
 
 
+class HostMatmul:
+    """C = A @ B for operands that live in (pinned) host memory: the call a host-side user of the
+    matmul makes.  B goes to the device once per call; A is sent in row blocks and every block's
+    product is copied back while the next block is on its way, so the two directions of the link
+    and the tensor cores overlap (the product of a block takes a fraction of its transfer time).
+    Device buffers and the two copy streams are kept by the object; `run` returns after enqueueing,
+    the caller's current stream waits for the last copy-out."""
+
+    def __init__(self, M, N, K, dtype=torch.float16, device="cuda", blocks=8):
+        self.M, self.N, self.K = M, N, K
+        self.rows = max(1, -(-M // max(1, blocks)))
+        self.dev = torch.device(device)
+        with torch.cuda.device(self.dev):
+            self.a = torch.empty(M, K, dtype=dtype, device=self.dev)
+            self.b = torch.empty(K, N, dtype=dtype, device=self.dev)
+            self.c = torch.empty(M, N, dtype=dtype, device=self.dev)
+            self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+
+    def run(self, a_h, b_h, c_h, activation=""):
+        assert a_h.shape == (self.M, self.K) and b_h.shape == (self.K, self.N) and c_h.shape == (self.M, self.N)
+        cur = torch.cuda.current_stream(self.dev)
+        self.s_in.wait_stream(cur)   # earlier work that still reads the device buffers
+        self.s_out.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            self.b.copy_(b_h, non_blocking=True)
+        for r0 in range(0, self.M, self.rows):
+            r1 = min(self.M, r0 + self.rows)
+            with torch.cuda.stream(self.s_in):
+                self.a[r0:r1].copy_(a_h[r0:r1], non_blocking=True)
+                arrived = self.s_in.record_event()
+            cur.wait_event(arrived)
+            matmul(self.a[r0:r1], self.b, activation, out=self.c[r0:r1], out_dtype=self.c.dtype)
+            done = cur.record_event()
+            self.s_out.wait_event(done)
+            with torch.cuda.stream(self.s_out):
+                c_h[r0:r1].copy_(self.c[r0:r1], non_blocking=True)
+        cur.wait_stream(self.s_out)
+        return c_h
+
+
 def quantize_e4m3(x):
     """Per-tensor amax scaling to the e4m3 range; returns (x8, scale) with x ~= x8 * scale.
     `scale` is a 1-element fp32 tensor on x's device (no host synchronisation)."""
