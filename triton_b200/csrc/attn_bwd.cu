@@ -314,13 +314,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         tmem_ld_wait();
         if (!DQ) asm volatile("bar.sync 1, 256;" ::: "memory");  // both halves hold their T1 columns in registers
 #pragma unroll
-        for (int c = 0; c < HC; ++c) {
-          const float mm = DQ ? m_row : sm[c];
-          float pv = ex2(fmaf(__uint_as_float(pr[c]), scale, -mm));
-          // dK/dV kernel: row = kv, column = q, keep q >= kv.   dQ kernel: row = q, column = kv, keep kv <= q.
-          const int cc = half * HC + c;
-          if (diag && (DQ ? (cc > r) : (cc < r))) pv = 0.f;
-          pr[c] = __float_as_uint(pv);
+        for (int c4 = 0; c4 < HC; c4 += 4) {
+          // column statistics: one 16-byte broadcast load for four columns
+          const float4 m4 = DQ ? make_float4(m_row, m_row, m_row, m_row) : *reinterpret_cast<const float4*>(sm + c4);
+          const float mq[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int c = c4 + u;
+            float pv = ex2(fmaf(__uint_as_float(pr[c]), scale, -mq[u]));
+            // dK/dV kernel: row = kv, column = q, keep q >= kv.   dQ kernel: row = q, column = kv, keep kv <= q.
+            const int cc = half * HC + c;
+            if (diag && (DQ ? (cc > r) : (cc < r))) pv = 0.f;
+            pr[c] = __float_as_uint(pv);
+          }
         }
         if (!DQ) {
 #pragma unroll
@@ -343,12 +349,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
           tmem_ld32(tm_t2 + lane_addr + half * HC + c, dp);
           tmem_ld_wait();
 #pragma unroll
-          for (int k = 0; k < 16; ++k) {
-            const float d0 = DQ ? d_row : sd[c + 2 * k];
-            const float d1 = DQ ? d_row : sd[c + 2 * k + 1];
-            const float ds0 = __uint_as_float(pr[c + 2 * k]) * (__uint_as_float(dp[2 * k]) - d0);
-            const float ds1 = __uint_as_float(pr[c + 2 * k + 1]) * (__uint_as_float(dp[2 * k + 1]) - d1);
-            dsw[(c >> 1) + k] = pack2<BF16>(ds0, ds1);
+          for (int k4 = 0; k4 < 32; k4 += 4) {
+            const float4 d4 = DQ ? make_float4(d_row, d_row, d_row, d_row) : *reinterpret_cast<const float4*>(sd + c + k4);
+            const float ds0 = __uint_as_float(pr[c + k4]) * (__uint_as_float(dp[k4]) - d4.x);
+            const float ds1 = __uint_as_float(pr[c + k4 + 1]) * (__uint_as_float(dp[k4 + 1]) - d4.y);
+            const float ds2 = __uint_as_float(pr[c + k4 + 2]) * (__uint_as_float(dp[k4 + 2]) - d4.z);
+            const float ds3 = __uint_as_float(pr[c + k4 + 3]) * (__uint_as_float(dp[k4 + 3]) - d4.w);
+            dsw[((c + k4) >> 1)] = pack2<BF16>(ds0, ds1);
+            dsw[((c + k4) >> 1) + 1] = pack2<BF16>(ds2, ds3);
           }
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");  // both halves have read all of T2
