@@ -33,6 +33,7 @@ typedef struct CUstream_st* b200_stream_t; /* a cudaStream_t / CUstream */
 
 enum b200_dtype { B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3 };
 enum b200_activation { B200_ACT_NONE = 0, B200_ACT_LEAKY_RELU = 1 };
+enum b200_bias { B200_BIAS_NONE = 0, B200_BIAS_MATRIX = 1, B200_BIAS_ROWS = 2, B200_BIAS_COLS = 3 };
 enum b200_error {
   B200_OK = 0,
   B200_ERR_ARG = 1,         /* shapes / dtypes / null pointers (the reference's Python asserts) */
@@ -80,6 +81,20 @@ B200_API int b200_matmul_splitk(b200_stream_t stream, const void* a, const void*
                                 int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
                                 int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
                                 const float* scale_a, const float* scale_b, int splits, float* workspace);
+
+/* Matmul with the reference's bias epilogues (python/test/unit/hopper/test_gemm.py:213-222, cases
+ * 'add-matrix', 'add-rows', 'add-cols' at :281): c = out_type(act(scale * a @ b)) + bias, the sum
+ * formed in the output type as the reference does (`z = z.to(out_dtype); z += bias`).  `bias` has
+ * the output type (F16, BF16 or F32) and is indexed bias[m * bias_stride_m + n * bias_stride_n];
+ * B200_BIAS_ROWS reads one value per output row (n ignored), B200_BIAS_COLS one per column
+ * (m ignored), B200_BIAS_NONE makes this b200_matmul_splitk.  out_dtype B200_E4M3 (8-bit output,
+ * python/tutorials/09-persistent-matmul.py: `c = accumulator.to(tl.float8e4nv)`, round to nearest
+ * even, saturating) is accepted here, by b200_matmul and by b200_matmul_splitk, without a bias. */
+B200_API int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
+                              int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
+                              int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
+                              const float* scale_a, const float* scale_b, const void* bias, int bias_mode,
+                              int64_t bias_stride_m, int64_t bias_stride_n, int splits, float* workspace);
 
 /* Flash-attention forward: O = softmax(Q K^T * sm_scale, causal mask optional) V, and per-row
  * statistics M[Z,H,N] (fp32) = base-2 log-sum-exp of the scores scaled by sm_scale * log2(e)

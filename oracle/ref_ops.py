@@ -64,10 +64,37 @@ def decode_e4m3(bits_u8):
     return E4M3[np.asarray(bits_u8, dtype=np.uint8)]
 
 
+def round_e4m3(x):
+    """fp32 -> e4m3fn (round to nearest even, saturating at +-448) -> fp32: what the reference's
+    `accumulator.to(tl.float8e4nv)` (python/tutorials/09-persistent-matmul.py:93-94, 208-209) lowers to on NVIDIA GPUs (cvt.rn.satfinite.e4m3x2.f32,
+    third_party/nvidia/lib/TritonNVIDIAGPUToLLVM/ElementwiseOpToLLVM.cpp:214-220).  Below 448 it is
+    the conversion torch implements for float8_e4m3fn, which pins it (tests/test_oracle.py)."""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.minimum(np.abs(x).astype(np.float64), 448.0)
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(np.where(a > 0, a, 1.0)))
+    e = np.maximum(e, -6.0)            # subnormals share the quantum of the smallest binade
+    q = np.exp2(e - 3.0)               # 3 mantissa bits
+    r = np.rint(a / q) * q             # rint: ties to even; a carry into the next binade is exact
+    out = np.copysign(r, x).astype(np.float32)
+    return np.where(np.isnan(x), np.float32(np.nan), out)
+
+
+ROUND["e4m3"] = round_e4m3
+
+
+def add_bias(c, bias, out):
+    """The reference's bias epilogues, python/test/unit/hopper/test_gemm.py:213-222: the tile is
+    already converted to the output type (`z = z.to(out_dtype)`) and `z += bias` rounds again in
+    that type.  `bias` broadcasts: [M, N] ('add-matrix'), [M, 1] ('add-rows'), [1, N] ('add-cols')."""
+    rnd = ROUND.get(out, lambda v: v)
+    return rnd(rnd(c) + np.asarray(bias, dtype=np.float32))
+
+
 # ----------------------------------------------------------------------------- matmul
 
 
-def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8):
+def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8, bias=None):
     """C = A @ B, tile by tile.
 
     Follows matmul_kernel, python/tutorials/03-matrix-multiplication.py:241-316:
@@ -104,6 +131,8 @@ def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8):
         m0, n0 = pid_m * BM, pid_n * BN
         mm, nn = min(BM, M - m0), min(BN, N - n0)
         c[m0:m0 + mm, n0:n0 + nn] = acc[:mm, :nn]
+    if bias is not None:
+        return add_bias(c, bias, out)
     return ROUND[out](c) if out in ROUND else c
 
 

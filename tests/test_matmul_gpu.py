@@ -307,3 +307,79 @@ def test_host_matmul_pipeline_matches_device_matmul():
         want = triton_b200.matmul(a_h.to(DEV), b_h.to(DEV), activation="leaky_relu")
         np.testing.assert_allclose(f32(c_h), f32(want), rtol=1e-2, atol=1e-2)
     status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("mode", ["matrix", "rows", "cols"])
+@pytest.mark.parametrize("shape", [(256, 512, 128), (200, 136, 72), (16, 4096, 4096)])
+def test_bias_epilogues(dtype, mode, shape):
+    """The reference's 'add-matrix' / 'add-rows' / 'add-cols' epilogues (test_gemm.py:213-222, 281)
+    on the tensor-core path (TMA-store and direct-store epilogues) and on the split-K path."""
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + 3 * N + K)
+    a = torch.randn(M, K, generator=g).half()
+    b = torch.randn(K, N, generator=g).half()
+    bshape = {"matrix": (M, N), "rows": (M, 1), "cols": (1, N)}[mode]
+    bias = (torch.randn(bshape, generator=g) * 4).to(dtype)
+    got = triton_b200.matmul(a.to(DEV), b.to(DEV), out_dtype=dtype, bias=bias.to(DEV))
+    status_ok()
+    out = {torch.float16: "fp16", torch.bfloat16: "bf16", torch.float32: "fp32"}[dtype]
+    want = R.matmul(f32(a), f32(b), out=out, bias=f32(bias))
+    # the product is rounded to the output type before the addition: one ulp of the product (not
+    # of the possibly much smaller sum) is the unit of disagreement
+    prod = np.abs(R.matmul(f32(a), f32(b), out="fp32"))
+    rel = 2e-2 if dtype == torch.bfloat16 else 1e-2  # two bf16 roundings: up to two ulps of 2^-8 .. 2^-7
+    assert (np.abs(f32(got) - want) <= 1e-2 + rel * (prod + np.abs(f32(bias)))).all()
+    if dtype != torch.float32 and K <= 128:
+        assert (f32(got) != want).mean() < 0.05  # same two roundings: almost all elements bit-identical
+    # a strided bias view (every second column of a wider buffer)
+    if mode == "matrix":
+        wide = torch.zeros(M, 2 * N, dtype=dtype)
+        wide[:, ::2] = bias
+        got2 = triton_b200.matmul(a.to(DEV), b.to(DEV), out_dtype=dtype, bias=wide.to(DEV)[:, ::2])
+        assert torch.equal(got2, got)
+
+
+def test_bias_on_the_plain_kernel_and_errors():
+    a = torch.randn(70, 13).half().to(DEV)   # K pitch of 26 bytes: TMA cannot address it
+    b = torch.randn(13, 9).half().to(DEV)
+    bias = torch.randn(1, 9).half().to(DEV)
+    got = triton_b200.matmul(a, b, bias=bias)
+    want = R.matmul(f32(a), f32(b), out="fp16", bias=f32(bias))
+    np.testing.assert_allclose(f32(got), want, rtol=1e-2, atol=2e-2)
+    with pytest.raises(AssertionError, match="bias shape"):
+        triton_b200.matmul(a, b, bias=torch.zeros(9, 1, dtype=torch.float16, device=DEV))
+    with pytest.raises(RuntimeError, match="e4m3"):
+        triton_b200.matmul(a, b, out_dtype=torch.float8_e4m3fn, bias=torch.zeros(1, 9, dtype=torch.float8_e4m3fn, device=DEV))
+    status_ok()
+
+
+@pytest.mark.parametrize("shape", [(256, 512, 256), (130, 200, 136), (64, 4096, 4096)])
+@pytest.mark.parametrize("in_dtype", [torch.float16, torch.float8_e4m3fn])
+def test_e4m3_output(shape, in_dtype):
+    """8-bit output (python/tutorials/09-persistent-matmul.py:93-94): round to nearest even,
+    saturating; checked against the oracle's rounding of the exact fp32 accumulator."""
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    a = torch.randn(M, K, generator=g)
+    b = torch.randn(K, N, generator=g)
+    if in_dtype == torch.float8_e4m3fn:
+        a8, sa = triton_b200.quantize_e4m3(a.to(DEV))
+        b8, sb = triton_b200.quantize_e4m3(b.to(DEV))
+        got = triton_b200.matmul(a8, b8, scale_a=sa, scale_b=sb, out_dtype=torch.float8_e4m3fn)
+        acc = (a8.float() @ b8.float()) * (sa * sb)
+    else:
+        ah, bh = a.half().to(DEV), b.half().to(DEV)
+        got = triton_b200.matmul(ah, bh, out_dtype=torch.float8_e4m3fn)
+        acc = ah.float() @ bh.float()
+    status_ok()
+    assert got.dtype == torch.float8_e4m3fn
+    want = R.round_e4m3(f32(acc))
+    gotf = f32(got)
+    assert not np.isnan(gotf).any(), "saturating conversion never produces NaN"
+    assert np.abs(gotf).max() <= 448
+    # fp32 summation order differs from torch's matmul: values next to a rounding boundary may land
+    # on the neighbouring e4m3 value (1/8 relative step); everything else is identical
+    close = np.abs(gotf - want) <= 0.13 * np.maximum(np.abs(want), 2.0 ** -6)
+    assert close.all()
+    assert (gotf != want).mean() < 0.02

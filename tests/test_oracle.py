@@ -139,3 +139,38 @@ def test_noncausal_bwd_full_against_torch():
     ro, rdq, rdk, rdv = _torch_reference(q, k, v, do, False, c["sm_scale"])
     for got, want in ((o, ro), (dq, rdq), (dk, rdk), (dv, rdv)):
         np.testing.assert_allclose(got, want, atol=1e-2, rtol=1e-2)
+
+
+def test_round_e4m3_matches_torch_and_saturates():
+    """The oracle's fp32 -> e4m3 rounding is torch's float8_e4m3fn conversion below the largest
+    finite value and saturates above it (the reference's cvt.rn.satfinite lowering)."""
+    import torch
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(50000).astype(np.float32) * s for s in (1e-3, 0.02, 1.0, 30.0, 200.0)] +
+                       [np.array([0.0, -0.0, 448.0, -448.0, 447.9, 2.0 ** -9, 2.0 ** -10, 1.5 * 2.0 ** -9,
+                                  2.5 * 2.0 ** -9, 0.0029296875], dtype=np.float32)])
+    x = x[np.abs(x) <= 448]
+    want = torch.tensor(x).to(torch.float8_e4m3fn).float().numpy()
+    got = R.round_e4m3(x)
+    assert np.array_equal(got, want)
+    assert np.array_equal(np.signbit(got), np.signbit(want))
+    np.testing.assert_array_equal(R.round_e4m3(np.array([500.0, -1e9, 460.0, 464.1], dtype=np.float32)),
+                                  np.array([448.0, -448.0, 448.0, 448.0], dtype=np.float32))
+    # every e4m3 value is a fixed point
+    finite = R.E4M3[~np.isnan(R.E4M3)]
+    assert np.array_equal(R.round_e4m3(finite), finite)
+
+
+def test_bias_epilogue_rounds_twice_in_the_output_type():
+    """`z = z.to(out_dtype); z += bias` (test_gemm.py:213-222): the oracle's add_bias rounds the
+    product, adds, rounds again; checked against torch arithmetic in the output type."""
+    import torch
+    rng = np.random.default_rng(1)
+    a = R.round_fp16(rng.standard_normal((64, 96)).astype(np.float32))
+    b = R.round_fp16(rng.standard_normal((96, 80)).astype(np.float32))
+    for shape in ((64, 80), (64, 1), (1, 80)):
+        bias = R.round_fp16(rng.standard_normal(shape).astype(np.float32))
+        got = R.matmul(a, b, out="fp16", bias=bias)
+        z = torch.tensor(R.matmul(a, b, out="fp32")).half()  # the oracle's own fp32 accumulator
+        z = z + torch.tensor(bias).half()
+        np.testing.assert_array_equal(got, z.float().numpy())

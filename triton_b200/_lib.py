@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_PKG, "libtriton_b200.so")
 
 F16, BF16, E4M3, F32 = 0, 1, 2, 3
 ACT_NONE, ACT_LEAKY_RELU = 0, 1
+BIAS_NONE, BIAS_MATRIX, BIAS_ROWS, BIAS_COLS = 0, 1, 2, 3
 
 _i, _i64, _p, _f = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float
 _s4 = ctypes.c_int64 * 4  # an element-stride quadruple {z, h, n, d}
@@ -24,6 +25,8 @@ SIGNATURES = {
     "b200_matmul": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p],
     "b200_matmul_plan": [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_size_t)],
     "b200_matmul_splitk": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p, _i, _p],
+    "b200_matmul_bias": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p,
+                         _p, _i, _i64, _i64, _i, _p],
     "b200_attention_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
     "b200_attention_bwd": [_p] + [_p] * 10 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
     "b200_attention_bwd_noalloc": [_p] + [_p] * 9 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],

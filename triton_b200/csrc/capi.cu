@@ -210,20 +210,35 @@ int b200_matmul_splitk(b200_stream_t stream, const void* a, const void* b, void*
                        int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn, int64_t stride_cm,
                        int64_t stride_cn, int in_dtype, int out_dtype, int activation, const float* scale_a,
                        const float* scale_b, int splits, float* workspace) {
+  return b200_matmul_bias(stream, a, b, c, M, N, K, stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn,
+                          in_dtype, out_dtype, activation, scale_a, scale_b, nullptr, B200_BIAS_NONE, 0, 0, splits,
+                          workspace);
+}
+
+int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
+                     int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn, int64_t stride_cm,
+                     int64_t stride_cn, int in_dtype, int out_dtype, int activation, const float* scale_a,
+                     const float* scale_b, const void* bias, int bias_mode, int64_t bias_stride_m,
+                     int64_t bias_stride_n, int splits, float* workspace) {
+  if (bias_mode < B200_BIAS_NONE || bias_mode > B200_BIAS_COLS) return fail(B200_ERR_ARG, "bad bias mode");
+  if (bias_mode != B200_BIAS_NONE && !bias) return fail(B200_ERR_ARG, "null bias pointer");
+  if (bias_mode != B200_BIAS_NONE && out_dtype == B200_E4M3)
+    return fail(B200_ERR_ARG, "no bias epilogue with an e4m3 output");
   if (splits < 1 || splits > 64) return fail(B200_ERR_ARG, "splits must be in [1, 64]");
   if (splits > 1 && (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15)))
     return fail(B200_ERR_ARG, "split-K needs a 16-byte aligned workspace of splits * M * N floats");
   if (M < 0 || N < 0 || K < 0) return fail(B200_ERR_ARG, "negative dimension");
   if (in_dtype != B200_F16 && in_dtype != B200_BF16 && in_dtype != B200_E4M3)
     return fail(B200_ERR_ARG, "in_dtype must be F16, BF16 or E4M3");
-  if (out_dtype != B200_F16 && out_dtype != B200_BF16 && out_dtype != B200_F32)
-    return fail(B200_ERR_ARG, "out_dtype must be F16, BF16 or F32");
+  if (out_dtype != B200_F16 && out_dtype != B200_BF16 && out_dtype != B200_F32 && out_dtype != B200_E4M3)
+    return fail(B200_ERR_ARG, "out_dtype must be F16, BF16, F32 or E4M3");
   if (activation != B200_ACT_NONE && activation != B200_ACT_LEAKY_RELU) return fail(B200_ERR_ARG, "bad activation");
   DeviceCtx* ctx = current_ctx();
   if (!ctx) return B200_ERR_DEVICE;
   if (M == 0 || N == 0) return B200_OK;
   if (!c || (K > 0 && (!a || !b))) return fail(B200_ERR_ARG, "null pointer");
   if (stride_cn != 1 && N != 1) return fail(B200_ERR_UNSUPPORTED, "C must have stride_cn == 1");
+  if (K == 0 && bias_mode != B200_BIAS_NONE) return fail(B200_ERR_UNSUPPORTED, "bias epilogue with K == 0");
   if (K == 0) {
     // an empty sum: the reference's K loop does not run and the zero accumulator is stored
     const int es = dtype_bytes(out_dtype);
@@ -233,7 +248,8 @@ int b200_matmul_splitk(b200_stream_t stream, const void* a, const void* b, void*
     return B200_OK;
   }
   return launch_gemm(ctx, reinterpret_cast<cudaStream_t>(stream), a, b, c, M, N, K, stride_am, stride_ak, stride_bk,
-                     stride_bn, stride_cm, in_dtype, out_dtype, activation, scale_a, scale_b, splits, workspace);
+                     stride_bn, stride_cm, in_dtype, out_dtype, activation, scale_a, scale_b, bias, bias_mode, bias_stride_m,
+                     bias_stride_n, splits, workspace);
 }
 
 int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m, int Z,

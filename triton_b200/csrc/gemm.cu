@@ -31,6 +31,8 @@
 //               (`tmem_empty[acc]`)
 // Out-of-range rows / columns / K are zero-filled by TMA, which is the masked load of the
 // reference (03-...py:297-298); stores are bounds-checked.
+#include <cuda_fp8.h>
+
 #include <cstdlib>
 
 #include "common.cuh"
@@ -65,6 +67,9 @@ struct GemmParams {
   int splits;   // split-K: work items = tiles x splits, each writes an fp32 partial tile to `ws`
   int kb_per_split;
   float* ws;    // [splits][M][N] fp32 partial sums (caller's workspace), reduced by splitk_reduce_kernel
+  const void* bias;  // epilogue addend of the output type: [M,N] matrix, one value per row, or one per column
+  int bias_mode;     // b200_bias
+  long long bias_sm, bias_sn;
   uint32_t idesc;
   OperandGeom ga, gb;
 };
@@ -82,13 +87,64 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   return (act == B200_ACT_LEAKY_RELU) ? (v >= 0.f ? v : 0.01f * v) : v;
 }
 
+// value -> nearest value of the output type, as fp32
+__device__ __forceinline__ float round_out(float v, int out_dtype) {
+  if (out_dtype == B200_F16) return __half2float(__float2half_rn(v));
+  if (out_dtype == B200_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  return v;
+}
+// The reference's bias epilogues (python/test/unit/hopper/test_gemm.py:213-222) convert the
+// accumulator to the output type first and add the bias in that type: round, add, round again
+// (the second rounding is the caller's final conversion).
+__device__ __forceinline__ float add_bias(const GemmParams& p, float v, int row, int col) {
+  if (row >= p.M || col >= p.N) return v;  // lanes past the edge compute values that are never stored
+  long long i = 0;
+  if (p.bias_mode != B200_BIAS_COLS) i += (long long)row * p.bias_sm;
+  if (p.bias_mode != B200_BIAS_ROWS) i += (long long)col * p.bias_sn;
+  float b;
+  if (p.out_dtype == B200_F16) b = __half2float(reinterpret_cast<const __half*>(p.bias)[i]);
+  else if (p.out_dtype == B200_BF16) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[i]);
+  else b = reinterpret_cast<const float*>(p.bias)[i];
+  return round_out(v, p.out_dtype) + b;
+}
+// accumulator -> scale, activation, bias: the fp32 value that is rounded once to the output type.
+// BIAS is a template parameter so that the code without a bias is exactly the plain epilogue.
+template <bool BIAS>
+__device__ __forceinline__ float finish(const GemmParams& p, float acc, float scale, int row, int col) {
+  const float v = apply_act(acc * scale, p.activation);
+  if constexpr (BIAS) return add_bias(p, v, row, col);
+  else return v;
+}
+// four fp32 -> four e4m3 bytes (round to nearest even, saturating at +-448 like the reference's
+// cvt.rn.satfinite lowering of `.to(tl.float8e4nv)`)
+__device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
 // one thread's 32 consecutive accumulator columns -> scale, activation, one rounding, store
+// EXT: the instantiation also knows the 8-bit output (kept out of the plain kernels, whose register
+// allocation and speed it would otherwise change)
+template <bool BIAS, bool EXT>
 __device__ __forceinline__ void store_chunk32(const GemmParams& p, int row, int col, const uint32_t* r, float scale,
                                               bool vec_ok) {
   float v[32];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) v[j] = apply_act(__uint_as_float(r[j]) * scale, p.activation);
-  if (p.out_dtype == B200_F32) {
+  for (int j = 0; j < 32; ++j) v[j] = finish<BIAS>(p, __uint_as_float(r[j]), scale, row, col + j);
+  if (EXT && p.out_dtype == B200_E4M3) {
+    uint8_t* dst = reinterpret_cast<uint8_t*>(p.c) + (long long)row * p.ldc + col;
+    uint32_t w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = pack4_e4m3(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    if (vec_ok && col + 32 <= p.N) {
+      reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+      reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+      for (int j = 0; j < 32; ++j)
+        if (col + j < p.N) dst[j] = (uint8_t)(w[j >> 2] >> (8 * (j & 3)));
+    }
+  } else if (p.out_dtype == B200_F32) {
     float* dst = reinterpret_cast<float*>(p.c) + (long long)row * p.ldc + col;
     if (vec_ok && col + 32 <= p.N) {
 #pragma unroll
@@ -134,9 +190,10 @@ constexpr int pair_staging_warps(int stages, int nb) {
 // a warp-wide store of one row each would touch 32 separate lines per instruction and made the
 // epilogue cost 9 % of a 256 x 256 tile.  Other outputs (fp32, or a C that TMA cannot address) take
 // direct stores.
-__device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tma_c, uint8_t* stg,
-                                                  uint32_t taddr, int ncols, int row0, int col0, int lane,
-                                                  float scale, bool vec_ok) {
+template <bool BIAS, bool EXT>
+__device__ __forceinline__ void drain_accumulator_t(const GemmParams& p, const CUtensorMap* tma_c, uint8_t* stg,
+                                                    uint32_t taddr, int ncols, int row0, int col0, int lane,
+                                                    float scale, bool vec_ok) {
   if (p.c_tma) {
 #pragma unroll 1
     for (int c0 = 0; c0 < ncols; c0 += 64) {
@@ -151,8 +208,8 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
         uint32_t w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float v0 = apply_act(__uint_as_float(r[8 * c + 2 * j]) * scale, p.activation);
-          const float v1 = apply_act(__uint_as_float(r[8 * c + 2 * j + 1]) * scale, p.activation);
+          const float v0 = finish<BIAS>(p, __uint_as_float(r[8 * c + 2 * j]), scale, row0 + lane, col0 + c0 + 8 * c + 2 * j);
+          const float v1 = finish<BIAS>(p, __uint_as_float(r[8 * c + 2 * j + 1]), scale, row0 + lane, col0 + c0 + 8 * c + 2 * j + 1);
           w[j] = (p.out_dtype == B200_BF16) ? pack2<true>(v0, v1) : pack2<false>(v0, v1);
         }
         *reinterpret_cast<uint4*>(stg + sw128_offset(lane, c)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -171,8 +228,20 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
       uint32_t r[32];
       tmem_ld32(taddr + c0, r);
       tmem_ld_wait();
-      if (row < p.M) store_chunk32(p, row, col0 + c0, r, scale, vec_ok);
+      if (row < p.M) store_chunk32<BIAS, EXT>(p, row, col0 + c0, r, scale, vec_ok);
     }
+  }
+}
+
+template <bool EXT>
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tma_c, uint8_t* stg,
+                                                  uint32_t taddr, int ncols, int row0, int col0, int lane,
+                                                  float scale, bool vec_ok) {
+  if constexpr (EXT) {
+    if (p.bias_mode) drain_accumulator_t<true, true>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok);
+    else drain_accumulator_t<false, true>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok);
+  } else {
+    drain_accumulator_t<false, false>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok);
   }
 }
 
@@ -216,7 +285,7 @@ __device__ __forceinline__ void load_operand(const OperandGeom& g, const CUtenso
 }
 
 // ------------------------------------------------------------------------------- single CTA
-template <int BM, int BN, int STAGES>
+template <int BM, int BN, int STAGES, bool EXT>
 __global__ void __launch_bounds__(64 + BM + (BM == 256 ? 32 : 0), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
             const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
@@ -329,7 +398,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     float scale = 1.f;
     if (p.scale_a) scale *= __ldg(p.scale_a);
     if (p.scale_b) scale *= __ldg(p.scale_b);
-    const int esize = (p.out_dtype == B200_F32) ? 4 : 2;
+    const int esize = (p.out_dtype == B200_F32) ? 4 : (p.out_dtype == B200_E4M3 ? 1 : 2);
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (((p.ldc * esize) & 15) == 0);
     uint32_t ti = 0;
     for (int work = blockIdx.x; work < p.num_tiles * p.splits; work += gridDim.x, ++ti) {
@@ -345,7 +414,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                       tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
                       pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane);
       } else
-      drain_accumulator(p, &tma_c, staging + (warp - 2) * STG_BYTES,
+      drain_accumulator<EXT>(p, &tma_c, staging + (warp - 2) * STG_BYTES,
                         tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
                         pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
       tc_fence_before();
@@ -368,7 +437,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 // Barriers: both producers credit the LEADER's full[s] (the peer through the leader's cluster
 // address); the leader's tcgen05.commit is multicast to both CTAs' empty[s] / tmem_full[acc];
 // the peer's epilogue warps arrive remotely on the leader's tmem_empty[acc].
-template <int STAGES, int NB>
+template <int STAGES, int NB, bool EXT>
 __global__ void __launch_bounds__(192, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                  const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
@@ -480,7 +549,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     float scale = 1.f;
     if (p.scale_a) scale *= __ldg(p.scale_a);
     if (p.scale_b) scale *= __ldg(p.scale_b);
-    const int esize = (p.out_dtype == B200_F32) ? 4 : 2;
+    const int esize = (p.out_dtype == B200_F32) ? 4 : (p.out_dtype == B200_E4M3 ? 1 : 2);
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (((p.ldc * esize) & 15) == 0);
     uint32_t ti = 0;
     for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++ti) {
@@ -489,7 +558,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       const uint32_t acc = ti % NACC;
       mbar_wait(&tmem_full[acc], (ti / NACC) & 1u, p.status, SITE_GEMM_TMEM_FULL);
       tc_fence_after();
-      drain_accumulator(p, &tma_c, staging + (warp - 2) * STG_BYTES,
+      drain_accumulator<EXT>(p, &tma_c, staging + (warp - 2) * STG_BYTES,
                         tmem_base + ((quarter * 32u) << 16) + acc * 256, BN,
                         pid_m * 256 + rank * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
       tc_fence_before();
@@ -562,9 +631,10 @@ gemm_plain_kernel(const void* a, const void* b, GemmParams p, long long sam, lon
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tx * 4 + j;
       if (gn >= p.N) continue;
-      const float v = apply_act(acc[i][j] * scale, p.activation);
+      const float v = p.bias_mode ? finish<true>(p, acc[i][j], scale, gm, gn) : finish<false>(p, acc[i][j], scale, gm, gn);
       const long long o = (long long)gm * p.ldc + gn;
-      if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
+      if (p.out_dtype == B200_E4M3) reinterpret_cast<uint8_t*>(p.c)[o] = (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+      else if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
       else if (p.out_dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
       else reinterpret_cast<__half*>(p.c)[o] = __float2half_rn(v);
     }
@@ -581,9 +651,10 @@ splitk_reduce_kernel(GemmParams p) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     float v = 0.f;
     for (int sp = 0; sp < p.splits; ++sp) v += p.ws[(long long)sp * total + i];  // fixed order: deterministic
-    v = apply_act(v * scale, p.activation);
+    v = p.bias_mode ? finish<true>(p, v, scale, (int)(i / p.N), (int)(i % p.N)) : finish<false>(p, v, scale, 0, 0);
     const long long o = (i / p.N) * p.ldc + (i % p.N);
-    if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
+    if (p.out_dtype == B200_E4M3) reinterpret_cast<uint8_t*>(p.c)[o] = (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+    else if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
     else if (p.out_dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
     else reinterpret_cast<__half*>(p.c)[o] = __float2half_rn(v);
   }
@@ -620,33 +691,33 @@ constexpr size_t smem_bytes(int stages, int stage_bytes, int epilogue_warps) {
   return (size_t)stages * stage_bytes + (size_t)epilogue_warps * STG_BYTES + (2 * stages + 4) * 8 + 16 + 1024;
 }
 
-template <int BM, int BN, int STAGES>
-int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
+template <int BM, int BN, int STAGES, bool EXT>
+int launch_tile_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
                 GemmParams& p) {
   static bool attr_done[64] = {};
   constexpr size_t smem = smem_bytes(STAGES, (BM + BN) * KBYTES, BM / 32);
   if (!attr_done[ctx->device]) {
     cudaError_t e =
-        cudaFuncSetAttribute(gemm_kernel<BM, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(gemm_kernel<BM, BN, STAGES, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
     attr_done[ctx->device] = true;
   }
   const int work = p.num_tiles * p.splits;
   const int grid = work < ctx->sm_count ? work : ctx->sm_count;
-  gemm_kernel<BM, BN, STAGES><<<grid, 64 + BM + (BM == 256 ? 32 : 0), smem, stream>>>(ta, tb_, tc, p);
+  gemm_kernel<BM, BN, STAGES, EXT><<<grid, 64 + BM + (BM == 256 ? 32 : 0), smem, stream>>>(ta, tb_, tc, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
 
-template <int STAGES, int NB>
-int launch_pair(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
+template <int STAGES, int NB, bool EXT>
+int launch_pair_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
                 GemmParams& p) {
   static bool attr_done[64] = {};
   constexpr size_t smem = smem_bytes(STAGES, (128 + 128 * NB) * KBYTES, pair_staging_warps(STAGES, NB));
   if (pair_staging_warps(STAGES, NB) == 0) p.c_tma = 0;
   if (!attr_done[ctx->device]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<STAGES, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<STAGES, NB, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(gemm pair): %s", cudaGetErrorString(e));
     attr_done[ctx->device] = true;
@@ -665,9 +736,23 @@ int launch_pair(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<STAGES, NB>, ta, tb_, tc, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<STAGES, NB, EXT>, ta, tb_, tc, p);
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "gemm pair launch: %s", cudaGetErrorString(e));
   return B200_OK;
+}
+
+// the kernels with the bias and 8-bit-output epilogues are separate instantiations
+template <int BM, int BN, int STAGES>
+int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_,
+                const CUtensorMap& tc, GemmParams& p) {
+  if (p.bias_mode || p.out_dtype == B200_E4M3) return launch_tile_t<BM, BN, STAGES, true>(ctx, stream, ta, tb_, tc, p);
+  return launch_tile_t<BM, BN, STAGES, false>(ctx, stream, ta, tb_, tc, p);
+}
+template <int STAGES, int NB>
+int launch_pair(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_,
+                const CUtensorMap& tc, GemmParams& p) {
+  if (p.bias_mode || p.out_dtype == B200_E4M3) return launch_pair_t<STAGES, NB, true>(ctx, stream, ta, tb_, tc, p);
+  return launch_pair_t<STAGES, NB, false>(ctx, stream, ta, tb_, tc, p);
 }
 
 }  // namespace
@@ -691,7 +776,8 @@ int gemm_plan_splits(DeviceCtx* ctx, int M, int N, int K, int in_dtype) {
 
 int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                 int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t scm, int in_dtype, int out_dtype,
-                int activation, const float* scale_a, const float* scale_b, int splits, float* ws) {
+                int activation, const float* scale_a, const float* scale_b, const void* bias, int bias_mode,
+                int64_t bias_sm, int64_t bias_sn, int splits, float* ws) {
   const int elt = dtype_bytes(in_dtype);
   const int bk_elems = KBYTES / elt;
   const bool a_mn = !(sak == 1 || K == 1);  // K contiguous preferred
@@ -708,6 +794,7 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     q.c = c; q.M = M; q.N = N; q.K = K; q.ldc = scm;
     q.out_dtype = out_dtype; q.activation = activation;
     q.scale_a = scale_a; q.scale_b = scale_b;
+    q.bias = bias; q.bias_mode = bias_mode; q.bias_sm = bias_sm; q.bias_sn = bias_sn;
     dim3 grid((N + 63) / 64, (M + 63) / 64, 1);
     gemm_plain_kernel<<<grid, 256, 0, stream>>>(a, b, q, sam, sak, sbk, sbn, in_dtype);
     cudaError_t e = cudaGetLastError();
@@ -765,6 +852,7 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   p.kb_per_split = (p.num_k + splits - 1) / splits;
   p.splits = (p.num_k + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
   p.ws = ws;
+  p.bias = bias; p.bias_mode = bias_mode; p.bias_sm = bias_sm; p.bias_sn = bias_sn;
   p.group_m = env_int("B200_GEMM_GROUP_M", 8);
   if (p.group_m < 1) p.group_m = 1;
   const int fmt = (in_dtype == B200_BF16) ? 1 : 0;  // kind::f16: f16 = 0, bf16 = 1; kind::f8f6f4: e4m3 = 0
@@ -786,7 +874,7 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   // C through TMA stores when it is a 16-bit output that a tensor map can describe
   CUtensorMap tcm = ta;  // a valid map even when unused
   p.c_tma = 0;
-  if (out_dtype != B200_F32 && (reinterpret_cast<uintptr_t>(c) & 15) == 0 && ((scm * 2) & 15) == 0 &&
+  if ((out_dtype == B200_F16 || out_dtype == B200_BF16) && (reinterpret_cast<uintptr_t>(c) & 15) == 0 && ((scm * 2) & 15) == 0 &&
       !env_int("B200_GEMM_DIRECT_STORE", 0)) {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)scm * 2};
     uint32_t box[2] = {64, 32};

@@ -44,7 +44,8 @@ inline int dtype_bytes(int dt) {
 // launchers implemented in the kernel translation units
 int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                 int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t scm, int in_dtype, int out_dtype,
-                int activation, const float* scale_a, const float* scale_b, int splits, float* ws);
+                int activation, const float* scale_a, const float* scale_b, const void* bias, int bias_mode,
+                int64_t bias_sm, int64_t bias_sn, int splits, float* ws);
 int gemm_plan_splits(DeviceCtx* ctx, int M, int N, int K, int in_dtype);
 
 int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,

@@ -36,7 +36,7 @@ def _require_cuda(*ts):
     return dev
 
 
-def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, out=None):
+def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, out=None, bias=None):
     """C = act(A @ B) with fp32 accumulation.
 
     Same contract as the reference wrapper: `a.shape[1] == b.shape[0]`, `a` contiguous, `b`
@@ -44,6 +44,10 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
     as the reference; bf16 for bf16 and fp8 inputs unless `out_dtype` says otherwise).
     fp8-e4m3 inputs take optional per-tensor dequantisation scales (`scale_a`, `scale_b`:
     python floats or 1-element fp32 CUDA tensors) that the epilogue multiplies in.
+    `out_dtype=torch.float8_e4m3fn` stores an 8-bit C (round to nearest even, saturating).
+    `bias` is the reference's epilogue addend (test_gemm.py 'add-matrix' / 'add-rows' /
+    'add-cols'): a tensor of the output type and shape [M, N], [M, 1] (one value per row) or
+    [1, N] (one per column), added after the conversion to the output type.
     """
     assert a.dim() == 2 and b.dim() == 2, "matmul takes 2-D tensors"
     assert a.shape[1] == b.shape[0], "Incompatible dimensions"
@@ -70,16 +74,28 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
 
         pa, keep_a = scale_ptr(scale_a)
         pb, keep_b = scale_ptr(scale_b)
+        bias_mode, bias_ptr, bias_sm, bias_sn = _lib.BIAS_NONE, None, 0, 0
+        if bias is not None:
+            assert bias.dim() == 2 and bias.dtype == out_dtype and bias.device == dev, "bias: 2-D, output type, same device"
+            if bias.shape == (M, N):
+                bias_mode = _lib.BIAS_MATRIX
+            elif bias.shape == (M, 1):
+                bias_mode = _lib.BIAS_ROWS
+            elif bias.shape == (1, N):
+                bias_mode = _lib.BIAS_COLS
+            else:
+                raise AssertionError(f"bias shape {tuple(bias.shape)} is not [M, N], [M, 1] or [1, N]")
+            bias_ptr, bias_sm, bias_sn = bias.data_ptr(), bias.stride(0), bias.stride(1)
         # skinny problems (few tiles, long K) are split along K; the fp32 partial tiles need scratch
         splits, ws_bytes = ctypes.c_int(1), ctypes.c_size_t(0)
         _lib.check(_lib.lib().b200_matmul_plan(M, N, K, _DT[a.dtype], ctypes.byref(splits), ctypes.byref(ws_bytes)),
                    "matmul_plan")
         ws = torch.empty(ws_bytes.value // 4, device=dev, dtype=torch.float32) if splits.value > 1 else None
-        code = _lib.lib().b200_matmul_splitk(
+        code = _lib.lib().b200_matmul_bias(
             _stream(a), a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K,
             a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
-            _DT[a.dtype], _DT[out_dtype], _ACT[activation], pa, pb, splits.value,
-            ws.data_ptr() if ws is not None else None)
+            _DT[a.dtype], _DT[out_dtype], _ACT[activation], pa, pb, bias_ptr, bias_mode, bias_sm, bias_sn,
+            splits.value, ws.data_ptr() if ws is not None else None)
         _lib.check(code, "matmul")
     return c
 
