@@ -96,6 +96,23 @@ B200_API int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b
                               const float* scale_a, const float* scale_b, const void* bias, int bias_mode,
                               int64_t bias_stride_m, int64_t bias_stride_n, int splits, float* workspace);
 
+/* Grouped matmul: c[g] = a[g] @ b[g] for group_count independent problems in one persistent launch
+ * (python/tutorials/08-grouped-gemm.py:64-141 grouped_matmul_kernel, :144-191 group_gemm_fn).
+ * a, b, c are HOST arrays of device pointers; sizes = {M, N, K} and lds = {lda, ldb, ldc} per group
+ * are host arrays laid out like the reference's `group_gemm_sizes` and `g_lds` tensors ([group][3]).
+ * A[g] is [M, K] row-major with leading dimension lda, B[g] is [K, N] row-major (ldb), C[g] is
+ * [M, N] row-major (ldc), as in the reference; in_dtype F16 or BF16, out_dtype F16, BF16 or F32,
+ * fp32 accumulation, one rounding.  Partial tiles are handled (the reference assumes full tiles).
+ * Operands must be addressable by TMA (16-byte aligned base, lda and ldb multiples of 8 elements),
+ * else B200_ERR_UNSUPPORTED.  `workspace`: b200_grouped_matmul_workspace(group_count) bytes of
+ * device memory, 128-byte aligned, owned by the caller; the call writes the groups' descriptors
+ * there (asynchronously, on `stream`) and the kernel reads them, so it must stay untouched until
+ * the work on `stream` has finished. */
+B200_API size_t b200_grouped_matmul_workspace(int group_count);
+B200_API int b200_grouped_matmul(b200_stream_t stream, int group_count, const void* const* a, const void* const* b,
+                                 void* const* c, const int* sizes, const int* lds, int in_dtype, int out_dtype,
+                                 void* workspace);
+
 /* Flash-attention forward: O = softmax(Q K^T * sm_scale, causal mask optional) V, and per-row
  * statistics M[Z,H,N] (fp32) = base-2 log-sum-exp of the scores scaled by sm_scale * log2(e)
  * (natural-log LSE = M * ln 2).

@@ -383,3 +383,69 @@ def test_e4m3_output(shape, in_dtype):
     close = np.abs(gotf - want) <= 0.13 * np.maximum(np.abs(want), 2.0 ** -6)
     assert close.all()
     assert (gotf != want).mean() < 0.02
+
+
+def _grouped_inputs(shapes, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    A = [torch.rand(M, K, generator=g).to(dtype) for (M, N, K) in shapes]   # the reference uses torch.rand
+    B = [torch.rand(K, N, generator=g).to(dtype) for (M, N, K) in shapes]
+    return A, B
+
+
+def test_grouped_matmul_reference_sizes():
+    """python/tutorials/08-grouped-gemm.py:194-215: four square problems 1024 .. 128, fp16, compared
+    per group with atol 1e-2 (the reference's check) against the oracle's tile loop."""
+    shapes = [(s, s, s) for s in (1024, 512, 256, 128)]
+    A, B = _grouped_inputs(shapes, torch.float16, 0)
+    C = triton_b200.group_gemm_fn([t.to(DEV) for t in A], [t.to(DEV) for t in B])
+    status_ok()
+    assert len(C) == 4
+    for a, b, c in zip(A, B, C):
+        assert c.dtype == torch.float16 and c.shape == (a.shape[0], b.shape[1])
+        want = R.matmul(f32(a), f32(b), out="fp16")
+        # torch.rand inputs: |c| ~ K/4, one fp16 ulp at 256 is 0.125
+        np.testing.assert_allclose(f32(c), want, rtol=1e-2, atol=1e-2)
+        assert (f32(c) != want).mean() < 0.05
+
+
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.float16, None), (torch.bfloat16, torch.float32)])
+def test_grouped_matmul_ragged_and_empty_groups(dtype, out_dtype):
+    """Partial tiles in every dimension, one-row and one-tile problems, an empty group, a K = 0 group
+    (an empty sum: zeros), more tiles than SMs; each group equals the single matmul's bits (up to the summation order
+    where the single matmul splits K)."""
+    shapes = [(130, 72, 200), (1, 8, 8), (300, 520, 64), (0, 64, 64), (64, 128, 0), (2000, 1544, 136), (128, 128, 4096)]
+    A, B = _grouped_inputs(shapes, dtype, 1)
+    Ad, Bd = [t.to(DEV) for t in A], [t.to(DEV) for t in B]
+    C = triton_b200.group_gemm_fn(Ad, Bd, out_dtype=out_dtype)
+    status_ok()
+    od = out_dtype or dtype
+    for (M, N, K), a, b, c in zip(shapes, Ad, Bd, C):
+        assert c.shape == (M, N) and c.dtype == od
+        if M == 0:
+            continue
+        if K == 0:
+            assert float(c.abs().max()) == 0.0
+            continue
+        single = triton_b200.matmul(a, b, out_dtype=od)
+        if K < 2048:  # longer K loops take split-K in the single matmul: another summation order
+            assert torch.equal(c, single), (M, N, K)
+        else:
+            assert torch.allclose(c.float(), single.float(), rtol=4e-3, atol=1e-2), (M, N, K)
+        out = {torch.float16: "fp16", torch.bfloat16: "bf16", torch.float32: "fp32"}[od]
+        if M * N * K <= 300 * 520 * 64:
+            np.testing.assert_allclose(f32(c), R.matmul(f32(a), f32(b), out=out), rtol=1e-2, atol=1e-2)
+
+
+def test_grouped_matmul_layout_errors_and_strided_operands():
+    a = torch.rand(64, 72, dtype=torch.float16, device=DEV)
+    b9 = torch.rand(72, 9, dtype=torch.float16, device=DEV)   # ldb = 9 elements: not addressable by TMA
+    with pytest.raises(RuntimeError, match="16 bytes"):
+        triton_b200.group_gemm_fn([a], [b9])
+    # row-major views with padded leading dimensions are fine
+    wide_a = torch.rand(64, 144, dtype=torch.float16, device=DEV)
+    wide_b = torch.rand(72, 80, dtype=torch.float16, device=DEV)
+    av, bv = wide_a[:, :72], wide_b[:, :40]
+    (c,) = triton_b200.group_gemm_fn([av], [bv])
+    assert torch.equal(c, triton_b200.matmul(av.contiguous(), bv.contiguous()))
+    assert triton_b200.group_gemm_fn([], []) == []
+    status_ok()

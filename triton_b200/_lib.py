@@ -27,6 +27,8 @@ SIGNATURES = {
     "b200_matmul_splitk": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p, _i, _p],
     "b200_matmul_bias": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p,
                          _p, _i, _i64, _i64, _i, _p],
+    "b200_grouped_matmul_workspace": [_i],
+    "b200_grouped_matmul": [_p, _i, _p, _p, _p, _p, _p, _i, _i, _p],
     "b200_attention_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
     "b200_attention_bwd": [_p] + [_p] * 10 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
     "b200_attention_bwd_noalloc": [_p] + [_p] * 9 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
@@ -48,7 +50,8 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = args
             fn.restype = (ctypes.c_char_p if name == "b200_last_error" else
-                          ctypes.c_longlong if name.endswith("_capacity") else ctypes.c_int)
+                          ctypes.c_longlong if name.endswith("_capacity") else
+                          ctypes.c_size_t if name.endswith("_workspace") else ctypes.c_int)
         _lib = L
     return _lib
 

@@ -252,6 +252,23 @@ int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c
                      bias_stride_n, splits, workspace);
 }
 
+size_t b200_grouped_matmul_workspace(int group_count) { return gemm_grouped_workspace_bytes(group_count); }
+
+int b200_grouped_matmul(b200_stream_t stream, int group_count, const void* const* a, const void* const* b,
+                        void* const* c, const int* sizes, const int* lds, int in_dtype, int out_dtype,
+                        void* workspace) {
+  if (group_count < 0) return fail(B200_ERR_ARG, "negative group count");
+  if (group_count == 0) return B200_OK;
+  if (!a || !b || !c || !sizes || !lds) return fail(B200_ERR_ARG, "null array");
+  if (in_dtype != B200_F16 && in_dtype != B200_BF16) return fail(B200_ERR_ARG, "grouped matmul takes F16 or BF16 inputs");
+  if (out_dtype != B200_F16 && out_dtype != B200_BF16 && out_dtype != B200_F32)
+    return fail(B200_ERR_ARG, "out_dtype must be F16, BF16 or F32");
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  return launch_gemm_grouped(ctx, reinterpret_cast<cudaStream_t>(stream), group_count, a, b, c, sizes, lds, in_dtype,
+                             out_dtype, workspace);
+}
+
 int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m, int Z,
                        int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
                        const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal, int dtype) {

@@ -34,6 +34,7 @@
 #include <cuda_fp8.h>
 
 #include <cstdlib>
+#include <vector>
 
 #include "common.cuh"
 #include "host.h"
@@ -660,6 +661,152 @@ splitk_reduce_kernel(GemmParams p) {
   }
 }
 
+// ------------------------------------------------------------------------------------- grouped
+// Grouped matmul (python/tutorials/08-grouped-gemm.py:64-141): several independent problems in one
+// persistent launch.  The reference walks the groups on the device with a running tile count and
+// reads pointers and sizes from device tensors; here each group has a descriptor in device memory
+// (written by the host for this call) that also carries the group's three tensor maps, and every
+// role warp walks the same tile sequence: tile t belongs to the group whose [tile_start,
+// tile_start + num_tiles) contains it, tiles of a group in row-major order as in the reference.
+// 128 x 128 tiles, two accumulators, so a group's epilogue overlaps the next tile's main loop even
+// across a group boundary.  Partial tiles are zero-filled on load and clipped on store (the
+// reference assumes full tiles).
+struct alignas(128) GroupDesc {
+  CUtensorMap ta, tb, tc;
+  void* c;
+  long long ldc;
+  int M, N, num_k, num_pid_n, tile_start, num_tiles, c_tma, pad_;
+};
+static_assert(sizeof(GroupDesc) == 512, "GroupDesc is 512 bytes");
+
+__device__ __forceinline__ int find_group(const GroupDesc* groups, int g, int tile) {
+  while (tile >= groups[g].tile_start + groups[g].num_tiles) ++g;  // tiles only move forward
+  return g;
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_grouped_kernel(const GroupDesc* __restrict__ groups, int total_tiles, const GemmParams p) {
+  constexpr int BM = 128, BN = 128;
+  constexpr uint32_t A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;  // one 4 KiB buffer per epilogue warp
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + (BM / 32) * STG_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tmem_full[i], 1);
+      mbar_init(&tmem_empty[i], BM);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      int g = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        g = find_group(groups, g, tile);
+        const GroupDesc* gd = groups + g;
+        const int t = tile - gd->tile_start;
+        const int m0 = (t / gd->num_pid_n) * BM, n0 = (t % gd->num_pid_n) * BN;
+        const int num_k = gd->num_k;
+        for (int kb = 0; kb < num_k; ++kb) {
+          mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          uint8_t* a_dst = smem + s * STAGE_BYTES;
+          load_operand<false>(p.ga, &gd->ta, a_dst, &full[s], kb * p.bk_elems, m0);
+          load_operand<false>(p.gb, &gd->tb, a_dst + A_BYTES, &full[s], kb * p.bk_elems, n0);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    const uint64_t da0 = smem_desc_sw128(smem_u32(smem), p.ga.lbo, p.ga.sbo);
+    const uint64_t db0 = smem_desc_sw128(smem_u32(smem) + A_BYTES, p.gb.lbo, p.gb.sbo);
+    const uint32_t ka = p.ga.kstep_bytes >> 4, kb16 = p.gb.kstep_bytes >> 4;
+    const uint32_t idesc = p.idesc;
+    uint32_t s = 0, ph = 0, ti = 0;
+    int g = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
+      g = find_group(groups, g, tile);
+      const int num_k = groups[g].num_k;
+      const uint32_t acc = ti & 1u;
+      mbar_wait(&tmem_empty[acc], ((ti >> 1) & 1u) ^ 1u, p.status, SITE_GEMM_TMEM_EMPTY);
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      uint32_t accum = 0;
+      for (int kb = 0; kb < num_k; ++kb) {
+        mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);
+        const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
+#pragma unroll
+        for (int k = 0; k < KBYTES / 32; ++k) {
+          umma_ss_elect<false>(d_tmem, das + k * ka, dbs + k * kb16, idesc, accum);
+          accum = 1;
+        }
+        tc_commit_elect(&empty[s]);
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+      tc_commit_elect(&tmem_full[acc]);
+    }
+    __syncwarp();
+  } else {
+    const uint32_t quarter = warp & 3u;
+    const int esize = (p.out_dtype == B200_F32) ? 4 : 2;
+    uint32_t ti = 0;
+    int g = 0;
+    bool any_tma = false;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
+      g = find_group(groups, g, tile);
+      const GroupDesc* gd = groups + g;
+      const int t = tile - gd->tile_start;
+      GemmParams q = p;  // the group's output replaces the common parameters' placeholders
+      q.c = gd->c; q.ldc = gd->ldc; q.M = gd->M; q.N = gd->N; q.c_tma = gd->c_tma;
+      any_tma |= q.c_tma != 0;
+      const bool vec_ok = ((reinterpret_cast<uintptr_t>(q.c) & 15) == 0) && (((q.ldc * esize) & 15) == 0);
+      const uint32_t acc = ti & 1u;
+      mbar_wait(&tmem_full[acc], (ti >> 1) & 1u, p.status, SITE_GEMM_TMEM_FULL);
+      tc_fence_after();
+      drain_accumulator<false>(q, &gd->tc, staging + (warp - 2) * STG_BYTES,
+                               tmem_base + ((quarter * 32u) << 16) + acc * BN, BN,
+                               (t / gd->num_pid_n) * BM + quarter * 32, (t % gd->num_pid_n) * BN, lane, 1.f, vec_ok);
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[acc]);
+    }
+    if (any_tma && lane == 0) tma_store_wait_all<0>();
+  }
+
+  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------------------------- host
 int env_int(const char* name, int dflt) {
   const char* v = getenv(name);
@@ -897,6 +1044,81 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "split-K reduce launch: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+size_t gemm_grouped_workspace_bytes(int group_count) { return (size_t)(group_count > 0 ? group_count : 0) * sizeof(GroupDesc); }
+
+int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, int group_count, const void* const* a,
+                        const void* const* b, void* const* c, const int* sizes, const int* lds, int in_dtype,
+                        int out_dtype, void* workspace) {
+  constexpr int BM = 128, BN = 128, STAGES = 6;
+  const int elt = dtype_bytes(in_dtype);  // 2
+  const int bk_elems = KBYTES / elt;
+  std::vector<GroupDesc> descs;
+  descs.reserve(group_count);
+  int total_tiles = 0;
+  for (int g = 0; g < group_count; ++g) {
+    const int M = sizes[3 * g], N = sizes[3 * g + 1], K = sizes[3 * g + 2];
+    const long long lda = lds[3 * g], ldb = lds[3 * g + 1], ldc = lds[3 * g + 2];
+    if (M < 0 || N < 0 || K < 0) return fail(B200_ERR_ARG, "group %d: negative dimension", g);
+    if (M == 0 || N == 0) continue;
+    if (!c[g] || (K > 0 && (!a[g] || !b[g]))) return fail(B200_ERR_ARG, "group %d: null pointer", g);
+    if (K == 0) {  // an empty sum
+      cudaError_t e = cudaMemset2DAsync(c[g], (size_t)ldc * dtype_bytes(out_dtype), 0, (size_t)N * dtype_bytes(out_dtype),
+                                        (size_t)M, stream);
+      if (e != cudaSuccess) return fail(B200_ERR_CUDA, "memset: %s", cudaGetErrorString(e));
+      continue;
+    }
+    GroupDesc d{};
+    uint64_t dims[2], strides[1];
+    uint32_t box[2];
+    // A [M, K] row-major: K-major operand; B [K, N] row-major: N-major operand (as in the reference)
+    dims[0] = K; dims[1] = M; strides[0] = (uint64_t)lda * elt; box[0] = bk_elems; box[1] = BM;
+    if (!encode_tmap(&d.ta, in_dtype, 2, a[g], dims, strides, box, true)) return B200_ERR_UNSUPPORTED;
+    dims[0] = N; dims[1] = K; strides[0] = (uint64_t)ldb * elt; box[0] = 128 / elt; box[1] = bk_elems;
+    if (!encode_tmap(&d.tb, in_dtype, 2, b[g], dims, strides, box, true)) return B200_ERR_UNSUPPORTED;
+    d.tc = d.ta;
+    d.c_tma = 0;
+    if ((out_dtype == B200_F16 || out_dtype == B200_BF16) && (reinterpret_cast<uintptr_t>(c[g]) & 15) == 0 &&
+        ((ldc * 2) & 15) == 0) {
+      uint64_t cd[2] = {(uint64_t)N, (uint64_t)M}, cs[1] = {(uint64_t)ldc * 2};
+      uint32_t cb[2] = {64, 32};
+      if (encode_tmap(&d.tc, out_dtype, 2, c[g], cd, cs, cb, true)) d.c_tma = 1;
+    }
+    d.c = c[g]; d.ldc = ldc; d.M = M; d.N = N;
+    d.num_k = (K + bk_elems - 1) / bk_elems;
+    d.num_pid_n = (N + BN - 1) / BN;
+    d.tile_start = total_tiles;
+    d.num_tiles = ((M + BM - 1) / BM) * d.num_pid_n;
+    total_tiles += d.num_tiles;
+    descs.push_back(d);
+  }
+  if (descs.empty()) return B200_OK;
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 127))
+    return fail(B200_ERR_ARG, "grouped matmul needs a 128-byte aligned device workspace (b200_grouped_matmul_workspace)");
+  // pageable host memory: the copy has left the vector when the call returns
+  cudaError_t e = cudaMemcpyAsync(workspace, descs.data(), descs.size() * sizeof(GroupDesc), cudaMemcpyHostToDevice, stream);
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "descriptor copy: %s", cudaGetErrorString(e));
+
+  GemmParams p{};
+  p.out_dtype = out_dtype; p.activation = B200_ACT_NONE; p.status = ctx->status;
+  p.bk_elems = bk_elems; p.splits = 1;
+  const int fmt = (in_dtype == B200_BF16) ? 1 : 0;
+  p.idesc = make_idesc(fmt, fmt, 0, 1, BM, BN);
+  p.ga = make_geom(false, BM, elt, bk_elems);
+  p.gb = make_geom(true, BN, elt, bk_elems);
+  static bool attr_done[64] = {};
+  constexpr size_t smem = smem_bytes(STAGES, (BM + BN) * KBYTES, BM / 32);
+  if (!attr_done[ctx->device]) {
+    e = cudaFuncSetAttribute(gemm_grouped_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(grouped gemm): %s", cudaGetErrorString(e));
+    attr_done[ctx->device] = true;
+  }
+  const int grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
+  gemm_grouped_kernel<STAGES><<<grid, 192, smem, stream>>>(reinterpret_cast<const GroupDesc*>(workspace), total_tiles, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "grouped gemm launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
 

@@ -100,6 +100,44 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
     return c
 
 
+def group_gemm_fn(group_A, group_B, out_dtype=None):
+    """[A_i @ B_i for every i] in one persistent launch: the reference's grouped GEMM
+    (python/tutorials/08-grouped-gemm.py:144-191, same name and argument lists): every A_i is
+    [M_i, K_i] and every B_i is [K_i, N_i], row-major 2-D CUDA tensors of one 16-bit dtype; returns
+    the list of new C_i (dtype of A unless `out_dtype` says otherwise).  Unlike the reference,
+    sizes need not be multiples of the tile shape."""
+    assert len(group_A) == len(group_B)
+    G = len(group_A)
+    if G == 0:
+        return []
+    dev = _require_cuda(*group_A, *group_B)
+    dt = group_A[0].dtype
+    assert dt in (torch.float16, torch.bfloat16), "grouped matmul takes fp16 or bf16"
+    out_dtype = out_dtype or dt
+    sizes, lds, group_C = [], [], []
+    with torch.cuda.device(dev):
+        for A, B in zip(group_A, group_B):
+            assert A.dim() == 2 and B.dim() == 2 and A.shape[1] == B.shape[0]
+            assert A.dtype == dt and B.dtype == dt
+            assert (A.stride(1) == 1 or A.shape[1] == 1) and (B.stride(1) == 1 or B.shape[1] == 1), "row-major operands"
+            M, K = A.shape
+            N = B.shape[1]
+            C = torch.empty((M, N), device=dev, dtype=out_dtype)
+            group_C.append(C)
+            sizes += [M, N, K]
+            lds += [A.stride(0), B.stride(0), C.stride(0)]
+        L = _lib.lib()
+        PtrArr, IntArr = ctypes.c_void_p * G, ctypes.c_int * (3 * G)
+        ws = torch.empty(L.b200_grouped_matmul_workspace(G) + 128, dtype=torch.uint8, device=dev)
+        ws_ptr = (ws.data_ptr() + 127) & ~127
+        code = L.b200_grouped_matmul(
+            _stream(group_A[0]), G, PtrArr(*[t.data_ptr() for t in group_A]), PtrArr(*[t.data_ptr() for t in group_B]),
+            PtrArr(*[t.data_ptr() for t in group_C]), IntArr(*sizes), IntArr(*lds), _DT[dt], _DT[out_dtype], ws_ptr)
+        _lib.check(code, "grouped_matmul")
+        ws.record_stream(torch.cuda.current_stream(dev))  # the kernel reads the descriptors after this returns
+    return group_C
+
+
 class HostMatmul:
     """C = A @ B for operands that live in (pinned) host memory: the call a host-side user of the
     matmul makes.  B goes to the device once per call; A is sent in row blocks and every block's
