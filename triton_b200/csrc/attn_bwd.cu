@@ -207,7 +207,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       auto issue_acc = [&](uint32_t tm_acc, uint32_t tm_opnd, uint64_t dun, uint32_t accum) {  // acc (+)= X U, 8 MMAs
 #pragma unroll
         for (int kk = 0; kk < BLK / 16; ++kk)
-          umma_ts_f16_elect(tm_acc, tm_opnd + kk * 8, dun + kk * ((16 * 128) >> 4), IDESC_ACC, (accum | kk) != 0);
+          umma_ts_f16_elect(tm_acc, tm_opnd + (kk >> 2) * 64 + (kk & 3) * 8, dun + kk * ((16 * 128) >> 4), IDESC_ACC,
+                            (accum | kk) != 0);
       };
 
       uint32_t s = 0, ph = 0;  // ring position
@@ -269,9 +270,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   } else {
     // ------------------------------------------------------------------ compute
     // Two threads per row: warps w and w+4 own the same TMEM lanes and split the 128 columns of
-    // T1 / T2 (and, in the epilogue, of the accumulators) in halves.  P and dS are packed over the
-    // FIRST 64 columns of T1 / T2, i.e. over columns the other half's thread reads, so a named
-    // barrier separates "both halves have read" from "either half writes".
+    // T1 / T2 (and, in the epilogue, of the accumulators) in halves.  Each thread packs its P and
+    // dS over the first 32 of its OWN 64 columns (the MMA reads its A operand from columns
+    // [0, 32) and [64, 96)), so the two halves never touch each other's columns and need no
+    // barrier between them: they may drift apart, and one half's exponentials overlap the other
+    // half's dS arithmetic on the same scheduler.
     const uint32_t quarter = warp & 3u;
     const int half = warp >> 2;
     constexpr int HC = BLK / 2, HD = D / 2;
@@ -312,7 +315,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
 #pragma unroll
         for (int c = 0; c < HC; c += 32) tmem_ld32(tm_t1 + lane_addr + half * HC + c, pr + c);
         tmem_ld_wait();
-        if (!DQ) asm volatile("bar.sync 1, 256;" ::: "memory");  // both halves hold their T1 columns in registers
 #pragma unroll
         for (int c4 = 0; c4 < HC; c4 += 4) {
           // column statistics: one 16-byte broadcast load for four columns
@@ -334,7 +336,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
             uint32_t wv[16];
 #pragma unroll
             for (int k = 0; k < 16; ++k) wv[k] = pack2<BF16>(__uint_as_float(pr[c + 2 * k]), __uint_as_float(pr[c + 2 * k + 1]));
-            tmem_st16(tm_t1 + lane_addr + ((half * HC + c) >> 1), wv);
+            tmem_st16(tm_t1 + lane_addr + half * HC + (c >> 1), wv);  // over the first 32 of the own 64 columns
           }
           tmem_st_wait();
           tc_fence_before();
@@ -359,9 +361,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
             dsw[((c + k4) >> 1) + 1] = pack2<BF16>(ds2, ds3);
           }
         }
-        asm volatile("bar.sync 2, 256;" ::: "memory");  // both halves have read all of T2
 #pragma unroll
-        for (int c = 0; c < HC / 2; c += 16) tmem_st16(tm_t2 + lane_addr + half * (HC / 2) + c, dsw + c);
+        for (int c = 0; c < HC / 2; c += 16) tmem_st16(tm_t2 + lane_addr + half * HC + c, dsw + c);  // own columns
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(ds_full);
