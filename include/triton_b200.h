@@ -31,7 +31,7 @@ extern "C" {
 
 typedef struct CUstream_st* b200_stream_t; /* a cudaStream_t / CUstream */
 
-enum b200_dtype { B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3 };
+enum b200_dtype { B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3, B200_E5M2 = 4 };
 enum b200_activation { B200_ACT_NONE = 0, B200_ACT_LEAKY_RELU = 1 };
 enum b200_bias { B200_BIAS_NONE = 0, B200_BIAS_MATRIX = 1, B200_BIAS_ROWS = 2, B200_BIAS_COLS = 3 };
 enum b200_error {
@@ -121,7 +121,13 @@ B200_API int b200_grouped_matmul(b200_stream_t stream, int group_count, const vo
  * stride quadruples, Z, H, N_CTX, HEAD_DIM, STAGE -> causal).
  * q, k, v, o: [Z, H, N, D] of `dtype` (F16 or BF16) with element strides {z, h, n, d} each; the d
  * stride must be 1 and the others multiples of 8 elements; D is 64 or 128; sm_scale > 0.
- * m: contiguous [Z, H, N] fp32. */
+ * m: contiguous [Z, H, N] fp32.
+ * dtype E5M2 is the reference's 8-bit forward (06-fused-attention.py:38-40, 66-69, 127, 609-615):
+ * q, k, v and o are e5m2, both products run on 8-bit MMAs, P is converted to e5m2 (round to
+ * nearest even, saturating) before the second product and O is stored as e5m2.  D must be 128;
+ * q, k, o need a d stride of 1 and other strides that are multiples of 16 elements; v must have its
+ * KEY dimension contiguous (stride_v[2] == 1, the `v.permute(0, 1, 3, 2).contiguous().permute(0,
+ * 1, 3, 2)` layout the reference gives an fp8 V) and stride_v[3] a multiple of 16. */
 B200_API int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m,
                                 int Z, int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
                                 const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal,

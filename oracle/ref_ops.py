@@ -83,6 +83,25 @@ def round_e4m3(x):
 ROUND["e4m3"] = round_e4m3
 
 
+def round_e5m2(x):
+    """fp32 -> e5m2 (round to nearest even, saturating at +-57344) -> fp32: the reference's
+    `p.to(tl.float8e5)` (python/tutorials/06-fused-attention.py:66-67) and its e5m2 stores,
+    cvt.rn.satfinite.e5m2x2.f32 on NVIDIA GPUs; below the largest finite value it is torch's
+    float8_e5m2 conversion, which pins it (tests/test_oracle.py)."""
+    x = np.asarray(x, dtype=np.float32)
+    a = np.minimum(np.abs(x).astype(np.float64), 57344.0)
+    with np.errstate(divide="ignore"):
+        e = np.floor(np.log2(np.where(a > 0, a, 1.0)))
+    e = np.maximum(e, -14.0)           # subnormals share the quantum of the smallest binade
+    q = np.exp2(e - 2.0)               # 2 mantissa bits
+    r = np.rint(a / q) * q
+    out = np.copysign(r, x).astype(np.float32)
+    return np.where(np.isnan(x), np.float32(np.nan), out)
+
+
+ROUND["e5m2"] = round_e5m2
+
+
 def add_bias(c, bias, out):
     """The reference's bias epilogues, python/test/unit/hopper/test_gemm.py:213-222: the tile is
     already converted to the output type (`z = z.to(out_dtype)`) and `z += bias` rounds again in

@@ -174,3 +174,17 @@ def test_bias_epilogue_rounds_twice_in_the_output_type():
         z = torch.tensor(R.matmul(a, b, out="fp32")).half()  # the oracle's own fp32 accumulator
         z = z + torch.tensor(bias).half()
         np.testing.assert_array_equal(got, z.float().numpy())
+
+
+def test_round_e5m2_matches_torch_and_saturates():
+    import torch
+    rng = np.random.default_rng(0)
+    x = np.concatenate([rng.standard_normal(50000).astype(np.float32) * s for s in (1e-5, 1e-3, 1.0, 300.0, 20000.0)] +
+                       [np.array([0.0, -0.0, 57344.0, -57344.0, 2.0 ** -16, 2.0 ** -17, 1.5 * 2.0 ** -16, 2.5 * 2.0 ** -16],
+                                 dtype=np.float32)])
+    x = x[np.abs(x) <= 57344]
+    want = torch.tensor(x).to(torch.float8_e5m2).float().numpy()
+    got = R.round_e5m2(x)
+    assert np.array_equal(got, want) and np.array_equal(np.signbit(got), np.signbit(want))
+    np.testing.assert_array_equal(R.round_e5m2(np.array([6e4, -1e9], dtype=np.float32)),
+                                  np.array([57344.0, -57344.0], dtype=np.float32))

@@ -10,7 +10,7 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libtriton_b200.so")
 
-F16, BF16, E4M3, F32 = 0, 1, 2, 3
+F16, BF16, E4M3, F32, E5M2 = 0, 1, 2, 3, 4
 ACT_NONE, ACT_LEAKY_RELU = 0, 1
 BIAS_NONE, BIAS_MATRIX, BIAS_ROWS, BIAS_COLS = 0, 1, 2, 3
 

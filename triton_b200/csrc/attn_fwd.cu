@@ -51,19 +51,30 @@ struct FwdParams {
   unsigned* status;
 };
 
-template <int D>
+// FP8: Q, K, V, P and O are 8-bit (e5m2, the reference's fp8 forward, 06-fused-attention.py:38-40,
+// 66-69, 127): both products use kind::f8f6f4 MMAs with K = 32 per instruction; V is read with its
+// key dimension contiguous (the layout the reference gives an fp8 V), i.e. as a K-major operand.
+template <int D, bool FP8 = false>
 struct FwdCfg {
-  static constexpr int TILE_BYTES = BLK * D * 2;               // one Q tile or one K / V block
-  static constexpr int KV_STAGES = (D == 128) ? 4 : 8;
+  static constexpr int TILE_BYTES = BLK * D * (FP8 ? 1 : 2);   // one Q tile or one K / V block
+  static constexpr int KV_STAGES = (D == 128 && !FP8) ? 4 : 8;
   // tiles + barriers + TMEM slot + scheduler slots + alignment slack
   static constexpr int STG_BYTES = 32 * 128;  // epilogue staging of one softmax warp: 32 rows x 64 columns
   static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + 8 * STG_BYTES + (2 * KV_STAGES + 18) * 8 + 32 + 1024;
 };
 
-template <int D>
-__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int z) {
+// one Q tile or K / V block of 128 rows: boxes of 128 bytes x 128 rows.  `along_rows`: the 8-bit V,
+// whose map is [D rows][N keys]: the block is 128 keys wide and starts at key row0.
+template <int D, bool FP8>
+__device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int z,
+                                          bool along_rows = false) {
+  if constexpr (FP8) {
+    if (along_rows) tma_load_4d(dst, map, bar, row0, 0, h, z);
+    else tma_load_4d(dst, map, bar, 0, row0, h, z);
+  } else {
 #pragma unroll
-  for (int b = 0; b < D / 64; ++b) tma_load_4d(dst + b * (BLK * 128), map, bar, b * 64, row0, h, z);
+    for (int b = 0; b < D / 64; ++b) tma_load_4d(dst + b * (BLK * 128), map, bar, b * 64, row0, h, z);
+  }
 }
 
 // One work item = 256 query rows of one (batch, head).  Items are numbered head-major, heavy
@@ -84,12 +95,12 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int w) {
   return it;
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool FP8>
 __global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o_map,
                 const FwdParams p) {
-  using Cfg = FwdCfg<D>;
+  using Cfg = FwdCfg<D, FP8>;
   constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES;
   constexpr int MMA_WARP = 8, TMA_WARP = 9;
 
@@ -161,13 +172,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_wait(q_empty, (n & 1u) ^ 1u, p.status, SITE_FWD_Q);  // previous item's S MMAs are done with Q
         for (int i = 0; i < 2; ++i) {
           mbar_expect_tx(&q_full[i], TILE);
-          load_tile<D>(sq + i * TILE, &tm_q, &q_full[i], it.qb * 256 + i * BLK, it.h, it.z);
+          load_tile<D, FP8>(sq + i * TILE, &tm_q, &q_full[i], it.qb * 256 + i * BLK, it.h, it.z);
         }
         for (int j = 0; j < it.n1; ++j) {
           for (int kv = 0; kv < 2; ++kv) {  // K_j then V_j
             mbar_wait(&kv_empty[s], ph ^ 1u, p.status, SITE_FWD_KV_EMPTY);
             mbar_expect_tx(&kv_full[s], TILE);
-            load_tile<D>(skv + s * TILE, kv == 0 ? &tm_k : &tm_v, &kv_full[s], j * BLK, it.h, it.z);
+            load_tile<D, FP8>(skv + s * TILE, kv == 0 ? &tm_k : &tm_v, &kv_full[s], j * BLK, it.h, it.z, kv == 1);
             if (++s == NST) { s = 0; ph ^= 1u; }
           }
         }
@@ -180,21 +191,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     // one per tile, were measured 20 % slower: MMAs of different threads interleave in the pipe
     // at a cost.)
     {
-      constexpr int FMT = BF16 ? 1 : 0;
+      constexpr int FMT = (BF16 || FP8) ? 1 : 0;  // kind::f16: bf16 = 1; kind::f8f6f4: e5m2 = 1
       constexpr uint32_t IDESC_S = make_idesc(FMT, FMT, 0, 0, 128, BLK);  // Q (K-major) x K (K-major)
-      constexpr uint32_t IDESC_O = make_idesc(FMT, FMT, 0, 1, 128, D);    // P (TMEM) x V (N-major)
+      constexpr uint32_t IDESC_O = make_idesc(FMT, FMT, 0, FP8 ? 0 : 1, 128, D);  // P (TMEM) x V (N-major; K-major when 8-bit)
       const uint64_t dq0 = smem_desc_sw128(smem_u32(sq), 0, 1024);
       const uint64_t dk0 = smem_desc_sw128(smem_u32(skv), 0, 1024);
-      const uint64_t dv0 = smem_desc_sw128(smem_u32(skv), BLK * 128, 1024);  // LBO: next 64-column box
+      const uint64_t dv0 = smem_desc_sw128(smem_u32(skv), FP8 ? 0 : BLK * 128, 1024);  // LBO: next 64-column box
       uint32_t s = 0, ph = 0;        // ring position of the next unconsumed K / V block
       uint32_t pcnt[2] = {0, 0};     // blocks of tile i whose P has been consumed (parity of p_full)
 
       auto issue_s = [&](int i, uint32_t stage) {  // S_i = Q_i K^T, D/16 MMAs
         const uint64_t dq = dq0 + i * (TILE >> 4), dk = dk0 + stage * (TILE >> 4);
+        if constexpr (FP8) {
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * ((BLK * 128) >> 4) + (kk & 3) * 2;  // 64-col box, 32 B per step
-          umma_ss_elect<false>(tm_s[i], dq + off, dk + off, IDESC_S, kk != 0);
+          for (int kk = 0; kk < D / 32; ++kk)  // one 128-byte box: 32 B (32 elements) per step
+            umma_ss_elect<true>(tm_s[i], dq + kk * 2, dk + kk * 2, IDESC_S, kk != 0);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint32_t off = (kk >> 2) * ((BLK * 128) >> 4) + (kk & 3) * 2;  // 64-col box, 32 B per step
+            umma_ss_elect<false>(tm_s[i], dq + off, dk + off, IDESC_S, kk != 0);
+          }
         }
         tc_commit_elect(&s_full[i]);
       };
@@ -205,9 +222,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int h = 0; h < 2; ++h) {
           mbar_wait(&p_full[2 * i + h], parity, p.status, SITE_FWD_P_FULL);
           tc_fence_after();
+          if constexpr (FP8) {
 #pragma unroll
-          for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
-            umma_ts_f16_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
+            for (int kk = 2 * h; kk < 2 * h + 2; ++kk)  // 32 keys per MMA: 8 TMEM columns of P, 32 B of the V rows
+              umma_ts_f8_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * 2, IDESC_O, (accum | kk) != 0);
+          } else {
+#pragma unroll
+            for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
+              umma_ts_f16_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
+          }
         }
       };
       auto advance = [&]() { if (++s == NST) { s = 0; ph ^= 1u; } };
@@ -322,7 +345,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float m_new = fmaxf(m_ref, mx * scale);
         // lazy rescale of the accumulator (the ld/st below are warp collectives, so the warp
         // rescales if any of its rows has to)
-        const bool grow = (m_new - m_ref) > kRescaleThreshold;  // true on the first block (m_ref = -inf)
+        // true on the first block (m_ref = -inf).  The 8-bit forward follows the exact running maximum,
+        // as the reference does: the 2-bit mantissa of P makes its rounding depend on the scale
+        const bool grow = FP8 ? (m_new > m_ref) : ((m_new - m_ref) > kRescaleThreshold);
         if (__any_sync(0xffffffffu, grow)) {
           const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
           if (grow) { m_ref = m_new; l *= alpha; }
@@ -348,9 +373,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
             const float p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));
             sum4[k & 3] += p0 + p1;
-            wv[k] = pack2<BF16>(p0, p1);
+            if constexpr (FP8) {  // keep the values; four are packed into one column below
+              r[c + 2 * k] = __float_as_uint(p0);
+              r[c + 2 * k + 1] = __float_as_uint(p1);
+            } else {
+              wv[k] = pack2<BF16>(p0, p1);
+            }
           }
-          tmem_st16(tm_s[i] + lane_addr + (c >> 1), wv);
+          if constexpr (FP8) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              wv[k] = pack4_e5m2(__uint_as_float(r[c + 4 * k]), __uint_as_float(r[c + 4 * k + 1]),
+                                 __uint_as_float(r[c + 4 * k + 2]), __uint_as_float(r[c + 4 * k + 3]));
+            tmem_st8(tm_s[i] + lane_addr + (c >> 2), wv);
+          } else {
+            tmem_st16(tm_s[i] + lane_addr + (c >> 1), wv);
+          }
           if (c == 32 || c == 96) {  // a half of P is complete: its four P V MMAs may start
             tmem_st_wait();
             tc_fence_before();
@@ -376,6 +414,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // 5200 clk per item at D = 128.
         uint8_t* stg = sstage + warp * Cfg::STG_BYTES;
         const int warp_row0 = qb * 256 + i * BLK + quarter * 32;
+        if constexpr (FP8) {
+          // 8-bit O: the 128 columns of a row are one 128-byte line of the staging buffer
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(tm_o[i] + lane_addr + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int ch = 0; ch < 2; ++ch) {
+              uint32_t wv[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                wv[k] = pack4_e5m2(__uint_as_float(o[16 * ch + 4 * k]) * inv_l, __uint_as_float(o[16 * ch + 4 * k + 1]) * inv_l,
+                                   __uint_as_float(o[16 * ch + 4 * k + 2]) * inv_l, __uint_as_float(o[16 * ch + 4 * k + 3]) * inv_l);
+              *reinterpret_cast<uint4*>(stg + sw128_offset(lane, (c >> 4) + ch)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && warp_row0 < p.N) {
+            tma_store_4d(&tm_o_map, stg, 0, warp_row0, it.h, it.z);
+            tma_store_commit();
+          }
+        } else
 #pragma unroll 1
         for (int c = 0; c < D; c += 64) {
           uint32_t o[64];
@@ -405,7 +469,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint32_t o[32];
           tmem_ld32(tm_o[i] + lane_addr + c, o);
           tmem_ld_wait();
-          if (valid) {
+          if (valid && FP8) {
+            uint8_t* brow = reinterpret_cast<uint8_t*>(p.o) + (long long)it.z * p.o_sz + (long long)it.h * p.o_sh +
+                            (long long)row * p.o_sn + c;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t wq = pack4_e5m2(__uint_as_float(o[4 * k]) * inv_l, __uint_as_float(o[4 * k + 1]) * inv_l,
+                                             __uint_as_float(o[4 * k + 2]) * inv_l, __uint_as_float(o[4 * k + 3]) * inv_l);
+              for (int b = 0; b < 4; ++b) brow[4 * k + b] = (uint8_t)(wq >> (8 * b));
+            }
+          } else if (valid) {
             uint32_t wv[16];
 #pragma unroll
             for (int k = 0; k < 16; ++k)
@@ -438,18 +511,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 }
 
-template <int D, bool BF16>
+template <int D, bool BF16, bool FP8 = false>
 int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, const CUtensorMap& tk,
                  const CUtensorMap& tv, const CUtensorMap& to, const FwdParams& p) {
   static bool attr_done[64] = {};
-  constexpr size_t smem = FwdCfg<D>::SMEM;
+  constexpr size_t smem = FwdCfg<D, FP8>::SMEM;
   if (!attr_done[ctx->device]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D, BF16, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(attn fwd): %s", cudaGetErrorString(e));
     attr_done[ctx->device] = true;
   }
   const int grid = p.total_items < ctx->sm_count ? p.total_items : ctx->sm_count;
-  attn_fwd_kernel<D, BF16><<<grid, FWD_THREADS, smem, stream>>>(tq, tk, tv, to, p);
+  attn_fwd_kernel<D, BF16, FP8><<<grid, FWD_THREADS, smem, stream>>>(tq, tk, tv, to, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn fwd launch: %s", cudaGetErrorString(e));
   return B200_OK;
@@ -460,7 +533,8 @@ int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, con
 bool encode_rows_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
                      int64_t sn, int box_cols, int box_rows, bool swizzle128) {
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)N, (uint64_t)H, (uint64_t)Z};
-  uint64_t strides[3] = {(uint64_t)sn * 2, (uint64_t)sh * 2, (uint64_t)sz * 2};
+  const uint64_t eb = (uint64_t)dtype_bytes(dtype);
+  uint64_t strides[3] = {(uint64_t)sn * eb, (uint64_t)sh * eb, (uint64_t)sz * eb};
   uint32_t box[4] = {(uint32_t)box_cols, (uint32_t)box_rows, 1, 1};
   return encode_tmap(out, dtype, 4, base, dims, strides, box, swizzle128);
 }
@@ -474,6 +548,30 @@ bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H,
 int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,
                     float* m, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
                     const int64_t* so, float sm_scale, int causal, int dtype) {
+  if (dtype == B200_E5M2) {
+    // 8-bit forward: rows of 128 bytes; V is addressed as [D rows][N keys] (keys contiguous)
+    if (D != 128) return fail(B200_ERR_UNSUPPORTED, "the 8-bit forward has a kernel for head dim 128 only");
+    if (sq[3] != 1 || sk[3] != 1 || so[3] != 1) return fail(B200_ERR_UNSUPPORTED, "8-bit q, k, o need a contiguous head dimension");
+    if (sv[2] != 1 && N != 1) return fail(B200_ERR_UNSUPPORTED, "an 8-bit v needs its key dimension contiguous (stride_v[2] == 1)");
+    CUtensorMap tq8, tk8, tv8, to8;
+    if (!encode_rows_map(&tq8, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], 128, BLK, true)) return B200_ERR_UNSUPPORTED;
+    if (!encode_rows_map(&tk8, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], 128, BLK, true)) return B200_ERR_UNSUPPORTED;
+    // "rows" of the V map are head-dim indices, "columns" are keys
+    if (!encode_rows_map(&tv8, dtype, v, Z, H, D, N, sv[0], sv[1], sv[3], 128, 128, true)) return B200_ERR_UNSUPPORTED;
+    FwdParams p8{};
+    p8.o_tma = encode_rows_map(&to8, dtype, o, Z, H, N, D, so[0], so[1], so[2], 128, 32, true) ? 1 : 0;
+    if (!p8.o_tma) to8 = tq8;
+    p8.o = o; p8.m = m;
+    p8.o_sz = so[0]; p8.o_sh = so[1]; p8.o_sn = so[2];
+    p8.Z = Z; p8.H = H; p8.N = N; p8.causal = causal;
+    p8.scale_log2 = sm_scale * 1.44269504f;
+    p8.num_qb = (N + 255) / 256;
+    p8.total_items = p8.num_qb * Z * H;
+    p8.status = ctx->status;
+    p8.sched_counter = next_sched_counter(ctx, stream);
+    if (!p8.sched_counter) return B200_ERR_CUDA;
+    return launch_fwd_t<128, false, true>(ctx, stream, tq8, tk8, tv8, to8, p8);
+  }
   CUtensorMap tq, tk, tv;
   if (!encode_qkv_map(&tq, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], BLK)) return B200_ERR_UNSUPPORTED;
   if (!encode_qkv_map(&tk, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], BLK)) return B200_ERR_UNSUPPORTED;

@@ -119,7 +119,8 @@ bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const 
   switch (dtype) {
     case B200_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
     case B200_BF16: dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16; break;
-    case B200_E4M3: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
+    case B200_E4M3:
+    case B200_E5M2: dt = CU_TENSOR_MAP_DATA_TYPE_UINT8; break;
     case B200_F32: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32; break;
     default: fail(B200_ERR_ARG, "bad dtype %d", dtype); return false;
   }
@@ -273,11 +274,12 @@ int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const
                        int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
                        const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal, int dtype) {
   if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
-  if (dtype != B200_F16 && dtype != B200_BF16) return fail(B200_ERR_ARG, "attention dtype must be F16 or BF16");
+  if (dtype != B200_F16 && dtype != B200_BF16 && dtype != B200_E5M2)
+    return fail(B200_ERR_ARG, "forward attention dtype must be F16, BF16 or E5M2");
   if (D != 64 && D != 128) return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
   if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
   if (!stride_q || !stride_k || !stride_v || !stride_o) return fail(B200_ERR_ARG, "null stride array");
-  if (stride_q[3] != 1 || stride_k[3] != 1 || stride_v[3] != 1 || stride_o[3] != 1)
+  if (dtype != B200_E5M2 && (stride_q[3] != 1 || stride_k[3] != 1 || stride_v[3] != 1 || stride_o[3] != 1))
     return fail(B200_ERR_UNSUPPORTED, "the head dimension must be contiguous");
   DeviceCtx* ctx = current_ctx();
   if (!ctx) return B200_ERR_DEVICE;

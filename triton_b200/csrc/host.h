@@ -35,7 +35,8 @@ inline int dtype_bytes(int dt) {
   switch (dt) {
     case B200_F16:
     case B200_BF16: return 2;
-    case B200_E4M3: return 1;
+    case B200_E4M3:
+    case B200_E5M2: return 1;
     case B200_F32: return 4;
     default: return 0;
   }

@@ -18,6 +18,8 @@ from . import _lib
 _DT = {torch.float16: _lib.F16, torch.bfloat16: _lib.BF16, torch.float32: _lib.F32}
 if hasattr(torch, "float8_e4m3fn"):
     _DT[torch.float8_e4m3fn] = _lib.E4M3
+if hasattr(torch, "float8_e5m2"):
+    _DT[torch.float8_e5m2] = _lib.E5M2
 _ACT = {"": _lib.ACT_NONE, None: _lib.ACT_NONE, "leaky_relu": _lib.ACT_LEAKY_RELU}
 
 
@@ -194,11 +196,20 @@ def attention_forward(q, k, v, causal, sm_scale):
     assert q.dim() == 4 and k.shape == q.shape and v.shape == q.shape, "q, k, v must be [Z, H, N, D] of one shape"
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
     assert HEAD_DIM_K in {16, 32, 64, 128, 256}  # the reference's set; this library has kernels for 64 and 128
-    assert q.dtype in (torch.float16, torch.bfloat16) and k.dtype == q.dtype and v.dtype == q.dtype
+    fp8 = hasattr(torch, "float8_e5m2") and q.dtype == torch.float8_e5m2
+    assert (q.dtype in (torch.float16, torch.bfloat16) or fp8) and k.dtype == q.dtype and v.dtype == q.dtype
     dev = _require_cuda(q, k, v)
     Z, H, N, D = q.shape
     with torch.cuda.device(dev):
-        o = torch.empty_like(q)
+        if fp8:
+            # the reference's fp8 forward (06-fused-attention.py:609-615) is given V with the key
+            # dimension contiguous; any other V is brought into that layout first
+            assert D == 128, "the 8-bit forward has a kernel for head dim 128"
+            if v.stride(2) != 1:
+                v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+            o = torch.empty((Z, H, N, D), device=dev, dtype=q.dtype)
+        else:
+            o = torch.empty_like(q)
         M = torch.empty((Z, H, N), device=dev, dtype=torch.float32)
         code = _lib.lib().b200_attention_fwd(
             _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), M.data_ptr(), Z, H, N, D,
