@@ -32,7 +32,7 @@ extern "C" {
 typedef struct CUstream_st* b200_stream_t; /* a cudaStream_t / CUstream */
 
 enum b200_dtype { B200_F16 = 0, B200_BF16 = 1, B200_E4M3 = 2, B200_F32 = 3, B200_E5M2 = 4 };
-enum b200_activation { B200_ACT_NONE = 0, B200_ACT_LEAKY_RELU = 1 };
+enum b200_activation { B200_ACT_NONE = 0, B200_ACT_LEAKY_RELU = 1, B200_ACT_SOFTMAX = 2 };
 enum b200_bias { B200_BIAS_NONE = 0, B200_BIAS_MATRIX = 1, B200_BIAS_ROWS = 2, B200_BIAS_COLS = 3 };
 enum b200_error {
   B200_OK = 0,
@@ -89,7 +89,11 @@ B200_API int b200_matmul_splitk(b200_stream_t stream, const void* a, const void*
  * B200_BIAS_ROWS reads one value per output row (n ignored), B200_BIAS_COLS one per column
  * (m ignored), B200_BIAS_NONE makes this b200_matmul_splitk.  out_dtype B200_E4M3 (8-bit output,
  * python/tutorials/09-persistent-matmul.py: `c = accumulator.to(tl.float8e4nv)`, round to nearest
- * even, saturating) is accepted here, by b200_matmul and by b200_matmul_splitk, without a bias. */
+ * even, saturating) is accepted here, by b200_matmul and by b200_matmul_splitk, without a bias.
+ * activation B200_ACT_SOFTMAX is the reference's 'softmax' epilogue (test_gemm.py:223-228): a
+ * softmax over every output row, computed like the reference in the output type (F16, BF16 or
+ * F32); it needs N <= 256 (one tile spans the row), no bias, splits == 1 and TMA-addressable
+ * operands. */
 B200_API int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                               int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
                               int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,

@@ -152,7 +152,22 @@ def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8, bi
         c[m0:m0 + mm, n0:n0 + nn] = acc[:mm, :nn]
     if bias is not None:
         return add_bias(c, bias, out)
+    if activation == "softmax":
+        return softmax_epilogue(c, out)
     return ROUND[out](c) if out in ROUND else c
+
+
+def softmax_epilogue(c, out):
+    """The 'softmax' epilogue of python/test/unit/hopper/test_gemm.py:223-228 on the fp32 product:
+    z = c.to(out); z = z - max(z, 1); num = exp(z.to(fp32)).to(out); den = sum(num, 1);
+    z = num / den, every step rounded to the output type (the row sum is accumulated in fp32 and
+    rounded once)."""
+    rnd = ROUND.get(out, lambda v: np.asarray(v, dtype=np.float32))
+    z = rnd(c)
+    z = rnd(z - z.max(axis=1, keepdims=True))
+    num = rnd(np.exp(z, dtype=np.float32))
+    den = rnd(num.sum(axis=1, keepdims=True, dtype=np.float32))
+    return rnd(num / den)
 
 
 def matmul_fp8(a_bits, b_bits, scale_a=None, scale_b=None, out="bf16", BM=128, BN=256, BK=128):

@@ -449,3 +449,34 @@ def test_grouped_matmul_layout_errors_and_strided_operands():
     assert torch.equal(c, triton_b200.matmul(av.contiguous(), bv.contiguous()))
     assert triton_b200.group_gemm_fn([], []) == []
     status_ok()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(64, 64, 64), (128, 128, 128), (16, 16, 64), (300, 200, 136), (1000, 256, 520)])
+def test_softmax_epilogue(dtype, shape):
+    """The reference's 'softmax' epilogue (test_gemm.py:223-228; its shapes at :268-272 plus ragged
+    ones and more than one wave of row tiles): a softmax over every row of the product."""
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M + N + K)
+    a = (torch.randn(M, K, generator=g) / K ** 0.25).half()
+    b = (torch.randn(K, N, generator=g) / K ** 0.25).half()
+    got = triton_b200.matmul(a.to(DEV), b.to(DEV), activation="softmax", out_dtype=dtype)
+    status_ok()
+    out = {torch.float16: "fp16", torch.bfloat16: "bf16", torch.float32: "fp32"}[dtype]
+    want = R.matmul(f32(a), f32(b), activation="softmax", out=out)
+    gotf = f32(got)
+    np.testing.assert_allclose(gotf.sum(1), 1.0, atol=2e-2)
+    # the reference's check: rows normalised to unit length, rtol 1e-2, atol 1e-3 (bf16: its coarser ulp)
+    nz = lambda x: x / np.linalg.norm(x, axis=1, keepdims=True)
+    np.testing.assert_allclose(nz(gotf), nz(want), rtol=2e-2 if dtype == torch.bfloat16 else 1e-2,
+                               atol=4e-3 if dtype == torch.bfloat16 else 1e-3)
+    exact = torch.softmax(a.float() @ b.float(), dim=1).numpy()
+    np.testing.assert_allclose(gotf, exact, rtol=3e-2, atol=2e-3)
+
+
+def test_softmax_epilogue_errors():
+    a = torch.zeros(64, 64, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError, match="N <= 256"):
+        triton_b200.matmul(a, torch.zeros(64, 512, dtype=torch.float16, device=DEV), activation="softmax")
+    with pytest.raises(RuntimeError, match="no bias"):
+        triton_b200.matmul(a, a, activation="softmax", bias=torch.zeros(1, 64, dtype=torch.float16, device=DEV))

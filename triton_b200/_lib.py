@@ -11,7 +11,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libtriton_b200.so")
 
 F16, BF16, E4M3, F32, E5M2 = 0, 1, 2, 3, 4
-ACT_NONE, ACT_LEAKY_RELU = 0, 1
+ACT_NONE, ACT_LEAKY_RELU, ACT_SOFTMAX = 0, 1, 2
 BIAS_NONE, BIAS_MATRIX, BIAS_ROWS, BIAS_COLS = 0, 1, 2, 3
 
 _i, _i64, _p, _f = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_float

@@ -233,7 +233,14 @@ int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c
     return fail(B200_ERR_ARG, "in_dtype must be F16, BF16 or E4M3");
   if (out_dtype != B200_F16 && out_dtype != B200_BF16 && out_dtype != B200_F32 && out_dtype != B200_E4M3)
     return fail(B200_ERR_ARG, "out_dtype must be F16, BF16, F32 or E4M3");
-  if (activation != B200_ACT_NONE && activation != B200_ACT_LEAKY_RELU) return fail(B200_ERR_ARG, "bad activation");
+  if (activation != B200_ACT_NONE && activation != B200_ACT_LEAKY_RELU && activation != B200_ACT_SOFTMAX)
+    return fail(B200_ERR_ARG, "bad activation");
+  if (activation == B200_ACT_SOFTMAX) {
+    if (N > 256) return fail(B200_ERR_UNSUPPORTED, "the softmax epilogue needs N <= 256 (one tile spans the row)");
+    if (bias_mode != B200_BIAS_NONE || splits != 1 || out_dtype == B200_E4M3)
+      return fail(B200_ERR_ARG, "the softmax epilogue takes no bias, no split-K and a 16- or 32-bit output");
+    if (K == 0) return fail(B200_ERR_UNSUPPORTED, "softmax epilogue with K == 0");
+  }
   DeviceCtx* ctx = current_ctx();
   if (!ctx) return B200_ERR_DEVICE;
   if (M == 0 || N == 0) return B200_OK;

@@ -246,6 +246,54 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
   }
 }
 
+// Row-softmax epilogue (python/test/unit/hopper/test_gemm.py:223-228, 'softmax'): the whole row is
+// in this tile (N <= tile width), one thread per row.  As the reference: z = out_type(acc);
+// z -= max(z) in the output type; num = out_type(exp(fp32(z))); z = num / sum(num).  Three passes
+// over the accumulator in TMEM (maximum, sum, write).
+__device__ __forceinline__ void drain_softmax(const GemmParams& p, uint32_t taddr, int row0, int lane, float scale) {
+  const int row = row0 + lane;
+  const int nchunks = (p.N + 31) / 32;
+  float mx = -INFINITY;
+  for (int ch = 0; ch < nchunks; ++ch) {
+    uint32_t r[32];
+    tmem_ld32(taddr + ch * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (ch * 32 + j < p.N) mx = fmaxf(mx, round_out(__uint_as_float(r[j]) * scale, p.out_dtype));
+  }
+  float den = 0.f;
+  for (int ch = 0; ch < nchunks; ++ch) {
+    uint32_t r[32];
+    tmem_ld32(taddr + ch * 32, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (ch * 32 + j < p.N) {
+        const float z = round_out(round_out(__uint_as_float(r[j]) * scale, p.out_dtype) - mx, p.out_dtype);
+        den += round_out(__expf(z), p.out_dtype);
+      }
+  }
+  den = round_out(den, p.out_dtype);
+  for (int ch = 0; ch < nchunks; ++ch) {
+    uint32_t r[32];
+    tmem_ld32(taddr + ch * 32, r);
+    tmem_ld_wait();
+    if (row >= p.M) continue;
+#pragma unroll 4
+    for (int j = 0; j < 32; ++j) {
+      const int col = ch * 32 + j;
+      if (col >= p.N) break;
+      const float z = round_out(round_out(__uint_as_float(r[j]) * scale, p.out_dtype) - mx, p.out_dtype);
+      const float v = round_out(__expf(z), p.out_dtype) / den;
+      const long long o = (long long)row * p.ldc + col;
+      if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
+      else if (p.out_dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
+      else reinterpret_cast<__half*>(p.c)[o] = __float2half_rn(v);
+    }
+  }
+}
+
 // split-K: one epilogue warp writes its 32 rows of raw fp32 partial sums to a dense [M][N] slice
 __device__ __forceinline__ void drain_partial(float* ws, int M, int N, uint32_t taddr, int ncols, int row0, int col0,
                                               int lane) {
@@ -414,6 +462,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         drain_partial(p.ws + (long long)split * p.M * p.N, p.M, p.N,
                       tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
                       pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane);
+      } else if (EXT && p.activation == B200_ACT_SOFTMAX) {
+        drain_softmax(p, tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN,
+                      pid_m * BM + half * 128 + quarter * 32, lane, scale);
       } else
       drain_accumulator<EXT>(p, &tma_c, staging + (warp - 2) * STG_BYTES,
                         tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
@@ -892,7 +943,8 @@ int launch_pair_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, co
 template <int BM, int BN, int STAGES>
 int launch_tile(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_,
                 const CUtensorMap& tc, GemmParams& p) {
-  if (p.bias_mode || p.out_dtype == B200_E4M3) return launch_tile_t<BM, BN, STAGES, true>(ctx, stream, ta, tb_, tc, p);
+  if (p.bias_mode || p.out_dtype == B200_E4M3 || p.activation == B200_ACT_SOFTMAX)
+    return launch_tile_t<BM, BN, STAGES, true>(ctx, stream, ta, tb_, tc, p);
   return launch_tile_t<BM, BN, STAGES, false>(ctx, stream, ta, tb_, tc, p);
 }
 template <int STAGES, int NB>
@@ -937,6 +989,8 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   const bool a_ok = tma_ok(a, a_mn ? sak : sam) || (a_mn ? K : M) == 1;
   const bool b_ok = tma_ok(b, b_mn ? sbk : sbn) || (b_mn ? K : N) == 1;
   if (!a_ok || !b_ok || (a_mn && sam != 1) || (b_mn && sbn != 1) || env_int("B200_GEMM_PLAIN", 0)) {
+    if (activation == B200_ACT_SOFTMAX)
+      return fail(B200_ERR_UNSUPPORTED, "the softmax epilogue needs operands that TMA can address");
     GemmParams q{};
     q.c = c; q.M = M; q.N = N; q.K = K; q.ldc = scm;
     q.out_dtype = out_dtype; q.activation = activation;
@@ -956,7 +1010,9 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   bool pair = false;
   const int force = env_int("B200_GEMM_TILE", 0);
   int pair_nb = 1;  // 256-column MMAs per pair tile
-  if (splits > 1) {
+  if (activation == B200_ACT_SOFTMAX) {
+    bm = 128; bn = N <= 64 ? 64 : (N <= 128 ? 128 : 256);  // one tile spans the row
+  } else if (splits > 1) {
     bm = 128; bn = 64;  // split-K serves skinny problems: the shape with the most tiles
   } else if (force == 2256 || force == 2512) {
     pair = true;
@@ -1021,8 +1077,8 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   // C through TMA stores when it is a 16-bit output that a tensor map can describe
   CUtensorMap tcm = ta;  // a valid map even when unused
   p.c_tma = 0;
-  if ((out_dtype == B200_F16 || out_dtype == B200_BF16) && (reinterpret_cast<uintptr_t>(c) & 15) == 0 && ((scm * 2) & 15) == 0 &&
-      !env_int("B200_GEMM_DIRECT_STORE", 0)) {
+  if (activation != B200_ACT_SOFTMAX && (out_dtype == B200_F16 || out_dtype == B200_BF16) &&
+      (reinterpret_cast<uintptr_t>(c) & 15) == 0 && ((scm * 2) & 15) == 0 && !env_int("B200_GEMM_DIRECT_STORE", 0)) {
     uint64_t dims[2] = {(uint64_t)N, (uint64_t)M}, strides[1] = {(uint64_t)scm * 2};
     uint32_t box[2] = {64, 32};
     if (encode_tmap(&tcm, out_dtype, 2, c, dims, strides, box, true)) p.c_tma = 1;

@@ -20,7 +20,7 @@ if hasattr(torch, "float8_e4m3fn"):
     _DT[torch.float8_e4m3fn] = _lib.E4M3
 if hasattr(torch, "float8_e5m2"):
     _DT[torch.float8_e5m2] = _lib.E5M2
-_ACT = {"": _lib.ACT_NONE, None: _lib.ACT_NONE, "leaky_relu": _lib.ACT_LEAKY_RELU}
+_ACT = {"": _lib.ACT_NONE, None: _lib.ACT_NONE, "leaky_relu": _lib.ACT_LEAKY_RELU, "softmax": _lib.ACT_SOFTMAX}
 
 
 def _stream(t):
@@ -47,6 +47,8 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
     fp8-e4m3 inputs take optional per-tensor dequantisation scales (`scale_a`, `scale_b`:
     python floats or 1-element fp32 CUDA tensors) that the epilogue multiplies in.
     `out_dtype=torch.float8_e4m3fn` stores an 8-bit C (round to nearest even, saturating).
+    `activation="softmax"` is the reference's 'softmax' epilogue (test_gemm.py:223-228): a softmax
+    over every row of the product (N <= 256).
     `bias` is the reference's epilogue addend (test_gemm.py 'add-matrix' / 'add-rows' /
     'add-cols'): a tensor of the output type and shape [M, N], [M, 1] (one value per row) or
     [1, N] (one per column), added after the conversion to the output type.
@@ -90,8 +92,9 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
             bias_ptr, bias_sm, bias_sn = bias.data_ptr(), bias.stride(0), bias.stride(1)
         # skinny problems (few tiles, long K) are split along K; the fp32 partial tiles need scratch
         splits, ws_bytes = ctypes.c_int(1), ctypes.c_size_t(0)
-        _lib.check(_lib.lib().b200_matmul_plan(M, N, K, _DT[a.dtype], ctypes.byref(splits), ctypes.byref(ws_bytes)),
-                   "matmul_plan")
+        if activation != "softmax":  # the row softmax needs the whole K range in one tile
+            _lib.check(_lib.lib().b200_matmul_plan(M, N, K, _DT[a.dtype], ctypes.byref(splits), ctypes.byref(ws_bytes)),
+                       "matmul_plan")
         ws = torch.empty(ws_bytes.value // 4, device=dev, dtype=torch.float32) if splits.value > 1 else None
         code = _lib.lib().b200_matmul_bias(
             _stream(a), a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K,
