@@ -241,3 +241,22 @@ def test_forward_e5m2_errors():
     x = torch.zeros(1, 1, 128, 64, device=DEV).to(torch.float8_e5m2)
     with pytest.raises(AssertionError, match="head dim 128"):
         triton_b200.attention_forward(x, x, x, True, 0.5)
+
+
+def test_long_sequence_forward_sampled_rows():
+    """N = 65536 (512 key blocks per row, 4.3e9 scores per head): sampled query rows against a
+    dense fp32 softmax over all keys."""
+    Z, H, N, D = 1, 2, 65536, 64
+    g = torch.Generator(device=DEV).manual_seed(2)
+    q, k, v = ((torch.randn(Z, H, N, D, generator=g, device=DEV) * 0.5).half() for _ in range(3))
+    sm_scale = D ** -0.5
+    for causal in (True, False):
+        o, M = triton_b200.attention_forward(q, k, v, causal, sm_scale)
+        status_ok()
+        rows = torch.tensor([0, 1, 127, 128, 40000, N - 129, N - 1], device=DEV)
+        s = (q[:, :, rows].float() @ k.float().transpose(2, 3)) * sm_scale          # [Z, H, R, N]
+        if causal:
+            s = s.masked_fill(torch.arange(N, device=DEV)[None, None, None, :] > rows[None, None, :, None], float("-inf"))
+        want = torch.softmax(s, -1) @ v.float()
+        np.testing.assert_allclose(f32(o[:, :, rows]), f32(want), rtol=1e-2, atol=1e-2)
+        np.testing.assert_allclose(f32(M[:, :, rows]), f32(torch.logsumexp(s, -1) / math.log(2.0)), rtol=1e-4, atol=1e-3)

@@ -480,3 +480,26 @@ def test_softmax_epilogue_errors():
         triton_b200.matmul(a, torch.zeros(64, 512, dtype=torch.float16, device=DEV), activation="softmax")
     with pytest.raises(RuntimeError, match="no bias"):
         triton_b200.matmul(a, a, activation="softmax", bias=torch.zeros(1, 64, dtype=torch.float16, device=DEV))
+
+
+def test_output_with_more_than_2_31_elements():
+    """Index arithmetic past 32 bits: C has 46400^2 = 2.15e9 elements (4.3 GB); sampled entries are
+    compared with fp64 dot products, through the TMA-store epilogue and the direct-store one."""
+    M = N = 46400
+    K = 64
+    g = torch.Generator(device=DEV).manual_seed(1)
+    a = torch.randn(M, K, generator=g, device=DEV).half()
+    b = torch.randn(K, N, generator=g, device=DEV).half()
+    rows = torch.tensor([0, 1, 12345, 46271, 46272, M - 1], device=DEV)
+    cols = torch.tensor([0, 7, 33333, 46399], device=DEV)
+    want = (a[rows].double() @ b[:, cols].double()).cpu().numpy()
+    for out_dtype in (torch.float16, torch.float32):   # TMA stores / direct stores
+        c = triton_b200.matmul(a, b, out_dtype=out_dtype)
+        status_ok()
+        got = c[rows][:, cols].double().cpu().numpy()
+        np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2)
+        # the far corner block is written and nothing else was clobbered: checksum of the last rows
+        tail = c[-64:].float()
+        np.testing.assert_allclose(tail.cpu().numpy(), (a[-64:].float() @ b.float()).cpu().numpy(), rtol=1e-2, atol=1e-2)
+        del c, tail
+        torch.cuda.empty_cache()
