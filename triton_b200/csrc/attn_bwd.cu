@@ -14,11 +14,12 @@
 //   a ring as pairs (U1, U2) of 128 x D tiles.  Per step
 //       T1 = R1 U1^T        (scores: S^T = K Q^T, or S = Q K^T)
 //       T2 = R2 U2^T        (dP^T = V dO^T, or dP = dO V^T)
-//       P  = exp2(T1 * scale - M) masked;   dS = P * (T2 - delta)       (fp32, one thread per row)
+//       P  = exp2(T1 * scale - M) masked;   dS = P * (T2 - delta)       (fp32, two threads per row)
 //       accB += P  U2       (dV += P^T dO; dK/dV kernel only)
 //       accA += dS U1       (dK += dS^T Q, or dQ += dS K)
-//   T1/T2 live in TMEM and P/dS overwrite them as 16-bit A operands of the last two MMAs, which
-//   read U1/U2 through an N-major view of the same shared-memory tiles.
+//   T1/T2 live in TMEM and P/dS overwrite them as 16-bit A operands of the last two MMAs (each
+//   thread over the first 32 of its own 64 columns), which read U1/U2 through an N-major view of
+//   the same shared-memory tiles.  Gradients leave through staging buffers and TMA stores.
 // Warps 0-7 compute (two threads per row, splitting the columns), warp 8 issues MMAs, warp 9 runs TMA.
 #include <cmath>
 #include <mutex>
