@@ -260,3 +260,40 @@ def test_long_sequence_forward_sampled_rows():
         want = torch.softmax(s, -1) @ v.float()
         np.testing.assert_allclose(f32(o[:, :, rows]), f32(want), rtol=1e-2, atol=1e-2)
         np.testing.assert_allclose(f32(M[:, :, rows]), f32(torch.logsumexp(s, -1) / math.log(2.0)), rtol=1e-4, atol=1e-3)
+
+
+def test_ops_replay_from_a_cuda_graph():
+    """The reference benchmarks attention with do_bench_cudagraph (test_performance.py:199): the ops
+    must be capturable.  Forward, backward and a split-K matmul are captured once and replayed on
+    new input values; results equal the eager ones bit for bit."""
+    Z, H, N, D = 1, 2, 512, 64
+    g = torch.Generator(device=DEV).manual_seed(4)
+    q, k, v, do = ((torch.randn(Z, H, N, D, generator=g, device=DEV) * 0.5).to(torch.bfloat16) for _ in range(4))
+    a = torch.randn(16, 4096, generator=g, device=DEV).half()
+    b = torch.randn(4096, 256, generator=g, device=DEV).half()
+
+    def step():
+        o, M = triton_b200.attention_forward(q, k, v, True, 0.125)
+        dq, dk, dv = triton_b200.attention_backward(q, k, v, o, M, do, True, 0.125)
+        return o, dq, dk, dv, triton_b200.matmul(a, b)
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()  # first calls outside capture (function attributes, context)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        outs = step()
+    for trial in range(2):
+        q.copy_((torch.randn(Z, H, N, D, generator=g, device=DEV) * 0.5).to(torch.bfloat16))
+        a.copy_(torch.randn(16, 4096, generator=g, device=DEV).half())
+        graph.replay()
+        torch.cuda.synchronize()
+        eager = step()
+        for x, y in zip(outs, eager):
+            assert torch.equal(x, y)
+    status_ok()
+    # the older six-argument signature
+    o6 = triton_b200.attention(q, k, v, True, 0.125, True)
+    assert torch.equal(o6, eager[0])

@@ -262,4 +262,10 @@ class _attention(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
-attention = _attention.apply
+def attention(q, k, v, causal, sm_scale, sequence_parallel=False):
+    """O = softmax(Q K^T * sm_scale [causal]) V, differentiable: the reference's
+    `attention = _attention.apply` (06-fused-attention.py:520).  The sixth argument is the older
+    `triton.ops.attention(q, k, v, causal, sm_scale, sequence_parallel)` signature
+    (python/test/regression/test_performance.py:194); it changes nothing here: both backward
+    kernels are parallel over 128-row blocks of the sequence in either case."""
+    return _attention.apply(q, k, v, causal, sm_scale)
