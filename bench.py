@@ -262,6 +262,18 @@ def run_profile_case(name):
         def fn():
             o, m = tb.attention_forward(q, k, v, True, 0.5)
             tb.attention_backward(q, k, v, o, m, do, True, 0.5)
+    elif name == "fp8attn":  # the 8-bit forward on config 4's shape (the reference's fp8 benchmark scale 1.3)
+        q, k, v = ((torch.randn(4, 32, 4096, 128, generator=g) * 0.5).to(dev).to(torch.float8_e5m2) for _ in range(3))
+        v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+        fn = lambda: tb.attention_forward(q, k, v, True, 1.3)
+    elif name == "grouped":  # 64 problems of 512^3 in one launch
+        ga = [torch.rand(512, 512, generator=g).half().to(dev) for _ in range(64)]
+        gb = [torch.rand(512, 512, generator=g).half().to(dev) for _ in range(64)]
+        fn = lambda: tb.group_gemm_fn(ga, gb)
+    elif name == "skinny":  # split-K: 256 x 256 x 8192
+        a = (torch.randn(256, 8192, generator=g) / 90).half().to(dev)
+        b = (torch.randn(8192, 256, generator=g) / 90).half().to(dev)
+        fn = lambda: tb.matmul(a, b)
     else:
         raise SystemExit("unknown profile case " + name)
     for _ in range(3):
@@ -373,7 +385,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the short timings of configs 1, 3, 4, 5")
-    ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5"],
+    ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5", "fp8attn", "grouped", "skinny"],
                     help="run three launches of one configuration and exit (for ncu captures)")
     args = ap.parse_args()
     # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm and the cpu_baseline leg are meant to
