@@ -116,6 +116,17 @@ B200_API size_t b200_grouped_matmul_workspace(int group_count);
 B200_API int b200_grouped_matmul(b200_stream_t stream, int group_count, const void* const* a, const void* const* b,
                                  void* const* c, const int* sizes, const int* lds, int in_dtype, int out_dtype,
                                  void* workspace);
+/* The two halves of b200_grouped_matmul, for callers that run the same groups repeatedly (the
+ * reference times `triton_perf_fn`, which launches on device tensors prepared once,
+ * 08-grouped-gemm.py:218-229): _prepare writes the descriptors (pointers, sizes, tensor maps) to
+ * `workspace` and returns the tile count; _run launches on a prepared workspace and can be called
+ * any number of times while the operands stay where they were.  Groups with K == 0 are zeroed by
+ * _prepare only. */
+B200_API int b200_grouped_matmul_prepare(b200_stream_t stream, int group_count, const void* const* a,
+                                         const void* const* b, void* const* c, const int* sizes, const int* lds,
+                                         int in_dtype, int out_dtype, void* workspace, int* total_tiles);
+B200_API int b200_grouped_matmul_run(b200_stream_t stream, const void* workspace, int total_tiles, int in_dtype,
+                                     int out_dtype);
 
 /* Flash-attention forward: O = softmax(Q K^T * sm_scale, causal mask optional) V, and per-row
  * statistics M[Z,H,N] (fp32) = base-2 log-sum-exp of the scores scaled by sm_scale * log2(e)

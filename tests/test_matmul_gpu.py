@@ -503,3 +503,19 @@ def test_output_with_more_than_2_31_elements():
         np.testing.assert_allclose(tail.cpu().numpy(), (a[-64:].float() @ b.float()).cpu().numpy(), rtol=1e-2, atol=1e-2)
         del c, tail
         torch.cuda.empty_cache()
+
+
+def test_grouped_matmul_prepared_plan_reruns():
+    """GroupedMatmul: descriptors prepared once, launched repeatedly on changing operand values
+    (what the reference times as triton_perf_fn, 08-grouped-gemm.py:218-229)."""
+    shapes = [(256, 128, 64), (130, 72, 200), (512, 512, 512)]
+    A, B = _grouped_inputs(shapes, torch.float16, 3)
+    Ad, Bd = [t.to(DEV) for t in A], [t.to(DEV) for t in B]
+    plan = triton_b200.GroupedMatmul(Ad, Bd)
+    for trial in range(3):
+        for t in Ad:
+            t.uniform_(0, 1)
+        out = plan.run()
+        status_ok()
+        for a, b, c in zip(Ad, Bd, out):
+            assert torch.equal(c, triton_b200.matmul(a, b))

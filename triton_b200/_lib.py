@@ -29,6 +29,8 @@ SIGNATURES = {
                          _p, _i, _i64, _i64, _i, _p],
     "b200_grouped_matmul_workspace": [_i],
     "b200_grouped_matmul": [_p, _i, _p, _p, _p, _p, _p, _i, _i, _p],
+    "b200_grouped_matmul_prepare": [_p, _i, _p, _p, _p, _p, _p, _i, _i, _p, ctypes.POINTER(ctypes.c_int)],
+    "b200_grouped_matmul_run": [_p, _p, _i, _i, _i],
     "b200_attention_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
     "b200_attention_bwd": [_p] + [_p] * 10 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
     "b200_attention_bwd_noalloc": [_p] + [_p] * 9 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],

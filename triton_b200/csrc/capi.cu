@@ -262,19 +262,46 @@ int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c
 
 size_t b200_grouped_matmul_workspace(int group_count) { return gemm_grouped_workspace_bytes(group_count); }
 
-int b200_grouped_matmul(b200_stream_t stream, int group_count, const void* const* a, const void* const* b,
-                        void* const* c, const int* sizes, const int* lds, int in_dtype, int out_dtype,
-                        void* workspace) {
-  if (group_count < 0) return fail(B200_ERR_ARG, "negative group count");
-  if (group_count == 0) return B200_OK;
-  if (!a || !b || !c || !sizes || !lds) return fail(B200_ERR_ARG, "null array");
+static int grouped_args_ok(int in_dtype, int out_dtype) {
   if (in_dtype != B200_F16 && in_dtype != B200_BF16) return fail(B200_ERR_ARG, "grouped matmul takes F16 or BF16 inputs");
   if (out_dtype != B200_F16 && out_dtype != B200_BF16 && out_dtype != B200_F32)
     return fail(B200_ERR_ARG, "out_dtype must be F16, BF16 or F32");
+  return B200_OK;
+}
+
+int b200_grouped_matmul_prepare(b200_stream_t stream, int group_count, const void* const* a, const void* const* b,
+                                void* const* c, const int* sizes, const int* lds, int in_dtype, int out_dtype,
+                                void* workspace, int* total_tiles) {
+  if (!total_tiles) return fail(B200_ERR_ARG, "null total_tiles");
+  *total_tiles = 0;
+  if (group_count < 0) return fail(B200_ERR_ARG, "negative group count");
+  if (group_count == 0) return B200_OK;
+  if (!a || !b || !c || !sizes || !lds) return fail(B200_ERR_ARG, "null array");
+  if (int rc = grouped_args_ok(in_dtype, out_dtype)) return rc;
   DeviceCtx* ctx = current_ctx();
   if (!ctx) return B200_ERR_DEVICE;
-  return launch_gemm_grouped(ctx, reinterpret_cast<cudaStream_t>(stream), group_count, a, b, c, sizes, lds, in_dtype,
-                             out_dtype, workspace);
+  return prepare_gemm_grouped(ctx, reinterpret_cast<cudaStream_t>(stream), group_count, a, b, c, sizes, lds, in_dtype,
+                              out_dtype, workspace, total_tiles);
+}
+
+int b200_grouped_matmul_run(b200_stream_t stream, const void* workspace, int total_tiles, int in_dtype, int out_dtype) {
+  if (total_tiles < 0) return fail(B200_ERR_ARG, "negative tile count");
+  if (total_tiles == 0) return B200_OK;
+  if (!workspace) return fail(B200_ERR_ARG, "null workspace");
+  if (int rc = grouped_args_ok(in_dtype, out_dtype)) return rc;
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  return launch_gemm_grouped(ctx, reinterpret_cast<cudaStream_t>(stream), workspace, total_tiles, in_dtype, out_dtype);
+}
+
+int b200_grouped_matmul(b200_stream_t stream, int group_count, const void* const* a, const void* const* b,
+                        void* const* c, const int* sizes, const int* lds, int in_dtype, int out_dtype,
+                        void* workspace) {
+  int total_tiles = 0;
+  int rc = b200_grouped_matmul_prepare(stream, group_count, a, b, c, sizes, lds, in_dtype, out_dtype, workspace,
+                                       &total_tiles);
+  if (rc) return rc;
+  return b200_grouped_matmul_run(stream, workspace, total_tiles, in_dtype, out_dtype);
 }
 
 int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m, int Z,

@@ -1105,10 +1105,12 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
 
 size_t gemm_grouped_workspace_bytes(int group_count) { return (size_t)(group_count > 0 ? group_count : 0) * sizeof(GroupDesc); }
 
-int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, int group_count, const void* const* a,
-                        const void* const* b, void* const* c, const int* sizes, const int* lds, int in_dtype,
-                        int out_dtype, void* workspace) {
-  constexpr int BM = 128, BN = 128, STAGES = 6;
+// Writes the groups' descriptors to `workspace` (asynchronously on `stream`) and returns the number of tiles.
+int prepare_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, int group_count, const void* const* a,
+                         const void* const* b, void* const* c, const int* sizes, const int* lds, int in_dtype,
+                         int out_dtype, void* workspace, int* total_tiles_out) {
+  (void)ctx;
+  constexpr int BM = 128, BN = 128;
   const int elt = dtype_bytes(in_dtype);  // 2
   const int bk_elems = KBYTES / elt;
   std::vector<GroupDesc> descs;
@@ -1150,13 +1152,24 @@ int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, int group_count, co
     total_tiles += d.num_tiles;
     descs.push_back(d);
   }
+  *total_tiles_out = total_tiles;
   if (descs.empty()) return B200_OK;
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 127))
     return fail(B200_ERR_ARG, "grouped matmul needs a 128-byte aligned device workspace (b200_grouped_matmul_workspace)");
   // pageable host memory: the copy has left the vector when the call returns
   cudaError_t e = cudaMemcpyAsync(workspace, descs.data(), descs.size() * sizeof(GroupDesc), cudaMemcpyHostToDevice, stream);
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "descriptor copy: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
 
+// One persistent launch over the tiles described in `workspace` (prepare_gemm_grouped).
+int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, const void* workspace, int total_tiles, int in_dtype,
+                        int out_dtype) {
+  constexpr int BM = 128, BN = 128, STAGES = 6;
+  if (total_tiles <= 0) return B200_OK;
+  const int elt = dtype_bytes(in_dtype);
+  const int bk_elems = KBYTES / elt;
+  cudaError_t e;
   GemmParams p{};
   p.out_dtype = out_dtype; p.activation = B200_ACT_NONE; p.status = ctx->status;
   p.bk_elems = bk_elems; p.splits = 1;

@@ -49,9 +49,11 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
                 int64_t bias_sm, int64_t bias_sn, int splits, float* ws);
 int gemm_plan_splits(DeviceCtx* ctx, int M, int N, int K, int in_dtype);
 size_t gemm_grouped_workspace_bytes(int group_count);
-int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, int group_count, const void* const* a,
-                        const void* const* b, void* const* c, const int* sizes, const int* lds, int in_dtype,
-                        int out_dtype, void* workspace);
+int prepare_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, int group_count, const void* const* a,
+                         const void* const* b, void* const* c, const int* sizes, const int* lds, int in_dtype,
+                         int out_dtype, void* workspace, int* total_tiles_out);
+int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, const void* workspace, int total_tiles, int in_dtype,
+                        int out_dtype);
 
 int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,
                     float* m, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,

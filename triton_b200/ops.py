@@ -105,42 +105,67 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
     return c
 
 
+class GroupedMatmul:
+    """A prepared grouped matmul: the groups' descriptors (pointers, sizes, tensor maps) are written
+    to device memory once; `run()` is one persistent launch and can be repeated while the operand
+    tensors stay where they are (their values may change).  This is what the reference times as
+    `triton_perf_fn` (python/tutorials/08-grouped-gemm.py:218-229: launch only, tensors prepared
+    before).  `out` is the list of result tensors, rewritten by every run."""
+
+    def __init__(self, group_A, group_B, out_dtype=None):
+        assert len(group_A) == len(group_B) and len(group_A) > 0
+        G = len(group_A)
+        self.dev = _require_cuda(*group_A, *group_B)
+        dt = group_A[0].dtype
+        assert dt in (torch.float16, torch.bfloat16), "grouped matmul takes fp16 or bf16"
+        self.in_dt, self.out_dtype = dt, out_dtype or dt
+        self.operands = (list(group_A), list(group_B))  # kept alive: the descriptors hold their addresses
+        sizes, lds, self.out = [], [], []
+        with torch.cuda.device(self.dev):
+            for A, B in zip(group_A, group_B):
+                assert A.dim() == 2 and B.dim() == 2 and A.shape[1] == B.shape[0]
+                assert A.dtype == dt and B.dtype == dt
+                assert (A.stride(1) == 1 or A.shape[1] == 1) and (B.stride(1) == 1 or B.shape[1] == 1), "row-major operands"
+                M, K = A.shape
+                N = B.shape[1]
+                C = torch.empty((M, N), device=self.dev, dtype=self.out_dtype)
+                self.out.append(C)
+                sizes += [M, N, K]
+                lds += [A.stride(0), B.stride(0), C.stride(0)]
+            L = _lib.lib()
+            PtrArr, IntArr = ctypes.c_void_p * G, ctypes.c_int * (3 * G)
+            self.ws = torch.empty(L.b200_grouped_matmul_workspace(G) + 128, dtype=torch.uint8, device=self.dev)
+            self.ws_ptr = (self.ws.data_ptr() + 127) & ~127
+            tiles = ctypes.c_int(0)
+            code = L.b200_grouped_matmul_prepare(
+                _stream(group_A[0]), G, PtrArr(*[t.data_ptr() for t in group_A]),
+                PtrArr(*[t.data_ptr() for t in group_B]), PtrArr(*[t.data_ptr() for t in self.out]), IntArr(*sizes),
+                IntArr(*lds), _DT[dt], _DT[self.out_dtype], self.ws_ptr, ctypes.byref(tiles))
+            _lib.check(code, "grouped_matmul_prepare")
+            self.tiles = tiles.value
+
+    def run(self):
+        with torch.cuda.device(self.dev):
+            code = _lib.lib().b200_grouped_matmul_run(torch.cuda.current_stream(self.dev).cuda_stream, self.ws_ptr,
+                                                      self.tiles, _DT[self.in_dt], _DT[self.out_dtype])
+            _lib.check(code, "grouped_matmul_run")
+        return self.out
+
+
 def group_gemm_fn(group_A, group_B, out_dtype=None):
     """[A_i @ B_i for every i] in one persistent launch: the reference's grouped GEMM
     (python/tutorials/08-grouped-gemm.py:144-191, same name and argument lists): every A_i is
     [M_i, K_i] and every B_i is [K_i, N_i], row-major 2-D CUDA tensors of one 16-bit dtype; returns
     the list of new C_i (dtype of A unless `out_dtype` says otherwise).  Unlike the reference,
-    sizes need not be multiples of the tile shape."""
-    assert len(group_A) == len(group_B)
-    G = len(group_A)
-    if G == 0:
+    sizes need not be multiples of the tile shape.  (GroupedMatmul keeps the prepared descriptors
+    for repeated launches.)"""
+    if len(group_A) == 0:
+        assert len(group_B) == 0
         return []
-    dev = _require_cuda(*group_A, *group_B)
-    dt = group_A[0].dtype
-    assert dt in (torch.float16, torch.bfloat16), "grouped matmul takes fp16 or bf16"
-    out_dtype = out_dtype or dt
-    sizes, lds, group_C = [], [], []
-    with torch.cuda.device(dev):
-        for A, B in zip(group_A, group_B):
-            assert A.dim() == 2 and B.dim() == 2 and A.shape[1] == B.shape[0]
-            assert A.dtype == dt and B.dtype == dt
-            assert (A.stride(1) == 1 or A.shape[1] == 1) and (B.stride(1) == 1 or B.shape[1] == 1), "row-major operands"
-            M, K = A.shape
-            N = B.shape[1]
-            C = torch.empty((M, N), device=dev, dtype=out_dtype)
-            group_C.append(C)
-            sizes += [M, N, K]
-            lds += [A.stride(0), B.stride(0), C.stride(0)]
-        L = _lib.lib()
-        PtrArr, IntArr = ctypes.c_void_p * G, ctypes.c_int * (3 * G)
-        ws = torch.empty(L.b200_grouped_matmul_workspace(G) + 128, dtype=torch.uint8, device=dev)
-        ws_ptr = (ws.data_ptr() + 127) & ~127
-        code = L.b200_grouped_matmul(
-            _stream(group_A[0]), G, PtrArr(*[t.data_ptr() for t in group_A]), PtrArr(*[t.data_ptr() for t in group_B]),
-            PtrArr(*[t.data_ptr() for t in group_C]), IntArr(*sizes), IntArr(*lds), _DT[dt], _DT[out_dtype], ws_ptr)
-        _lib.check(code, "grouped_matmul")
-        ws.record_stream(torch.cuda.current_stream(dev))  # the kernel reads the descriptors after this returns
-    return group_C
+    plan = GroupedMatmul(group_A, group_B, out_dtype)
+    out = plan.run()
+    plan.ws.record_stream(torch.cuda.current_stream(plan.dev))  # the kernel reads the descriptors after this returns
+    return out
 
 
 class HostMatmul:
