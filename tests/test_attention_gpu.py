@@ -297,3 +297,36 @@ def test_ops_replay_from_a_cuda_graph():
     # the older six-argument signature
     o6 = triton_b200.attention(q, k, v, True, 0.125, True)
     assert torch.equal(o6, eager[0])
+
+
+def test_two_streams_and_two_host_threads():
+    """Launches interleaved on two streams from two host threads (separate work counters per launch,
+    per-thread error strings, one context per device): every result equals the single-stream one."""
+    import threading
+    Z, H, N, D = 2, 4, 1024, 64
+    g = torch.Generator(device=DEV).manual_seed(6)
+    q, k, v = ((torch.randn(Z, H, N, D, generator=g, device=DEV) * 0.5).half() for _ in range(3))
+    a = torch.randn(1024, 512, generator=g, device=DEV).half()
+    b = torch.randn(512, 768, generator=g, device=DEV).half()
+    o_ref, M_ref = triton_b200.attention_forward(q, k, v, True, 0.125)
+    c_ref = triton_b200.matmul(a, b)
+    torch.cuda.synchronize()
+    results, errors = {}, []
+
+    def worker(name, fn):
+        try:
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                outs = [fn() for _ in range(40)]
+            s.synchronize()
+            results[name] = outs
+        except Exception as e:  # surfaced below
+            errors.append(repr(e))
+
+    t1 = threading.Thread(target=worker, args=("attn", lambda: triton_b200.attention_forward(q, k, v, True, 0.125)[0]))
+    t2 = threading.Thread(target=worker, args=("mm", lambda: triton_b200.matmul(a, b)))
+    t1.start(); t2.start(); t1.join(); t2.join()
+    assert not errors, errors
+    assert all(torch.equal(o, o_ref) for o in results["attn"])
+    assert all(torch.equal(c, c_ref) for c in results["mm"])
+    status_ok()
