@@ -446,43 +446,54 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
 }
 
 // delta[zh, n] = sum_d O * dO in fp32 (_attn_bwd_preprocess, 06-fused-attention.py:190-204).
-// HBM-bound: one warp per row chunk, 16-byte loads; 8 rows per warp for D = 64, 4 for D = 128 ... generic:
-// each thread reads 8 elements (16 bytes) of O and dO, D/8 threads per row.
+// HBM-bound: each thread reads 8 elements (16 bytes) of O and of dO for four rows at a time (eight
+// independent loads in flight), D/8 threads per row, a shuffle reduction per row.
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256)
 attn_bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ dout, float* __restrict__ delta,
                       long long o_sz, long long o_sh, long long o_sn, long long d_sz, long long d_sh, long long d_sn,
-                      int H, int N, long long rows_total) {
-  constexpr int TPR = D / 8;  // threads per row
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = gid / TPR;
-  const int part = (int)(gid % TPR);
-  float acc = 0.f;
-  if (row < rows_total) {
-    const int n = (int)(row % N);
-    const long long zh = row / N;
-    const int hh = (int)(zh % H);
-    const long long zz = zh / H;
-    const uint4 ov = *reinterpret_cast<const uint4*>(o + zz * o_sz + hh * o_sh + (long long)n * o_sn + part * 8);
-    const uint4 dv = *reinterpret_cast<const uint4*>(dout + zz * d_sz + hh * d_sh + (long long)n * d_sn + part * 8);
-    const uint32_t ow[4] = {ov.x, ov.y, ov.z, ov.w}, dw[4] = {dv.x, dv.y, dv.z, dv.w};
+                      unsigned H, unsigned N, unsigned rows_total) {
+  constexpr int TPR = D / 8;           // threads per row
+  constexpr unsigned RPB = 256 / TPR;  // rows per block and step
+  constexpr int U = 4;                 // rows per thread in flight (independent 16-byte loads)
+  const unsigned part = threadIdx.x % TPR, rib = threadIdx.x / TPR;
+  // 32-bit index arithmetic: 64-bit divisions per row made this kernel ALU-bound
+  for (unsigned base = blockIdx.x * (RPB * U); base < rows_total; base += gridDim.x * (RPB * U)) {
+    uint4 ov[U], dv[U];
+    unsigned rows[U];
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      float2 a, b;
-      if (BF16) {
-        a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[k]));
-        b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dw[k]));
-      } else {
-        a = __half22float2(*reinterpret_cast<const __half2*>(&ow[k]));
-        b = __half22float2(*reinterpret_cast<const __half2*>(&dw[k]));
+    for (int u = 0; u < U; ++u) {
+      const unsigned row = base + u * RPB + rib;
+      rows[u] = row;
+      ov[u] = dv[u] = make_uint4(0, 0, 0, 0);
+      if (row < rows_total) {
+        const unsigned n = row % N, zh = row / N, hh = zh % H, zz = zh / H;
+        ov[u] = *reinterpret_cast<const uint4*>(o + zz * o_sz + hh * o_sh + (long long)n * o_sn + part * 8);
+        dv[u] = *reinterpret_cast<const uint4*>(dout + zz * d_sz + hh * d_sh + (long long)n * d_sn + part * 8);
       }
-      acc = fmaf(a.x, b.x, acc);
-      acc = fmaf(a.y, b.y, acc);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t ow[4] = {ov[u].x, ov[u].y, ov[u].z, ov[u].w}, dw[4] = {dv[u].x, dv[u].y, dv[u].z, dv[u].w};
+      float acc = 0.f;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 a, b;
+        if (BF16) {
+          a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&ow[k]));
+          b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&dw[k]));
+        } else {
+          a = __half22float2(*reinterpret_cast<const __half2*>(&ow[k]));
+          b = __half22float2(*reinterpret_cast<const __half2*>(&dw[k]));
+        }
+        acc = fmaf(a.x, b.x, acc);
+        acc = fmaf(a.y, b.y, acc);
+      }
+#pragma unroll
+      for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      if (rows[u] < rows_total && part == 0) delta[rows[u]] = acc;
     }
   }
-#pragma unroll
-  for (int off = TPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (row < rows_total && part == 0) delta[row] = acc;
 }
 
 template <int D, bool BF16, bool DQ>
@@ -514,10 +525,13 @@ int launch_bwd_all(DeviceCtx* ctx, cudaStream_t stream, const void* o, const voi
                    const CUtensorMap& tv, const CUtensorMap& tdo, BwdParams p, void* dq, void* dk, void* dv,
                    const int64_t* sdq, const int64_t* sdk, const int64_t* sdv) {
   const long long rows = (long long)p.Z * p.H * p.N;
-  const long long threads = rows * (D / 8);
-  attn_bwd_delta_kernel<D, BF16><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
+  if (rows >= (1ll << 32)) return fail(B200_ERR_UNSUPPORTED, "more than 2^32 rows");
+  const long long rows_per_block = (256 / (D / 8)) * 4;
+  long long blocks = (rows + rows_per_block - 1) / rows_per_block;
+  if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
+  attn_bwd_delta_kernel<D, BF16><<<(unsigned)blocks, 256, 0, stream>>>(
       reinterpret_cast<const uint16_t*>(o), reinterpret_cast<const uint16_t*>(dout), delta, so[0], so[1], so[2],
-      sdo[0], sdo[1], sdo[2], p.H, p.N, rows);
+      sdo[0], sdo[1], sdo[2], (unsigned)p.H, (unsigned)p.N, (unsigned)rows);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd delta launch: %s", cudaGetErrorString(e));
   p.delta = delta;
