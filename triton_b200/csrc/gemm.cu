@@ -696,19 +696,39 @@ gemm_plain_kernel(const void* a, const void* b, GemmParams p, long long sam, lon
 // split-K second pass: C = act(scale * sum over splits of the fp32 partial tiles), one rounding
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(GemmParams p) {
+  // one thread per four consecutive columns of a row (blockIdx.y strides over the rows): 16-byte
+  // loads of the partial sums where N allows, no division per element
   const long long total = (long long)p.M * p.N;
   float scale = 1.f;
   if (p.scale_a) scale *= __ldg(p.scale_a);
   if (p.scale_b) scale *= __ldg(p.scale_b);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
-    float v = 0.f;
-    for (int sp = 0; sp < p.splits; ++sp) v += p.ws[(long long)sp * total + i];  // fixed order: deterministic
-    v = p.bias_mode ? finish<true>(p, v, scale, (int)(i / p.N), (int)(i % p.N)) : finish<false>(p, v, scale, 0, 0);
-    const long long o = (i / p.N) * p.ldc + (i % p.N);
-    if (p.out_dtype == B200_E4M3) reinterpret_cast<uint8_t*>(p.c)[o] = (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
-    else if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = v;
-    else if (p.out_dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(v);
-    else reinterpret_cast<__half*>(p.c)[o] = __float2half_rn(v);
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (col >= p.N) return;
+  const bool vec = (p.N & 3) == 0;  // every row of the workspace slices starts 16-byte aligned
+  for (int row = blockIdx.y; row < p.M; row += gridDim.y) {
+    const long long i = (long long)row * p.N + col;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int sp = 0; sp < p.splits; ++sp) {  // fixed order: deterministic
+      const float* src = p.ws + (long long)sp * total + i;
+      if (vec) {
+        const float4 t = *reinterpret_cast<const float4*>(src);
+        v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (col + j < p.N) v[j] += src[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (col + j >= p.N) break;
+      const float r = p.bias_mode ? finish<true>(p, v[j], scale, row, col + j) : finish<false>(p, v[j], scale, 0, 0);
+      const long long o = (long long)row * p.ldc + col + j;
+      if (p.out_dtype == B200_E4M3) reinterpret_cast<uint8_t*>(p.c)[o] = (uint8_t)__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
+      else if (p.out_dtype == B200_F32) reinterpret_cast<float*>(p.c)[o] = r;
+      else if (p.out_dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(p.c)[o] = __float2bfloat16_rn(r);
+      else reinterpret_cast<__half*>(p.c)[o] = __float2half_rn(r);
+    }
   }
 }
 
@@ -1094,10 +1114,10 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     default: rc = launch_tile<128, 64, 7>(ctx, stream, ta, tbm, tcm, p); break;
   }
   if (rc || p.splits == 1) return rc;
-  const long long total = (long long)M * N;
-  int blocks = (int)((total + 255) / 256);
-  if (blocks > ctx->sm_count * 8) blocks = ctx->sm_count * 8;
-  splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
+  const int col_threads = (N + 3) / 4;
+  const int tpb = col_threads >= 256 ? 256 : ((col_threads + 31) / 32) * 32;
+  dim3 rgrid((col_threads + tpb - 1) / tpb, M < 65535 ? M : 65535, 1);
+  splitk_reduce_kernel<<<rgrid, tpb, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "split-K reduce launch: %s", cudaGetErrorString(e));
   return B200_OK;
