@@ -43,11 +43,14 @@ _lib = None
 def lib():
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        # TRITON_B200_LIB (read at first use) selects another build of the same library: the
+        # instrumented one of triton_b200/trace.py
+        path = os.environ.get("TRITON_B200_LIB") or LIB_PATH
+        if not os.path.exists(path):
             raise RuntimeError(
-                f"{LIB_PATH} is missing: build it with `python -m triton_b200.build` (needs nvcc); "
+                f"{path} is missing: build it with `python -m triton_b200.build` (needs nvcc); "
                 "there is no fallback implementation")
-        L = ctypes.CDLL(LIB_PATH)
+        L = ctypes.CDLL(path)
         for name, args in SIGNATURES.items():
             fn = getattr(L, name)
             fn.argtypes = args

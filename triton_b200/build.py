@@ -1,6 +1,6 @@
 """Build the in-tree shared library `triton_b200/libtriton_b200.so` with nvcc for sm_100a.
 
-    python -m triton_b200.build [--force] [--verbose]
+    python -m triton_b200.build [--force] [--verbose] [--trace]
 
 Each .cu under csrc/ is compiled to an object next to the library (stale objects are
 rebuilt when the source or a header is newer) and linked with the static CUDA runtime;
@@ -41,8 +41,12 @@ def _newest_header():
     return t
 
 
-def build(force=False, verbose=False):
+def build(force=False, verbose=False, trace=False):
+    """trace=True builds the instrumented variant (-DB200_TRACE) next to the production library, as
+    libtriton_b200_trace.so with its own object directory; see triton_b200/trace.py."""
     nvcc = _nvcc()
+    OBJ = os.path.join(PKG, "csrc", "_obj_trace" if trace else "_obj")
+    LIB = os.path.join(PKG, "libtriton_b200_trace.so" if trace else "libtriton_b200.so")
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
     hdr_t = _newest_header()
@@ -51,7 +55,7 @@ def build(force=False, verbose=False):
         src = os.path.join(CSRC, s)
         obj = os.path.join(OBJ, s[:-3] + ".o")
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_t):
-            cmd = [nvcc, *NVCC_FLAGS, "-c", src, "-o", obj]
+            cmd = [nvcc, *NVCC_FLAGS, *(["-DB200_TRACE"] if trace else []), "-c", src, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas")
                 cmd.insert(2, "-v")
@@ -82,5 +86,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--trace", action="store_true", help="build the instrumented variant libtriton_b200_trace.so")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.trace))

@@ -124,6 +124,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   volatile int* sched_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  B200_TRACE_DECL;  // trace builds: region 0 / 1 = first compute warp of the dK/dV / dQ kernel
 
   if (threadIdx.x == 0) {
     mbar_init(r_full, 1);
@@ -310,7 +311,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         const float* sd = sm + 128;                                                                  // column delta
         // the diagonal block is the only one that needs the causal mask
         const bool diag = p.causal && (t == blk);
+        const bool traced = warp == 0 && lane == 0;  // used by trace builds only
+        if (traced) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 0x100 | steps);
         mbar_wait(t1_full, cnt & 1u, p.status, SITE_BWD_S_FULL);
+        if (traced) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 1);
         tc_fence_after();
         uint32_t pr[HC];  // P as fp32 bits
 #pragma unroll
@@ -343,7 +347,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
           tc_fence_before();
           mbar_arrive(p_full);
         }
+        if (traced) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 2);
         mbar_wait(t2_full, cnt & 1u, p.status, SITE_BWD_DP_FULL);
+        if (traced) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 3);
         tc_fence_after();
         uint32_t dsw[HC / 2];  // dS packed to 16 bit
 #pragma unroll
@@ -367,6 +373,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(ds_full);
+        if (traced) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 4);
         if (++s == NST) s = 0;
       }
 
@@ -374,6 +381,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       // item's loads and first T MMAs; the next item's first accumulate MMA needs this warp's next
       // P / dS, i.e. comes after these reads in program order.
       mbar_wait(acc_full, n & 1u, p.status, SITE_BWD_ACC_FULL);
+      if (warp == 0 && lane == 0) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 8);
       tc_fence_after();
       auto store_rows = [&](uint32_t tm_acc, const CUtensorMap* map, void* out, long long sz, long long sh,
                             long long sn, float mul) {
@@ -432,6 +440,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       };
       store_rows(tm_a, &tm_oa, p.out_a, p.oa_sz, p.oa_sh, p.oa_sn, p.sm_scale);  // dK or dQ carry sm_scale
       if (!DQ) store_rows(tm_b, &tm_ob, p.out_b, p.ob_sz, p.ob_sh, p.ob_sn, 1.0f);
+      if (warp == 0 && lane == 0) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 9);
     }
     if (p.out_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
   }

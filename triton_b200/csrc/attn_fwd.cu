@@ -124,6 +124,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   volatile int* sched_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  B200_TRACE_DECL;  // trace builds: regions 0 / 1 = first softmax warp of tile 0 / 1, region 2 = MMA warp
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -214,13 +215,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
         tc_commit_elect(&s_full[i]);
+        if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x40 | i);
       };
       // O_i (+)= P_i V: 8 MMAs of 16 kv rows; the second four wait for the second half of P
       auto issue_pv = [&](int i, uint32_t stage, uint32_t accum, uint32_t parity) {
         const uint64_t dv = dv0 + stage * (TILE >> 4);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x10 | (i << 1) | h);
           mbar_wait(&p_full[2 * i + h], parity, p.status, SITE_FWD_P_FULL);
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x20 | (i << 1) | h);
           tc_fence_after();
           if constexpr (FP8) {
 #pragma unroll
@@ -309,9 +313,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int row = qb * 256 + i * BLK + row_in_tile;  // query index
       const int nb = i ? it.n1 : it.n0;
       float m_ref = -INFINITY, l = 0.f;
+      const bool traced = quarter == 0 && lane == 0;  // used by trace builds only
+      if (traced) B200_TRACE_EVENT(p.status, i, 0x100 | nb);
 
       for (int j = 0; j < nb; ++j, ++scnt) {
         mbar_wait(&s_full[i], scnt & 1u, p.status, SITE_FWD_S_FULL);
+        if (traced) B200_TRACE_EVENT(p.status, i, 1);
         tc_fence_after();
         const int col0 = j * BLK;
         const bool need_mask = (p.causal && col0 + BLK - 1 > qb * 256 + i * BLK) || (col0 + BLK > p.N);
@@ -341,6 +348,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(max3(mx4[u], mx4[u + 4], mx4[u + 8]), mx4[u + 12]);
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        if (traced) B200_TRACE_EVENT(p.status, i, 2);
         // mx is finite: every row sees at least one valid column in every block it visits
         const float m_new = fmaxf(m_ref, mx * scale);
         // lazy rescale of the accumulator (the ld/st below are warp collectives, so the warp
@@ -363,6 +371,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
           }
         }
+        if (traced) B200_TRACE_EVENT(p.status, i, 3);
         const float neg_m = -m_ref;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -396,12 +405,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if (traced) B200_TRACE_EVENT(p.status, i, 4);
       }
 
       // epilogue: O / l and M.  It overlaps the next item's Q / K loads and first S MMAs; the next
       // item's first P V (which overwrites O) needs this tile's next P, i.e. comes after these
       // reads in program order.
       mbar_wait(&o_full[i], n & 1u, p.status, SITE_FWD_O_FULL);
+      if (traced) B200_TRACE_EVENT(p.status, i, 8);
       tc_fence_after();
       const float inv_l = 1.f / l;
       const bool valid = row < p.N;
@@ -498,6 +509,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       if (valid) p.m[(long long)it.zh * p.N + row] = m_ref + log2f(l);
+      if (traced) B200_TRACE_EVENT(p.status, i, 9);
     }
     if (p.o_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
   }

@@ -10,7 +10,11 @@
 namespace tb {
 
 // Status word read by b200_status(); kernels receive its device address as a parameter.
+#ifdef B200_TRACE
+__device__ unsigned g_status_word[4 + 2 * tb::kTraceRegions * tb::kTraceEvents];  // status word + trace buffer
+#else
 __device__ unsigned g_status_word[4];
+#endif
 // Work counters of the persistent attention kernels: each launch takes the next word of this ring
 // and zeroes it on its stream, so launches in flight on different streams do not share one (more
 // than 256 attention launches in flight at once would).
@@ -172,6 +176,24 @@ extern "C" {
 int b200_version(void) { return 100; }
 
 const char* b200_last_error(void) { return g_err; }
+
+#ifdef B200_TRACE
+// trace builds only: copies the (tag, clock) pairs of all regions to `dst` and clears them
+extern "C" B200_API int b200_trace_read(void* dst, size_t bytes) {
+  const size_t all = sizeof(unsigned) * 2 * tb::kTraceRegions * tb::kTraceEvents;
+  if (!dst || bytes < all) return fail(B200_ERR_ARG, "trace buffer too small");
+  if (!current_ctx()) return B200_ERR_DEVICE;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(dst, g_status_word, all, sizeof(unsigned) * tb::kTraceOffset);
+  if (e == cudaSuccess) {
+    void* sym = nullptr;
+    e = cudaGetSymbolAddress(&sym, g_status_word);
+    if (e == cudaSuccess) e = cudaMemset(static_cast<unsigned*>(sym) + tb::kTraceOffset, 0, all);
+  }
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "trace read: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+#endif
 
 int b200_status(unsigned* value, int clear) {
   DeviceCtx* ctx = current_ctx();

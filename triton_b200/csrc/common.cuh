@@ -9,6 +9,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "trace.h"
+
 namespace tb {
 
 // ------------------------------------------------------------------ status word

@@ -6,6 +6,7 @@
 #include <stdint.h>
 
 #include "../../include/triton_b200.h"
+#include "trace.h"
 
 namespace tb {
 

@@ -1,0 +1,100 @@
+"""Device-side clock trace of the attention kernels.
+
+    python -m triton_b200.trace fwd [--case c4|c5|noncausal]
+    python -m triton_b200.trace bwd [--case c5|long]
+
+Builds the instrumented variant of the library (`-DB200_TRACE`, libtriton_b200_trace.so beside the
+production one), runs a few launches of one configuration through the normal Python wrappers and
+prints, for the traced warps of CTA 0, the mean number of SM clocks between consecutive trace
+points.  The instrumentation costs roughly 100 clocks per point, so the figures are for reading
+proportions, not for benchmarking; the production library contains none of it.
+"""
+import argparse
+import ctypes
+import os
+import sys
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+REGIONS, EVENTS = 4, 4096  # kTraceRegions, kTraceEvents of csrc/trace.h
+
+FWD_TAGS = {1: "wait for S (MMA of this tile + hand-over)", 2: "TMEM load + row maximum", 3: "rescale decision (+ O rescale)",
+            4: "exp2, pack, P store, arrive", 8: "wait for the last P V (o_full)", 9: "epilogue (O / l, stores)"}
+FWD_MMA = {0x10: "before the wait for P", 0x20: "P arrived", 0x40: "S issued (includes the P V issue before it)"}
+BWD_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3: "wait for T2 (dP)",
+            4: "dS, store, arrive", 8: "wait for the last accumulate (acc_full)", 9: "epilogue (gradient stores)"}
+
+
+def _summarise(ev, names, item_tag=0x100):
+    """mean clocks from the previous trace point to each tagged point; ev: [(tag, clock)]"""
+    import collections
+    tot, cnt = collections.OrderedDict(), collections.Counter()
+    prev = None
+    for tag, clk in ev:
+        if tag == 0 and clk == 0:
+            break
+        if prev is not None:
+            key = "item start (scheduler, next item)" if tag >= item_tag else names.get(tag, names.get(tag & 0xF0, hex(tag)))
+            tot[key] = tot.get(key, 0) + ((clk - prev) & 0xFFFFFFFF)
+            cnt[key] += 1
+        prev = clk
+    return [(k, cnt[k], tot[k] / cnt[k]) for k in tot]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["fwd", "bwd"])
+    ap.add_argument("--case", default=None)
+    args = ap.parse_args()
+    from . import build
+    lib = build.build(trace=True)
+    os.environ["TRITON_B200_LIB"] = lib
+    import numpy as np
+    import torch
+    import triton_b200 as tb
+    from triton_b200 import _lib
+    assert _lib._lib is None, "the library was loaded before the trace build was selected"
+    case = args.case or ("c4" if args.kernel == "fwd" else "c5")
+    Z, H, N, D, dt, causal, sm = {"c4": (4, 32, 4096, 128, torch.float16, True, 128 ** -0.5),
+                                  "noncausal": (4, 32, 4096, 128, torch.float16, False, 128 ** -0.5),
+                                  "c5": (4, 48, 1024, 64, torch.bfloat16, True, 0.5),
+                                  "long": (4, 48, 4096, 64, torch.bfloat16, True, 0.5)}[case]
+    g = torch.Generator(device="cuda").manual_seed(0)
+    q, k, v, do = ((torch.randn(Z, H, N, D, generator=g, device="cuda") * 0.5).to(dt) for _ in range(4))
+    L = _lib.lib()
+    L.b200_trace_read.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+    buf = np.zeros((REGIONS, EVENTS, 2), dtype=np.uint32)
+
+    def read():
+        _lib.check(L.b200_trace_read(ctypes.c_void_p(buf.ctypes.data), buf.nbytes), "trace_read")
+        return buf.copy()
+
+    o, M = tb.attention_forward(q, k, v, causal, sm)
+    if args.kernel == "bwd":
+        tb.attention_backward(q, k, v, o, M, do, causal, sm)
+    read()  # discard the first (cold) launch
+    if args.kernel == "fwd":
+        tb.attention_forward(q, k, v, causal, sm)
+    else:
+        tb.attention_backward(q, k, v, o, M, do, causal, sm)
+    t = read()
+    print(f"{args.kernel} Z{Z} H{H} N{N} D{D} causal={causal}: CTA 0, mean SM clocks since the previous trace point")
+    if args.kernel == "fwd":
+        for region, label in ((0, "softmax warp 0 of tile 0"), (1, "softmax warp 0 of tile 1")):
+            print(f"  {label}")
+            for key, n, mean in _summarise(t[region].tolist(), FWD_TAGS):
+                print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
+        print("  MMA warp")
+        for key, n, mean in _summarise(t[2].tolist(), FWD_MMA):
+            print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
+    else:
+        for region, label in ((0, "dK/dV kernel, compute warp 0"), (1, "dQ kernel, compute warp 0")):
+            print(f"  {label}")
+            for key, n, mean in _summarise(t[region].tolist(), BWD_TAGS):
+                print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
+    st = _lib.status()
+    print("status word", hex(st))
+    return 0 if st == 0 else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
