@@ -330,3 +330,28 @@ def test_two_streams_and_two_host_threads():
     assert all(torch.equal(o, o_ref) for o in results["attn"])
     assert all(torch.equal(c, c_ref) for c in results["mm"])
     status_ok()
+
+
+def test_custom_ops_on_gpu():
+    """torch.ops.triton_b200.*: same bits as the wrappers, autograd through `attention`, opcheck
+    (schema, fake-tensor consistency, autograd registration)."""
+    ns = torch.ops.triton_b200
+    g = torch.Generator(device=DEV).manual_seed(8)
+    a = torch.randn(256, 128, generator=g, device=DEV).half()
+    b = torch.randn(128, 192, generator=g, device=DEV).half()
+    assert torch.equal(ns.matmul(a, b), triton_b200.matmul(a, b))
+    bias = torch.randn(1, 192, generator=g, device=DEV).half()
+    assert torch.equal(ns.matmul(a, b, "leaky_relu", None, None, None, bias), triton_b200.matmul(a, b, "leaky_relu", bias=bias))
+    q, k, v, do = ((torch.randn(1, 2, 256, 64, generator=g, device=DEV) * 0.5).to(torch.bfloat16) for _ in range(4))
+    o_ref, M_ref = triton_b200.attention_forward(q, k, v, True, 0.125)
+    dq_ref, dk_ref, dv_ref = triton_b200.attention_backward(q, k, v, o_ref, M_ref, do, True, 0.125)
+    qg, kg, vg = (t.clone().requires_grad_() for t in (q, k, v))
+    o, M = ns.attention(qg, kg, vg, True, 0.125)
+    o.backward(do)
+    assert torch.equal(o, o_ref) and torch.equal(M, M_ref)
+    assert torch.equal(qg.grad, dq_ref) and torch.equal(kg.grad, dk_ref) and torch.equal(vg.grad, dv_ref)
+    torch.library.opcheck(ns.matmul.default, (a, b), test_utils=("test_schema", "test_faketensor"))
+    torch.library.opcheck(ns.attention_fwd.default, (q, k, v, True, 0.125), test_utils=("test_schema", "test_faketensor"))
+    torch.library.opcheck(ns.attention.default, (qg.detach().requires_grad_(), k, v, True, 0.125),
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+    status_ok()

@@ -95,3 +95,25 @@ def test_two_rank_gloo_shard_and_gather():
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in res)
     assert all(shape == (301, 48) for _, _, shape in res)
+
+
+def test_custom_ops_are_registered_with_fake_implementations():
+    """torch.ops.triton_b200.* exist in the dispatcher and trace on meta tensors (shapes and dtypes
+    only, no kernel); on CPU tensors they raise: there is no CPU implementation."""
+    import torch
+    import triton_b200  # noqa: F401
+    ns = torch.ops.triton_b200
+    a = torch.empty(48, 32, dtype=torch.float16, device="meta")
+    b = torch.empty(32, 80, dtype=torch.float16, device="meta")
+    c = ns.matmul(a, b)
+    assert c.shape == (48, 80) and c.dtype == torch.float16 and c.device.type == "meta"
+    assert ns.matmul(a.to(torch.bfloat16), b.to(torch.bfloat16), "", torch.float32).dtype == torch.float32
+    q = torch.empty(2, 3, 256, 64, dtype=torch.bfloat16, device="meta")
+    o, M = ns.attention_fwd(q, q, q, True, 0.125)
+    assert o.shape == q.shape and o.dtype == q.dtype and M.shape == (2, 3, 256) and M.dtype == torch.float32
+    dq, dk, dv = ns.attention_bwd(q, q, q, o, M, o, True, 0.125)
+    assert dq.shape == q.shape and dk.dtype == q.dtype and dv.shape == q.shape
+    o2, M2 = ns.attention(q, q, q, False, 0.5)
+    assert o2.shape == q.shape
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        ns.matmul(torch.zeros(4, 4, dtype=torch.float16), torch.zeros(4, 4, dtype=torch.float16))
