@@ -234,6 +234,20 @@ def other_configs(torch, tb, dev):
     out["c5_attn_fwd_bwd_causal_bf16_z4h48n1024d64"] = timed(fwd_bwd, fl * 3.5)
     out["c5_fwd_only"] = timed(lambda: tb.attention_forward(q, k, v, True, 0.5), fl)
     out["c5_bwd_only"] = timed(lambda: tb.attention_backward(q, k, v, o, Mst, do, True, 0.5), fl * 2.5)
+    del q, k, v, do, o, Mst
+    # rows beyond the five configs: the widened matmul / attention entry points
+    ga = [torch.rand(512, 512, generator=g).half().to(dev) for _ in range(64)]
+    gb = [torch.rand(512, 512, generator=g).half().to(dev) for _ in range(64)]
+    plan = tb.GroupedMatmul(ga, gb)
+    out["grouped_matmul_fp16_64x512_prepared"] = timed(plan.run, 64 * 2.0 * 512 ** 3)
+    a = (torch.randn(256, 8192, generator=g) / 90).half().to(dev)
+    b = (torch.randn(8192, 256, generator=g) / 90).half().to(dev)
+    out["splitk_matmul_fp16_256x256x8192"] = timed(lambda: tb.matmul(a, b), 2.0 * 256 * 256 * 8192)
+    if hasattr(torch, "float8_e5m2"):
+        q8, k8, v8 = ((torch.randn(4, 32, 4096, 128, generator=g) * 0.5).to(dev).to(torch.float8_e5m2) for _ in range(3))
+        v8 = v8.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
+        fl = 2 * 2.0 * 4 * 32 * 4096 * 4096 * 128 * 0.5
+        out["attn_fwd_causal_e5m2_z4h32n4096d128"] = timed(lambda: tb.attention_forward(q8, k8, v8, True, 1.3), fl)
     return out
 
 
