@@ -1,6 +1,6 @@
 """Device-side clock trace of the attention kernels.
 
-    python -m triton_b200.trace fwd [--case c4|c5|noncausal]
+    python -m triton_b200.trace fwd [--case c4|c5|noncausal|e5m2]
     python -m triton_b200.trace bwd [--case c5|long]
 
 Builds the instrumented variant of the library (`-DB200_TRACE`, libtriton_b200_trace.so beside the
@@ -57,9 +57,12 @@ def main():
     Z, H, N, D, dt, causal, sm = {"c4": (4, 32, 4096, 128, torch.float16, True, 128 ** -0.5),
                                   "noncausal": (4, 32, 4096, 128, torch.float16, False, 128 ** -0.5),
                                   "c5": (4, 48, 1024, 64, torch.bfloat16, True, 0.5),
-                                  "long": (4, 48, 4096, 64, torch.bfloat16, True, 0.5)}[case]
+                                  "long": (4, 48, 4096, 64, torch.bfloat16, True, 0.5),
+                                  "e5m2": (4, 32, 4096, 128, torch.float8_e5m2, True, 1.3)}[case]
     g = torch.Generator(device="cuda").manual_seed(0)
     q, k, v, do = ((torch.randn(Z, H, N, D, generator=g, device="cuda") * 0.5).to(dt) for _ in range(4))
+    if case == "e5m2":  # the 8-bit forward reads V with the key dimension contiguous
+        v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
     L = _lib.lib()
     L.b200_trace_read.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
     buf = np.zeros((REGIONS, EVENTS, 2), dtype=np.uint32)
