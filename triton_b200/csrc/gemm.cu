@@ -694,34 +694,48 @@ gemm_plain_kernel(const void* a, const void* b, GemmParams p, long long sam, lon
 }
 
 // split-K second pass: C = act(scale * sum over splits of the fp32 partial tiles), one rounding
+template <int VEC>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(GemmParams p) {
-  // one thread per four consecutive columns of a row (blockIdx.y strides over the rows): 16-byte
-  // loads of the partial sums where N allows, no division per element
+  // one thread per VEC consecutive columns of a row (blockIdx.y strides over the rows), no division
+  // per element.  VEC = 4 (16-byte loads) for large outputs, VEC = 1 for small ones, where more
+  // threads hide more latency.  Four loads are in flight and are added in split order, so the sum
+  // does not depend on timing.
   const long long total = (long long)p.M * p.N;
   float scale = 1.f;
   if (p.scale_a) scale *= __ldg(p.scale_a);
   if (p.scale_b) scale *= __ldg(p.scale_b);
-  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int col = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (col >= p.N) return;
-  const bool vec = (p.N & 3) == 0;  // every row of the workspace slices starts 16-byte aligned
   for (int row = blockIdx.y; row < p.M; row += gridDim.y) {
     const long long i = (long long)row * p.N + col;
-    float v[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int sp = 0; sp < p.splits; ++sp) {  // fixed order: deterministic
-      const float* src = p.ws + (long long)sp * total + i;
-      if (vec) {
-        const float4 t = *reinterpret_cast<const float4*>(src);
-        v[0] += t.x; v[1] += t.y; v[2] += t.z; v[3] += t.w;
-      } else {
+    float v[VEC];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          if (col + j < p.N) v[j] += src[j];
+    for (int j = 0; j < VEC; ++j) v[j] = 0.f;
+    for (int sp = 0; sp < p.splits; sp += 4) {
+      float t[4][VEC];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float* src = p.ws + (long long)(sp + u) * total + i;
+        if (sp + u < p.splits) {
+          if constexpr (VEC == 4) {
+            const float4 q = *reinterpret_cast<const float4*>(src);
+            t[u][0] = q.x; t[u][1] = q.y; t[u][2] = q.z; t[u][3] = q.w;
+          } else {
+            t[u][0] = *src;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) t[u][j] = 0.f;
+        }
       }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] += t[u][j];
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      if (col + j >= p.N) break;
+    for (int j = 0; j < VEC; ++j) {
       const float r = p.bias_mode ? finish<true>(p, v[j], scale, row, col + j) : finish<false>(p, v[j], scale, 0, 0);
       const long long o = (long long)row * p.ldc + col + j;
       if (p.out_dtype == B200_E4M3) reinterpret_cast<uint8_t*>(p.c)[o] = (uint8_t)__nv_cvt_float_to_fp8(r, __NV_SATFINITE, __NV_E4M3);
@@ -1114,10 +1128,12 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     default: rc = launch_tile<128, 64, 7>(ctx, stream, ta, tbm, tcm, p); break;
   }
   if (rc || p.splits == 1) return rc;
-  const int col_threads = (N + 3) / 4;
+  const bool vec4 = (N & 3) == 0 && (long long)M * N > (1 << 20);  // 16-byte loads only pay on large outputs
+  const int col_threads = vec4 ? N / 4 : N;
   const int tpb = col_threads >= 256 ? 256 : ((col_threads + 31) / 32) * 32;
   dim3 rgrid((col_threads + tpb - 1) / tpb, M < 65535 ? M : 65535, 1);
-  splitk_reduce_kernel<<<rgrid, tpb, 0, stream>>>(p);
+  if (vec4) splitk_reduce_kernel<4><<<rgrid, tpb, 0, stream>>>(p);
+  else splitk_reduce_kernel<1><<<rgrid, tpb, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "split-K reduce launch: %s", cudaGetErrorString(e));
   return B200_OK;
