@@ -388,8 +388,8 @@ def run_ours(args, rank, local_rank, world):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemm_kernel<256,256,3> launch on this workload
-# (877.3 MB + 119.7 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md); algorithmic: 402.7 MB
-TRAFFIC_BYTES_PER_LAUNCH = 997_027_584
+# (879.5 MB + 120.0 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md); algorithmic: 402.7 MB
+TRAFFIC_BYTES_PER_LAUNCH = 999_518_208
 
 
 def main():
