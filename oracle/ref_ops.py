@@ -17,6 +17,11 @@ bf16, which is what the reference's GPU lowering does (cvt.rn, third_party/nvidi
 TritonNVIDIAGPUToLLVM/ElementwiseOpToLLVM.cpp:346,368); the interpreter truncates
 fp32->bf16 and cannot run bf16 dots at all, so the bf16 mode of this oracle is
 pinned through its fp16 mode (same code, only the rounding function differs).
+The bias and row-softmax epilogues (`add_bias`, `softmax_epilogue`) are pinned the same
+way: against tests/golden/epilogue.npz, produced by the reference's own epilogue kernel
+(python/test/unit/hopper/test_gemm.py:143-247) under the interpreter; the two 8-bit
+roundings (`round_e4m3`, `round_e5m2`) are pinned bit for bit against torch's float8
+conversions, which implement the same IEEE-style round-to-nearest-even with saturation.
 """
 import math
 

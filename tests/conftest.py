@@ -18,7 +18,7 @@ def golden():
     import numpy as np
     d = os.path.join(ROOT, "tests", "golden")
     out = {}
-    for name in ("matmul", "fp8", "attn", "attn_old"):
+    for name in ("matmul", "fp8", "epilogue", "attn", "attn_old"):
         with np.load(os.path.join(d, name + ".npz")) as z:
             for k in z.files:
                 out[k] = z[k]

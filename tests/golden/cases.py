@@ -17,6 +17,28 @@ MATMUL_CASES = {
     "bT": dict(M=256, N=512, K=192, seed=3, b_transposed=True),
 }
 
+# Epilogue cases of python/test/unit/hopper/test_gemm.py (matmul_kernel with ADD_MATRIX / ADD_ROWS /
+# ADD_COLS / DO_SOFTMAX).  `out`: the kernel's out_dtype.  Softmax needs BLOCK_N >= N.
+EPILOGUE_CASES = {
+    "add_matrix_f16": dict(M=128, N=128, K=64, seed=41, epilogue="add-matrix", out="fp16"),
+    "add_rows_f16": dict(M=192, N=128, K=96, seed=42, epilogue="add-rows", out="fp16"),
+    "add_cols_f32": dict(M=128, N=256, K=64, seed=43, epilogue="add-cols", out="fp32"),
+    "softmax_f16": dict(M=128, N=128, K=128, seed=44, epilogue="softmax", out="fp16", scale=3.0),
+    "softmax_f32": dict(M=64, N=64, K=64, seed=45, epilogue="softmax", out="fp32", scale=2.0),
+}
+
+
+def epilogue_inputs(c):
+    """A, B fp16 and the bias of the output type: full [M, N] matrix as in the reference test
+    (add-rows reads its first column, add-cols its first row)."""
+    g = torch.Generator().manual_seed(c["seed"])
+    s = c.get("scale", 1.0)
+    a = (torch.randn(c["M"], c["K"], generator=g) / s).half()
+    b = (torch.randn(c["K"], c["N"], generator=g) / s).half()
+    bias = torch.randn(c["M"], c["N"], generator=g).to(torch.float16 if c["out"] == "fp16" else torch.float32)
+    return a, b, bias
+
+
 FP8_CASES = {
     "ref_shape": dict(M=128, N=256, K=256, seed=4),
     "k512": dict(M=256, N=512, K=512, seed=5),

@@ -10,6 +10,7 @@ reference is copied into this repository: only numeric outputs are written.
 Kernels used (paths inside the reference project):
   python/tutorials/03-matrix-multiplication.py   matmul_kernel, leaky_relu
   python/test/unit/language/test_core.py         matmul_kernel (fp8 in, fp32 out)
+  python/test/unit/hopper/test_gemm.py           matmul_kernel (bias and softmax epilogues)
   python/tutorials/06-fused-attention.py         _attn_fwd*, _attn_bwd*, _attention
   python/test/unit/hopper/test_flashattention.py _fwd_kernel, _bwd_preprocess, _bwd_kernel
 
@@ -143,6 +144,38 @@ def gen_fp8(ref_root, out):
         out[f"fp8.{name}.scales"] = np.array([float(sa), float(sb)], dtype=np.float32)
 
 
+def gen_epilogue(ref_root, out):
+    """matmul_kernel of python/test/unit/hopper/test_gemm.py:143-247 with its bias / softmax epilogues
+    (block-pointer loads, plain masked store)."""
+    import triton.language as tl
+    ns = _load(ref_root, "python/test/unit/hopper/test_gemm.py", {"matmul_kernel"}, pick=lambda c: c[0])
+    kern = ns["matmul_kernel"]
+    for name, c in cases.EPILOGUE_CASES.items():
+        a, b, bias = cases.epilogue_inputs(c)
+        M, K = a.shape
+        N = b.shape[1]
+        odt = torch.float16 if c["out"] == "fp16" else torch.float32
+        z = torch.full((M, N), 1.0, dtype=odt)
+        w = torch.zeros((N, N), dtype=torch.float16)
+        ep = c["epilogue"]
+        BM, BN, BK = 64, (N if ep == "softmax" else 64), 32
+        grid = (triton.cdiv(M, BM) * triton.cdiv(N, BN),)
+        t0 = time.time()
+        kern[grid](a_ptr=a, b_ptr=b, w_ptr=w, bias_ptr=bias, z_ptr=z, M=M, N=N, K=K,
+                   stride_am=a.stride(0), stride_ak=a.stride(1), stride_bk=b.stride(0), stride_bn=b.stride(1),
+                   stride_wm=w.stride(0), stride_wn=w.stride(1), stride_zm=z.stride(0), stride_zn=z.stride(1),
+                   BLOCK_M=BM, BLOCK_N=BN, BLOCK_K=BK, GROUP_SIZE_M=8,
+                   out_dtype=tl.float16 if c["out"] == "fp16" else tl.float32, USE_TMA_STORE=False,
+                   ADD_MATRIX=ep == "add-matrix", ADD_ROWS=ep == "add-rows", ADD_COLS=ep == "add-cols",
+                   DO_SOFTMAX=ep == "softmax", CHAIN_DOT=False,
+                   A_ORDER_0=1, A_ORDER_1=0, B_ORDER_0=1, B_ORDER_1=0, W_ORDER_0=0, W_ORDER_1=1,
+                   Z_ORDER_0=1, Z_ORDER_1=0)
+        print(f"epilogue {name}: {time.time()-t0:.2f}s")
+        out[f"epilogue.{name}.z"] = z.numpy()
+        for nm, t in (("a", a), ("b", b), ("bias", bias)):
+            out[f"epilogue.{name}.sha_{nm}"] = np.array(sha(t))
+
+
 def gen_attn(ref_root, out):
     wanted = {"_attn_fwd_inner", "_attn_fwd", "_attn_bwd_preprocess", "_attn_bwd_dkdv", "_attn_bwd_dq",
               "_attn_bwd", "_attention", "keep"}
@@ -190,7 +223,7 @@ def gen_attn_old(ref_root, out):
         out[f"attn_old.{name}.dv"] = v.grad.numpy()
 
 
-GENS = {"matmul": gen_matmul, "fp8": gen_fp8, "attn": gen_attn, "attn_old": gen_attn_old}
+GENS = {"matmul": gen_matmul, "fp8": gen_fp8, "epilogue": gen_epilogue, "attn": gen_attn, "attn_old": gen_attn_old}
 
 
 def main():

@@ -188,3 +188,28 @@ def test_round_e5m2_matches_torch_and_saturates():
     assert np.array_equal(got, want) and np.array_equal(np.signbit(got), np.signbit(want))
     np.testing.assert_array_equal(R.round_e5m2(np.array([6e4, -1e9], dtype=np.float32)),
                                   np.array([57344.0, -57344.0], dtype=np.float32))
+
+
+@pytest.mark.parametrize("name", list(cases.EPILOGUE_CASES))
+def test_epilogues_match_interpreter_fixture(golden, name):
+    """Fixtures produced by the reference's matmul_kernel with epilogues
+    (python/test/unit/hopper/test_gemm.py:143-247) under the interpreter: the bias epilogues are
+    reproduced bit for bit (same tile loop, same two roundings); the softmax epilogue within the
+    reference test's own tolerance (rows normalised, rtol 1e-2, atol 1e-3; the interpreter sums the
+    fp16 numerators in fp16, the oracle in fp32)."""
+    c = cases.EPILOGUE_CASES[name]
+    a, b, bias = cases.epilogue_inputs(c)
+    for nm, t in (("a", a), ("b", b), ("bias", bias)):
+        assert golden[f"epilogue.{name}.sha_{nm}"].item() == sha(t), "input generator drifted"
+    want = golden[f"epilogue.{name}.z"].astype(np.float32)
+    af, bf, biasf = a.float().numpy(), b.float().numpy(), bias.float().numpy()
+    ep = c["epilogue"]
+    if ep == "softmax":
+        got = R.matmul(af, bf, activation="softmax", out=c["out"], BM=64, BN=c["N"], BK=32)
+        nz = lambda x: x / np.linalg.norm(x, axis=1, keepdims=True)
+        np.testing.assert_allclose(nz(got), nz(want), rtol=1e-2, atol=1e-3)
+        np.testing.assert_allclose(got.sum(1), 1.0, atol=5e-3)
+    else:
+        bsel = {"add-matrix": biasf, "add-rows": biasf[:, :1], "add-cols": biasf[:1, :]}[ep]
+        got = R.matmul(af, bf, out=c["out"], BM=64, BN=64, BK=32, bias=bsel)
+        np.testing.assert_array_equal(got, want)
