@@ -87,6 +87,41 @@ def test_forward_ragged_lengths(dtype, D, N, causal):
 
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("where", ["first_half", "second_half", "growing", "one_row"])
+def test_forward_scores_far_above_the_first_block(dtype, D, causal, where):
+    """The 16-bit forward takes the row maximum on a row's first block only and moves the reference
+    point of a row when a later half block's probabilities sum too high; these inputs make that
+    happen in the first half of a block, in the second half (after the P V MMAs on the first half
+    were issued), in every block, and for a single row of a warp."""
+    N = 768
+    c = dict(Z=1, H=2, N=N, D=D, dtype=dtype, seed=7 * D + len(where))
+    q, k, v, _ = cases.attn_inputs(c)
+    k = k.float()
+    if where == "first_half":
+        k[:, :, 256 + 5] *= 40.0
+        k[:, :, 640 + 17] *= 90.0
+    elif where == "second_half":
+        k[:, :, 256 + 64 + 9] *= 40.0
+        k[:, :, 512 + 127] *= 90.0
+    elif where == "growing":
+        k *= (1.0 + torch.arange(N).float() / 16.0)[None, None, :, None]
+    else:
+        q = q.float()
+        q[:, :, 700] *= 30.0
+        k[:, :, 300:] *= 4.0
+        q = q.to(v.dtype)
+    k = k.to(v.dtype)
+    sm_scale = 0.5
+    got = run_gpu(q, k, v, None, causal, sm_scale, False)
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), causal, sm_scale, dtype)
+    np.testing.assert_allclose(got["o"], o, rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(got["m"], M, rtol=1e-4, atol=1e-3)
+    assert np.isfinite(got["o"]).all() and np.isfinite(got["m"]).all()
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("D", [64, 128])
 def test_backward_noncausal(dtype, D):
     c = dict(Z=2, H=2, N=384, D=D, dtype=dtype, seed=77 + D)
     q, k, v, do = cases.attn_inputs(c)

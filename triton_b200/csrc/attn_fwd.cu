@@ -263,7 +263,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           advance();
           const uint32_t ks = s, kph = ph;  // K_{j+1} (if any)
           const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
           mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x60);
           if (j < n0) {
             issue_pv(0, vs, j > 0, pcnt[0]++ & 1u);
             if (j == n0 - 1) tc_commit_elect(&o_full[0]);
@@ -457,8 +459,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tmem_ld32(tm_o[i] + lane_addr + c, o);
           tmem_ld32(tm_o[i] + lane_addr + c + 32, o + 32);
           tmem_ld_wait();
+          if (traced) B200_TRACE_EVENT(p.status, i, 0xA);
           if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging buffer
           __syncwarp();
+          if (traced) B200_TRACE_EVENT(p.status, i, 0xB);
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
             uint32_t wv[4];
@@ -469,6 +473,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           fence_proxy_async_smem();
           __syncwarp();
+          if (traced) B200_TRACE_EVENT(p.status, i, 0xC);
           if (lane == 0 && warp_row0 < p.N) {
             tma_store_4d(&tm_o_map, stg, c, warp_row0, it.h, it.z);
             tma_store_commit();

@@ -18,8 +18,11 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 REGIONS, EVENTS = 4, 4096  # kTraceRegions, kTraceEvents of csrc/trace.h
 
 FWD_TAGS = {1: "wait for S (MMA of this tile + hand-over)", 2: "TMEM load + row maximum", 3: "rescale decision (+ O rescale)",
-            4: "exp2, pack, P store, arrive", 8: "wait for the last P V (o_full)", 9: "epilogue (O / l, stores)"}
-FWD_MMA = {0x10: "before the wait for P", 0x20: "P arrived", 0x40: "S issued (includes the P V issue before it)"}
+            4: "exp2, pack, P store, arrive", 8: "wait for the last P V (o_full)", 9: "epilogue: store issue, M",
+            0xA: "epilogue: TMEM load of 64 columns", 0xB: "epilogue: wait for the staging buffer",
+            0xC: "epilogue: scale, pack, staging write, fence"}
+FWD_MMA = {0x10: "P V issued / before the wait for P", 0x20: "P arrived", 0x40: "S issued",
+           0x50: "tile 1's S issued; before the wait for V", 0x60: "V arrived"}
 BWD_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3: "wait for T2 (dP)",
             4: "dS, store, arrive", 8: "wait for the last accumulate (acc_full)", 9: "epilogue (gradient stores)"}
 
