@@ -2,7 +2,7 @@
 
 The reference's hot-path kernels are Python source written in the `tl` DSL.  This
 script loads their text at run time from a checkout of the reference (argument
---reference, default the read-only mount of this build container), executes them on
+--reference or the environment variable TRITON_REFERENCE), executes them on
 the CPU through the Triton interpreter (TRITON_INTERPRET=1, the pip `triton` package
 is the executor), and stores the outputs as small .npz fixtures.  Nothing of the
 reference is copied into this repository: only numeric outputs are written.
@@ -23,7 +23,7 @@ Inputs are not stored; they are regenerated from seeds by `cases.py` (shared wit
 the tests), and a SHA-256 of every input is stored so that drift of the generator is
 detected instead of silently comparing different data.
 
-Run:  python tests/golden/make_golden.py [--reference /path/to/triton] [--only name]
+Run:  python tests/golden/make_golden.py --reference /path/to/triton [--only name]
 """
 import argparse
 import ast
@@ -228,7 +228,8 @@ GENS = {"matmul": gen_matmul, "fp8": gen_fp8, "epilogue": gen_epilogue, "attn": 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("TRITON_REFERENCE"), required=not os.environ.get("TRITON_REFERENCE"),
+                    help="checkout of the reference project (or set TRITON_REFERENCE)")
     ap.add_argument("--only", default=None)
     args = ap.parse_args()
     for name, fn in GENS.items():
