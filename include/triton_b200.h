@@ -82,6 +82,19 @@ B200_API int b200_matmul_splitk(b200_stream_t stream, const void* a, const void*
                                 int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
                                 const float* scale_a, const float* scale_b, int splits, float* workspace);
 
+/* The reference's 'chain-dot' epilogue (python/test/unit/hopper/test_gemm.py:229-232: `w = tl.load(w_tile_ptr);
+ * z = tl.dot(z.to(w.dtype), w); z = z.to(out_dtype)`, case list :269-284) as one launch:
+ * c[M,N2] = out_type( in_type(out_type(a[M,K] @ b[K,N])) @ w[N,N2] ), fp32 accumulation in both
+ * products, the intermediate rounded to the output type and then to the input type as the reference
+ * does.  a, b, w: F16 or BF16 (one type), element strides as in b200_matmul (w[k * stride_wk +
+ * n * stride_wn]); a row of a @ b stays in one tile, so N and N2 are at most 128
+ * (B200_ERR_UNSUPPORTED beyond; the reference's test uses BLOCK_N == N); operands must be
+ * addressable by TMA (16-byte aligned base and rows). */
+B200_API int b200_matmul_chain(b200_stream_t stream, const void* a, const void* b, const void* w, void* c, int M, int N,
+                               int K, int N2, int64_t stride_am, int64_t stride_ak, int64_t stride_bk,
+                               int64_t stride_bn, int64_t stride_wk, int64_t stride_wn, int64_t stride_cm,
+                               int64_t stride_cn, int in_dtype, int out_dtype);
+
 /* Matmul with the reference's bias epilogues (python/test/unit/hopper/test_gemm.py:213-222, cases
  * 'add-matrix', 'add-rows', 'add-cols' at :281): c = out_type(act(scale * a @ b)) + bias, the sum
  * formed in the output type as the reference does (`z = z.to(out_dtype); z += bias`).  `bias` has

@@ -17,7 +17,7 @@ bf16, which is what the reference's GPU lowering does (cvt.rn, third_party/nvidi
 TritonNVIDIAGPUToLLVM/ElementwiseOpToLLVM.cpp:346,368); the interpreter truncates
 fp32->bf16 and cannot run bf16 dots at all, so the bf16 mode of this oracle is
 pinned through its fp16 mode (same code, only the rounding function differs).
-The bias and row-softmax epilogues (`add_bias`, `softmax_epilogue`) are pinned the same
+The bias, row-softmax and chain-dot epilogues (`add_bias`, `softmax_epilogue`, `matmul_chain`) are pinned the same
 way: against tests/golden/epilogue.npz, produced by the reference's own epilogue kernel
 (python/test/unit/hopper/test_gemm.py:143-247) under the interpreter; the two 8-bit
 roundings (`round_e4m3`, `round_e5m2`) are pinned bit for bit against torch's float8
@@ -173,6 +173,25 @@ def softmax_epilogue(c, out):
     num = rnd(np.exp(z, dtype=np.float32))
     den = rnd(num.sum(axis=1, keepdims=True, dtype=np.float32))
     return rnd(num / den)
+
+
+def matmul_chain(a, b, w, out="fp16", storage="fp16", BM=128, BK=64):
+    """The 'chain-dot' epilogue of python/test/unit/hopper/test_gemm.py:229-232 after the K loop of
+    :205-210: z = (A @ B in fp32).to(out); z = dot(z.to(w.dtype), w) in fp32; z = z.to(out).
+    BLOCK_N is N (the reference's condition for this epilogue, :187), so a program owns BM whole
+    rows; `storage` is the operands' type."""
+    a, b, w = (np.asarray(t, dtype=np.float32) for t in (a, b, w))
+    M, K = a.shape
+    N = b.shape[1]
+    rnd_out = ROUND.get(out, lambda v: np.asarray(v, dtype=np.float32))
+    c = np.zeros((M, w.shape[1]), dtype=np.float32)
+    for m0 in range(0, M, BM):
+        acc = np.zeros((min(BM, M - m0), N), dtype=np.float32)
+        for k0 in range(0, K, BK):
+            acc = np.matmul(a[m0:m0 + BM, k0:k0 + BK], b[k0:k0 + BK], dtype=np.float32) + acc
+        z = ROUND[storage](rnd_out(acc))
+        c[m0:m0 + BM] = rnd_out(np.matmul(z, w, dtype=np.float32))
+    return c
 
 
 def matmul_fp8(a_bits, b_bits, scale_a=None, scale_b=None, out="bf16", BM=128, BN=256, BK=128):

@@ -25,6 +25,9 @@ EPILOGUE_CASES = {
     "add_cols_f32": dict(M=128, N=256, K=64, seed=43, epilogue="add-cols", out="fp32"),
     "softmax_f16": dict(M=128, N=128, K=128, seed=44, epilogue="softmax", out="fp16", scale=3.0),
     "softmax_f32": dict(M=64, N=64, K=64, seed=45, epilogue="softmax", out="fp32", scale=2.0),
+    # chain-dot: BLOCK_N == N, W [N, N] (the reference's cases are M = N = K = BLOCK: test_gemm.py:269-284)
+    "chain_dot_f16": dict(M=128, N=128, K=128, seed=46, epilogue="chain-dot", out="fp16", scale=4.0),
+    "chain_dot_f32": dict(M=64, N=64, K=64, seed=47, epilogue="chain-dot", out="fp32", scale=4.0),
 }
 
 
@@ -37,6 +40,13 @@ def epilogue_inputs(c):
     b = (torch.randn(c["K"], c["N"], generator=g) / s).half()
     bias = torch.randn(c["M"], c["N"], generator=g).to(torch.float16 if c["out"] == "fp16" else torch.float32)
     return a, b, bias
+
+
+def chain_weight(c):
+    """W [N, N] fp16 of a chain-dot case, stored transposed as in the reference test
+    (`torch.randn((N, N)).T`, test_gemm.py:386)."""
+    g = torch.Generator().manual_seed(c["seed"] + 1000)
+    return (torch.randn(c["N"], c["N"], generator=g) / c.get("scale", 1.0)).half().T
 
 
 FP8_CASES = {

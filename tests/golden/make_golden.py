@@ -156,9 +156,9 @@ def gen_epilogue(ref_root, out):
         N = b.shape[1]
         odt = torch.float16 if c["out"] == "fp16" else torch.float32
         z = torch.full((M, N), 1.0, dtype=odt)
-        w = torch.zeros((N, N), dtype=torch.float16)
         ep = c["epilogue"]
-        BM, BN, BK = 64, (N if ep == "softmax" else 64), 32
+        w = cases.chain_weight(c) if ep == "chain-dot" else torch.zeros((N, N), dtype=torch.float16)
+        BM, BN, BK = 64, (N if ep in ("softmax", "chain-dot") else 64), 32
         grid = (triton.cdiv(M, BM) * triton.cdiv(N, BN),)
         t0 = time.time()
         kern[grid](a_ptr=a, b_ptr=b, w_ptr=w, bias_ptr=bias, z_ptr=z, M=M, N=N, K=K,
@@ -167,7 +167,7 @@ def gen_epilogue(ref_root, out):
                    BLOCK_M=BM, BLOCK_N=BN, BLOCK_K=BK, GROUP_SIZE_M=8,
                    out_dtype=tl.float16 if c["out"] == "fp16" else tl.float32, USE_TMA_STORE=False,
                    ADD_MATRIX=ep == "add-matrix", ADD_ROWS=ep == "add-rows", ADD_COLS=ep == "add-cols",
-                   DO_SOFTMAX=ep == "softmax", CHAIN_DOT=False,
+                   DO_SOFTMAX=ep == "softmax", CHAIN_DOT=ep == "chain-dot",
                    A_ORDER_0=1, A_ORDER_1=0, B_ORDER_0=1, B_ORDER_1=0, W_ORDER_0=0, W_ORDER_1=1,
                    Z_ORDER_0=1, Z_ORDER_1=0)
         print(f"epilogue {name}: {time.time()-t0:.2f}s")

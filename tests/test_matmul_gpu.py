@@ -535,10 +535,59 @@ def test_epilogues_against_interpreter_fixture(golden, name):
         got = f32(triton_b200.matmul(ad, bd, activation="softmax", out_dtype=dt))
         nz = lambda x: x / np.linalg.norm(x, axis=1, keepdims=True)
         np.testing.assert_allclose(nz(got), nz(want), rtol=1e-2, atol=1e-3)  # the reference test's check
+    elif ep == "chain-dot":
+        w = cases.chain_weight(c)
+        got = f32(triton_b200.matmul_chain(ad, bd, w.to(DEV), out_dtype=dt))
+        np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2 * np.abs(want).max())
     else:
         bsel = {"add-matrix": biasd, "add-rows": biasd[:, :1], "add-cols": biasd[:1, :]}[ep]
         got = f32(triton_b200.matmul(ad, bd, out_dtype=dt, bias=bsel))
         np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2)
         if c["out"] == "fp16":  # same roundings: all but a few elements bit-identical (fp32 outputs
             assert (got != want).mean() < 0.02  # differ in the last bits with the summation order)
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("out", ["same", "fp32"])
+@pytest.mark.parametrize("M,N,K,N2", [(128, 128, 128, 128), (64, 64, 64, 64), (300, 96, 200, 128), (1000, 128, 512, 80),
+                                      (5, 16, 8, 24), (4096, 128, 1024, 128)])
+@pytest.mark.parametrize("layout", ["row", "transposed"])
+def test_chain_dot(dtype, out, M, N, K, N2, layout):
+    """out_type(in_type(out_type(A B)) W) in one launch against the oracle's restatement of the
+    reference's chain-dot epilogue; ragged sizes, both operand layouts of B and W."""
+    tdt = torch.float16 if dtype == "fp16" else torch.bfloat16
+    odt = tdt if out == "same" else torch.float32
+    oname = dtype if out == "same" else "fp32"
+    g = torch.Generator().manual_seed(M + 3 * N + 5 * K + 7 * N2)
+    a = (torch.randn(M, K, generator=g) / K ** 0.25).to(tdt)
+    b = (torch.randn(K, N, generator=g) / K ** 0.25).to(tdt)
+    w = (torch.randn(N, N2, generator=g) / N ** 0.5).to(tdt)
+    ad = a.to(DEV)
+    if layout == "row":
+        bd, wd = b.to(DEV), w.to(DEV)
+    else:  # [N, K] and [N2, N] storage, passed as transposed views
+        bd, wd = b.t().contiguous().to(DEV).t(), w.t().contiguous().to(DEV).t()
+    got = f32(triton_b200.matmul_chain(ad, bd, wd, out_dtype=odt))
+    want = R.matmul_chain(f32(a), f32(b), f32(w), out=oname, storage=dtype)
+    tol = 1e-2 if dtype == "fp16" else 2e-2
+    np.testing.assert_allclose(got, want, rtol=tol, atol=tol * max(1.0, np.abs(want).max()))
+    # and against the same two products done by two launches of the plain matmul
+    two = f32(triton_b200.matmul(triton_b200.matmul(ad, bd, out_dtype=odt).to(tdt), wd, out_dtype=odt))
+    np.testing.assert_allclose(got, two, rtol=tol, atol=tol * max(1.0, np.abs(want).max()))
+    status_ok()
+
+
+def test_chain_dot_errors():
+    a = torch.zeros(128, 64, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError, match="at most 128"):
+        triton_b200.matmul_chain(a, torch.zeros(64, 256, dtype=torch.float16, device=DEV),
+                                 torch.zeros(256, 64, dtype=torch.float16, device=DEV))
+    with pytest.raises(AssertionError):
+        triton_b200.matmul_chain(a, torch.zeros(64, 64, dtype=torch.float16, device=DEV),
+                                 torch.zeros(32, 64, dtype=torch.float16, device=DEV))
+    z = triton_b200.matmul_chain(torch.zeros(16, 0, dtype=torch.float16, device=DEV),
+                                 torch.zeros(0, 32, dtype=torch.float16, device=DEV),
+                                 torch.ones(32, 32, dtype=torch.float16, device=DEV))
+    assert z.shape == (16, 32) and float(z.abs().max()) == 0.0
     status_ok()

@@ -194,7 +194,7 @@ def test_round_e5m2_matches_torch_and_saturates():
 def test_epilogues_match_interpreter_fixture(golden, name):
     """Fixtures produced by the reference's matmul_kernel with epilogues
     (python/test/unit/hopper/test_gemm.py:143-247) under the interpreter: the bias epilogues are
-    reproduced bit for bit (same tile loop, same two roundings); the softmax epilogue within the
+    reproduced bit for bit (same tile loop, same two roundings), and so is chain-dot; the softmax epilogue within the
     reference test's own tolerance (rows normalised, rtol 1e-2, atol 1e-3; the interpreter sums the
     fp16 numerators in fp16, the oracle in fp32)."""
     c = cases.EPILOGUE_CASES[name]
@@ -209,6 +209,12 @@ def test_epilogues_match_interpreter_fixture(golden, name):
         nz = lambda x: x / np.linalg.norm(x, axis=1, keepdims=True)
         np.testing.assert_allclose(nz(got), nz(want), rtol=1e-2, atol=1e-3)
         np.testing.assert_allclose(got.sum(1), 1.0, atol=5e-3)
+    elif ep == "chain-dot":  # same tile loop and the same three roundings: bit for bit
+        w = cases.chain_weight(c).float().numpy()
+        got = R.matmul_chain(af, bf, w, out=c["out"], storage="fp16", BM=64, BK=32)
+        np.testing.assert_array_equal(got, want)
+        exact = (af.astype(np.float64) @ bf.astype(np.float64)) @ w.astype(np.float64)
+        np.testing.assert_allclose(got, exact, rtol=1e-2, atol=1e-2 * np.abs(exact).max())
     else:
         bsel = {"add-matrix": biasf, "add-rows": biasf[:, :1], "add-cols": biasf[:1, :]}[ep]
         got = R.matmul(af, bf, out=c["out"], BM=64, BN=64, BK=32, bias=bsel)

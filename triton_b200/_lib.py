@@ -27,6 +27,7 @@ SIGNATURES = {
     "b200_matmul_splitk": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p, _i, _p],
     "b200_matmul_bias": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p,
                          _p, _i, _i64, _i64, _i, _p],
+    "b200_matmul_chain": [_p, _p, _p, _p, _p, _i, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i],
     "b200_grouped_matmul_workspace": [_i],
     "b200_grouped_matmul": [_p, _i, _p, _p, _p, _p, _p, _i, _i, _p],
     "b200_grouped_matmul_prepare": [_p, _i, _p, _p, _p, _p, _p, _i, _i, _p, ctypes.POINTER(ctypes.c_int)],

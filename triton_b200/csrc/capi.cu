@@ -238,6 +238,32 @@ int b200_matmul_splitk(b200_stream_t stream, const void* a, const void* b, void*
                           workspace);
 }
 
+int b200_matmul_chain(b200_stream_t stream, const void* a, const void* b, const void* w, void* c, int M, int N, int K,
+                      int N2, int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
+                      int64_t stride_wk, int64_t stride_wn, int64_t stride_cm, int64_t stride_cn, int in_dtype,
+                      int out_dtype) {
+  if (M < 0 || N < 0 || K < 0 || N2 < 0) return fail(B200_ERR_ARG, "negative dimension");
+  if (in_dtype != B200_F16 && in_dtype != B200_BF16) return fail(B200_ERR_ARG, "chain-dot: in_dtype must be F16 or BF16");
+  if (out_dtype != B200_F16 && out_dtype != B200_BF16 && out_dtype != B200_F32)
+    return fail(B200_ERR_ARG, "chain-dot: out_dtype must be F16, BF16 or F32");
+  if (N > 128 || N2 > 128)
+    return fail(B200_ERR_UNSUPPORTED, "chain-dot keeps a whole row of A B in one tile: N and N2 must be at most 128");
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return B200_ERR_DEVICE;
+  if (M == 0 || N2 == 0) return B200_OK;
+  if (!c || (N > 0 && !w) || (N > 0 && K > 0 && (!a || !b))) return fail(B200_ERR_ARG, "null pointer");
+  if (stride_cn != 1 && N2 != 1) return fail(B200_ERR_UNSUPPORTED, "C must have stride_cn == 1");
+  if (K == 0 || N == 0) {  // an empty sum in either product: zeros
+    const int es = dtype_bytes(out_dtype);
+    cudaError_t e = cudaMemset2DAsync(c, (size_t)stride_cm * es, 0, (size_t)N2 * es, (size_t)M,
+                                      reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "memset: %s", cudaGetErrorString(e));
+    return B200_OK;
+  }
+  return launch_gemm_chain(ctx, reinterpret_cast<cudaStream_t>(stream), a, b, w, c, M, N, K, N2, stride_am, stride_ak,
+                           stride_bk, stride_bn, stride_wk, stride_wn, stride_cm, in_dtype, out_dtype);
+}
+
 int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                      int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn, int64_t stride_cm,
                      int64_t stride_cn, int in_dtype, int out_dtype, int activation, const float* scale_a,

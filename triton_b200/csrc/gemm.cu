@@ -73,6 +73,10 @@ struct GemmParams {
   long long bias_sm, bias_sn;
   uint32_t idesc;
   OperandGeom ga, gb;
+  // chain-dot (gemm_chain_kernel): second product with W
+  int in_bf16;       // 16-bit input type: 0 fp16, 1 bf16
+  uint32_t idesc2;   // Z (TMEM) x W
+  OperandGeom gw;
 };
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& pid_m, int& pid_n) {
@@ -482,6 +486,146 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------- chain-dot
+// C = out_type( in_type(out_type(A B)) W ), the reference's 'chain-dot' epilogue
+// (python/test/unit/hopper/test_gemm.py:229-232): one 128-row tile per CTA spans all N <= 128
+// columns of A B, whose rounded values go back into TMEM as the 16-bit A operand of a second
+// product with W [N, N2 <= 128] (shared memory, loaded once), as P does in the attention kernels.
+// TMEM: columns [0,128) A B, [128,192) Z (two values per column), [256,384) Z W.
+// warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 conversion and epilogue.
+template <int STAGES>
+__global__ void __launch_bounds__(192, 1)
+gemm_chain_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                  const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_c,
+                  const GemmParams p) {
+  constexpr int BM = 128, BN = 128;
+  constexpr uint32_t A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TM_ACC1 = 0, TM_Z = 128, TM_ACC2 = 256;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;
+  uint8_t* sw = smem + STAGES * STAGE_BYTES;       // W: two K blocks of 64 rows
+  uint8_t* staging = sw + 2 * B_BYTES;             // one 4 KiB buffer per epilogue warp
+  uint64_t* full = reinterpret_cast<uint64_t*>(staging + 4 * STG_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* w_full = empty + STAGES;
+  uint64_t* acc1_full = w_full + 1;
+  uint64_t* z_full = acc1_full + 1;
+  uint64_t* acc2_full = z_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc2_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.x * BM;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(w_full, 1);
+    mbar_init(acc1_full, 1);
+    mbar_init(z_full, 4);  // one arrival per conversion warp
+    mbar_init(acc2_full, 1);
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+    tma_prefetch_desc(&tma_w);
+    if (p.c_tma) tma_prefetch_desc(&tma_c);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(w_full, 2 * B_BYTES);
+      for (int kb = 0; kb < 2; ++kb) load_operand<false>(p.gw, &tma_w, sw + kb * B_BYTES, w_full, kb * p.bk_elems, 0);
+      uint32_t s = 0, ph = 0;
+      for (int kb = 0; kb < p.num_k; ++kb) {
+        mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        uint8_t* a_dst = smem + s * STAGE_BYTES;
+        load_operand<false>(p.ga, &tma_a, a_dst, &full[s], kb * p.bk_elems, m0);
+        load_operand<false>(p.gb, &tma_b, a_dst + A_BYTES, &full[s], kb * p.bk_elems, 0);
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    const uint64_t da0 = smem_desc_sw128(smem_u32(smem), p.ga.lbo, p.ga.sbo);
+    const uint64_t db0 = smem_desc_sw128(smem_u32(smem) + A_BYTES, p.gb.lbo, p.gb.sbo);
+    const uint64_t dw0 = smem_desc_sw128(smem_u32(sw), p.gw.lbo, p.gw.sbo);
+    const uint32_t ka = p.ga.kstep_bytes >> 4, kb16 = p.gb.kstep_bytes >> 4, kw = p.gw.kstep_bytes >> 4;
+    uint32_t s = 0, ph = 0, accum = 0;
+    for (int kb = 0; kb < p.num_k; ++kb) {
+      mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);
+      const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
+#pragma unroll
+      for (int k = 0; k < KBYTES / 32; ++k) {
+        umma_ss_elect<false>(tmem_base + TM_ACC1, das + k * ka, dbs + k * kb16, p.idesc, accum);
+        accum = 1;
+      }
+      tc_commit_elect(&empty[s]);
+      if (++s == STAGES) { s = 0; ph ^= 1u; }
+    }
+    tc_commit_elect(acc1_full);
+    // second product: Z (TMEM, 8 columns per 16 values of K) x W
+    mbar_wait(w_full, 0, p.status, SITE_GEMM_FULL);
+    mbar_wait(z_full, 0, p.status, SITE_GEMM_TMEM_EMPTY);
+    tc_fence_after();
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk)
+      umma_ts_f16_elect(tmem_base + TM_ACC2, tmem_base + TM_Z + kk * 8, dw0 + (kk >> 2) * (B_BYTES >> 4) + (kk & 3) * kw,
+                        p.idesc2, kk != 0);
+    tc_commit_elect(acc2_full);
+    __syncwarp();
+  } else {
+    const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may access: [32*quarter, +32)
+    const uint32_t lane_addr = (quarter * 32u) << 16;
+    const int esize = (p.out_dtype == B200_F32) ? 4 : 2;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.c) & 15) == 0) && (((p.ldc * esize) & 15) == 0);
+    mbar_wait(acc1_full, 0, p.status, SITE_GEMM_TMEM_FULL);
+    tc_fence_after();
+    // z = out_type(acc), then the input type: the two roundings of the reference, in its order
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t r[32], wv[16];
+      tmem_ld32(tmem_base + TM_ACC1 + lane_addr + c, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        const float z0 = round_out(__uint_as_float(r[2 * k]), p.out_dtype);
+        const float z1 = round_out(__uint_as_float(r[2 * k + 1]), p.out_dtype);
+        wv[k] = p.in_bf16 ? pack2<true>(z0, z1) : pack2<false>(z0, z1);
+      }
+      tmem_st16(tmem_base + TM_Z + lane_addr + (c >> 1), wv);
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(z_full);
+    mbar_wait(acc2_full, 0, p.status, SITE_GEMM_TMEM_FULL);
+    tc_fence_after();
+    drain_accumulator<false>(p, &tma_c, staging + (warp - 2) * STG_BYTES, tmem_base + TM_ACC2 + lane_addr, BN,
+                             m0 + quarter * 32, 0, lane, 1.f, vec_ok);
+    if (p.c_tma && lane == 0) tma_store_wait_all<0>();
+  }
+
+  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -1136,6 +1280,70 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   else splitk_reduce_kernel<1><<<rgrid, tpb, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "split-K reduce launch: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
+// C[M,N2] = out_type( in_type(out_type(A[M,K] B[K,N])) W[N,N2] ) in one launch (gemm_chain_kernel).
+// 16-bit inputs, N and N2 at most 128, operands that TMA can address.
+int launch_gemm_chain(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* b, const void* w, void* c, int M,
+                      int N, int K, int N2, int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t swk, int64_t swn,
+                      int64_t scm, int in_dtype, int out_dtype) {
+  const int elt = 2, bk_elems = KBYTES / elt;
+  const bool a_mn = !(sak == 1 || K == 1), b_mn = !(sbk == 1 || K == 1), w_mn = !(swk == 1 || N == 1);
+  auto tma_ok = [&](const void* base, int64_t row_stride) {
+    return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ((row_stride * elt) & 15) == 0;
+  };
+  if (!(tma_ok(a, a_mn ? sak : sam) || (a_mn ? K : M) == 1) || !(tma_ok(b, b_mn ? sbk : sbn) || (b_mn ? K : N) == 1) ||
+      !(tma_ok(w, w_mn ? swk : swn) || (w_mn ? N : N2) == 1) || (a_mn && sam != 1) || (b_mn && sbn != 1) ||
+      (w_mn && swn != 1))
+    return fail(B200_ERR_UNSUPPORTED, "chain-dot needs A, B and W that TMA can address (16-byte aligned base and rows)");
+  GemmParams p{};
+  p.c = c; p.M = M; p.N = N2; p.K = K; p.ldc = scm;
+  p.out_dtype = out_dtype; p.activation = B200_ACT_NONE; p.status = ctx->status;
+  p.num_k = (K + bk_elems - 1) / bk_elems;
+  p.bk_elems = bk_elems;
+  p.splits = 1; p.kb_per_split = p.num_k;
+  p.in_bf16 = (in_dtype == B200_BF16);
+  const int fmt = p.in_bf16 ? 1 : 0;
+  p.idesc = make_idesc(fmt, fmt, a_mn, b_mn, 128, 128);
+  p.idesc2 = make_idesc(fmt, fmt, 0, w_mn, 128, 128);
+  p.ga = make_geom(a_mn, 128, elt, bk_elems);
+  p.gb = make_geom(b_mn, 128, elt, bk_elems);
+  p.gw = make_geom(w_mn, 128, elt, bk_elems);
+  CUtensorMap ta, tbm, tw;
+  {
+    uint64_t dims[2], strides[1];
+    uint32_t box[2];
+    if (!a_mn) { dims[0] = K; dims[1] = M; strides[0] = (uint64_t)sam * elt; box[0] = bk_elems; box[1] = 128; }
+    else       { dims[0] = M; dims[1] = K; strides[0] = (uint64_t)sak * elt; box[0] = p.ga.box_mn; box[1] = bk_elems; }
+    if (!encode_tmap(&ta, in_dtype, 2, a, dims, strides, box, true)) return B200_ERR_UNSUPPORTED;
+    if (!b_mn) { dims[0] = K; dims[1] = N; strides[0] = (uint64_t)sbn * elt; box[0] = bk_elems; box[1] = 128; }
+    else       { dims[0] = N; dims[1] = K; strides[0] = (uint64_t)sbk * elt; box[0] = p.gb.box_mn; box[1] = bk_elems; }
+    if (!encode_tmap(&tbm, in_dtype, 2, b, dims, strides, box, true)) return B200_ERR_UNSUPPORTED;
+    // W as the B operand of the second product: its "K" is N, its "N" is N2
+    if (!w_mn) { dims[0] = N; dims[1] = N2; strides[0] = (uint64_t)swn * elt; box[0] = bk_elems; box[1] = 128; }
+    else       { dims[0] = N2; dims[1] = N; strides[0] = (uint64_t)swk * elt; box[0] = p.gw.box_mn; box[1] = bk_elems; }
+    if (!encode_tmap(&tw, in_dtype, 2, w, dims, strides, box, true)) return B200_ERR_UNSUPPORTED;
+  }
+  CUtensorMap tcm = ta;
+  p.c_tma = 0;
+  if ((out_dtype == B200_F16 || out_dtype == B200_BF16) && (reinterpret_cast<uintptr_t>(c) & 15) == 0 &&
+      ((scm * 2) & 15) == 0) {
+    uint64_t dims[2] = {(uint64_t)N2, (uint64_t)M}, strides[1] = {(uint64_t)scm * 2};
+    uint32_t box[2] = {64, 32};
+    if (encode_tmap(&tcm, out_dtype, 2, c, dims, strides, box, true)) p.c_tma = 1;
+  }
+  constexpr int STAGES = 4;
+  constexpr size_t smem = (size_t)STAGES * 256 * KBYTES + 2 * 128 * KBYTES + 4 * STG_BYTES + (2 * STAGES + 6) * 8 + 16 + 1024;
+  static bool attr_done[64] = {};
+  if (!attr_done[ctx->device]) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_chain_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(chain gemm): %s", cudaGetErrorString(e));
+    attr_done[ctx->device] = true;
+  }
+  gemm_chain_kernel<STAGES><<<(M + 127) / 128, 192, smem, stream>>>(ta, tbm, tw, tcm, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "chain gemm launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
 

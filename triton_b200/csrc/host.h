@@ -44,6 +44,9 @@ inline int dtype_bytes(int dt) {
 }
 
 // launchers implemented in the kernel translation units
+int launch_gemm_chain(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* b, const void* w, void* c, int M,
+                      int N, int K, int N2, int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t swk, int64_t swn,
+                      int64_t scm, int in_dtype, int out_dtype);
 int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                 int64_t sam, int64_t sak, int64_t sbk, int64_t sbn, int64_t scm, int in_dtype, int out_dtype,
                 int activation, const float* scale_a, const float* scale_b, const void* bias, int bias_mode,

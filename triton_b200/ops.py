@@ -105,6 +105,29 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
     return c
 
 
+def matmul_chain(a, b, w, *, out_dtype=None):
+    """out_type( in_type(out_type(A @ B)) @ W ): the reference's 'chain-dot' epilogue
+    (python/test/unit/hopper/test_gemm.py:229-232) in one launch.  a [M, K], b [K, N], w [N, N2],
+    fp16 or bf16, N and N2 at most 128 (a row of A @ B stays in one tile, as with the reference's
+    BLOCK_N == N); `out_dtype` fp16 / bf16 / fp32 (default: the input type)."""
+    assert a.dim() == 2 and b.dim() == 2 and w.dim() == 2, "matmul_chain takes 2-D tensors"
+    assert a.shape[1] == b.shape[0] and b.shape[1] == w.shape[0], "Incompatible dimensions"
+    assert a.dtype == b.dtype == w.dtype and a.dtype in (torch.float16, torch.bfloat16), "fp16 or bf16 operands"
+    dev = _require_cuda(a, b, w)
+    M, K = a.shape
+    N, N2 = w.shape
+    if out_dtype is None:
+        out_dtype = a.dtype
+    with torch.cuda.device(dev):
+        c = torch.empty((M, N2), device=dev, dtype=out_dtype)
+        code = _lib.lib().b200_matmul_chain(
+            _stream(a), a.data_ptr(), b.data_ptr(), w.data_ptr(), c.data_ptr(), M, N, K, N2,
+            a.stride(0), a.stride(1), b.stride(0), b.stride(1), w.stride(0), w.stride(1), c.stride(0), c.stride(1),
+            _DT[a.dtype], _DT[out_dtype])
+        _lib.check(code, "matmul_chain")
+    return c
+
+
 class GroupedMatmul:
     """A prepared grouped matmul: the groups' descriptors (pointers, sizes, tensor maps) are written
     to device memory once; `run()` is one persistent launch and can be repeated while the operand
