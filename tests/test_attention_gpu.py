@@ -390,3 +390,26 @@ def test_custom_ops_on_gpu():
     torch.library.opcheck(ns.attention.default, (qg.detach().requires_grad_(), k, v, True, 0.125),
                           test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
     status_ok()
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("D", [16, 32])
+@pytest.mark.parametrize("causal", [True, False])
+def test_small_head_dims_run_zero_padded(dtype, D, causal):
+    """Head dims 16 and 32 of the reference's set (06-fused-attention.py:447) run on the head-dim-64
+    kernels with zero columns appended; forward and backward against the oracle at the true D."""
+    c = dict(Z=1, H=2, N=256, D=D, dtype=dtype, seed=900 + D)
+    q, k, v, do = cases.attn_inputs(c)
+    sm_scale = 0.5
+    got = run_gpu(q, k, v, do, causal, sm_scale, True)
+    assert got["o"].shape == (1, 2, 256, D) and got["dq"].shape == (1, 2, 256, D)
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), causal, sm_scale, dtype)
+    np.testing.assert_allclose(got["o"], o, rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(got["m"], M, rtol=1e-4, atol=1e-3)
+    if causal:
+        dq, dk, dv = R.attention_bwd(f32(q), f32(k), f32(v), o, f32(do), M, sm_scale, dtype)
+    else:
+        dq, dk, dv = R.attention_bwd_full(f32(q), f32(k), f32(v), o, f32(do), M, sm_scale, False, dtype)
+    tol = 1e-2 if dtype == "fp16" else 2e-2
+    for key, want in (("dq", dq), ("dk", dk), ("dv", dv)):
+        np.testing.assert_allclose(got[key], want, rtol=1e-2, atol=tol, err_msg=key)

@@ -246,11 +246,17 @@ def attention_forward(q, k, v, causal, sm_scale):
     HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
     assert q.dim() == 4 and k.shape == q.shape and v.shape == q.shape, "q, k, v must be [Z, H, N, D] of one shape"
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
-    assert HEAD_DIM_K in {16, 32, 64, 128, 256}  # the reference's set; this library has kernels for 64 and 128
+    # the reference's set; kernels exist for 64 and 128, 16 and 32 run zero-padded to 64, 256 is rejected by the library
+    assert HEAD_DIM_K in {16, 32, 64, 128, 256}
     fp8 = hasattr(torch, "float8_e5m2") and q.dtype == torch.float8_e5m2
     assert (q.dtype in (torch.float16, torch.bfloat16) or fp8) and k.dtype == q.dtype and v.dtype == q.dtype
     dev = _require_cuda(q, k, v)
     Z, H, N, D = q.shape
+    if D in (16, 32) and not fp8:
+        # head dims below the kernels' 64: zero columns change neither q k^T nor the kept columns of O
+        qp, kp, vp = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v))
+        o, M = attention_forward(qp, kp, vp, causal, sm_scale)
+        return o[..., :D].contiguous(), M
     with torch.cuda.device(dev):
         if fp8:
             # the reference's fp8 forward (06-fused-attention.py:609-615) is given V with the key
@@ -277,6 +283,9 @@ def attention_backward(q, k, v, o, M, do, causal, sm_scale):
     Z, H, N, D = q.shape
     assert N % 128 == 0
     dev = _require_cuda(q, k, v, o, do, M)
+    if D in (16, 32):  # as in attention_forward: zero-padded to the kernels' head dim 64
+        qp, kp, vp, op, dop = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v, o, do))
+        return tuple(g[..., :D].contiguous() for g in attention_backward(qp, kp, vp, op, M, dop, causal, sm_scale))
     with torch.cuda.device(dev):
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
