@@ -17,7 +17,8 @@
 //       P  = exp2(T1 * scale - M) masked;   dS = P * (T2 - delta)       (fp32, two threads per row)
 //       accB += P  U2       (dV += P^T dO; dK/dV kernel only)
 //       accA += dS U1       (dK += dS^T Q, or dQ += dS K)
-//   T1/T2 live in TMEM and P/dS overwrite them as 16-bit A operands of the last two MMAs (each
+//   T1/T2 live in TMEM (at head dim 64 there are two T1 buffers used in turn, so T1 of the next
+//   step is computed during this step) and P/dS overwrite them as 16-bit A operands of the last two MMAs (each
 //   thread over the first 32 of its own 64 columns), which read U1/U2 through an N-major view of
 //   the same shared-memory tiles.  Gradients leave through staging buffers and TMA stores.
 // Warps 0-7 compute (two threads per row, splitting the columns), warp 8 issues MMAs, warp 9 runs TMA.
@@ -56,7 +57,7 @@ struct BwdCfg {
   static constexpr int NST = (D == 128) ? 2 : 3;
   static constexpr int STAGE = 2 * TILE + 1024;  // U1, U2, column statistics (M, delta of the streamed rows)
   static constexpr int STG_BYTES = 32 * 64;  // epilogue staging of one compute warp: 32 rows x 32 columns
-  static constexpr size_t SMEM = 2 * TILE + (size_t)NST * STAGE + 8 * STG_BYTES + (2 * NST + 14) * 8 + 32 + 1024;
+  static constexpr size_t SMEM = 2 * TILE + (size_t)NST * STAGE + 8 * STG_BYTES + (2 * NST + 16) * 8 + 32 + 1024;
 };
 
 template <int D>
@@ -113,8 +114,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   uint64_t* r_empty = bars + 1;         // every T MMA of the item has read them
   uint64_t* full = bars + 2;            // [NST]
   uint64_t* empty = full + NST;         // [NST]
-  uint64_t* t1_full = empty + NST;      // T1(t) in TMEM
-  uint64_t* t2_full = t1_full + 1;      // T2(t) in TMEM
+  uint64_t* t1_full = empty + NST;      // [2] T1(t) in TMEM (head dim 64: two T1 buffers used in turn, one barrier each)
+  uint64_t* t2_full = t1_full + 2;      // T2(t) in TMEM
   uint64_t* p_full = t2_full + 1;       // P(t) written (dK/dV kernel)
   uint64_t* ds_full = p_full + 1;       // dS(t) written
   uint64_t* acc_full = ds_full + 1;     // accumulators of the item final
@@ -133,7 +134,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(t1_full, 1);
+    mbar_init(&t1_full[0], 1);
+    mbar_init(&t1_full[1], 1);
     mbar_init(t2_full, 1);
     mbar_init(p_full, 256);
     mbar_init(ds_full, 256);
@@ -156,7 +158,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
-  const uint32_t tm_t1 = tmem_base, tm_t2 = tmem_base + 128, tm_a = tmem_base + 256, tm_b = tmem_base + 256 + D;
+  const uint32_t tm_t2 = tmem_base + 128, tm_a = tmem_base + 256, tm_b = tmem_base + 256 + D;
+  // At head dim 64 the accumulators leave 128 TMEM columns free: a second T1 buffer, so that the
+  // scores of step t+1 are computed while the compute warps still work on step t (P / dS overwrite
+  // T1 / T2 in place, so with one buffer T1(t+1) has to wait until P(t) has been consumed).
+  constexpr bool DB = (D == 64);
+  auto t1_addr = [&](uint32_t step) { return tmem_base + ((DB && (step & 1u)) ? 384u : 0u); };
+  auto t1_bar = [&](uint32_t step) { return &t1_full[DB ? (step & 1u) : 0u]; };
+  auto t1_parity = [&](uint32_t step) { return DB ? ((step >> 1) & 1u) : (step & 1u); };
 
   if (warp == TMA_WARP) {
     // ------------------------------------------------------------------ scheduler + TMA producer
@@ -227,8 +236,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
 
         mbar_wait(r_full, n & 1u, p.status, SITE_BWD_KV);
         mbar_wait(&full[s], ph, p.status, SITE_BWD_LOAD_FULL);
-        issue_t(tm_t1, dr0, du0 + s * (STAGE >> 4));
-        tc_commit_elect(t1_full);
+        issue_t(t1_addr(cnt), dr0, du0 + s * (STAGE >> 4));
+        tc_commit_elect(t1_bar(cnt));
         issue_t(tm_t2, dr0 + (TILE >> 4), du0 + s * (STAGE >> 4) + (TILE >> 4));
         tc_commit_elect(t2_full);
         if (steps == 1) tc_commit_elect(r_empty);
@@ -238,16 +247,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
           if (ns == NST) { ns = 0; nph ^= 1u; }
           const uint64_t dun1 = dun0 + cs * (STAGE >> 4), dun2 = dun1 + (TILE >> 4);
           const bool more = it + 1 < steps;
+          if (DB && more) {
+            // two T1 buffers: the other one was last read two steps ago (its P by the dV MMAs issued
+            // in that step, or by the compute warps before that step's ds_full)
+            mbar_wait(&full[ns], nph, p.status, SITE_BWD_LOAD_FULL);
+            issue_t(t1_addr(cnt + 1), dr0, du0 + ns * (STAGE >> 4));
+            tc_commit_elect(t1_bar(cnt + 1));
+          }
           if (!DQ) {
             mbar_wait(p_full, cnt & 1u, p.status, SITE_BWD_P_FULL);
             tc_fence_after();
-            issue_acc(tm_b, tm_t1, dun2, it > 0);  // dV += P^T dO
+            issue_acc(tm_b, t1_addr(cnt), dun2, it > 0);  // dV += P^T dO
           }
-          if (more) {
+          if (!DB && more) {
             mbar_wait(&full[ns], nph, p.status, SITE_BWD_LOAD_FULL);
             if (!DQ) {  // T1 of the next step may start as soon as P was consumed (in-order pipe)
-              issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
-              tc_commit_elect(t1_full);
+              issue_t(t1_addr(cnt + 1), dr0, du0 + ns * (STAGE >> 4));
+              tc_commit_elect(t1_bar(cnt + 1));
             }
           }
           mbar_wait(ds_full, cnt & 1u, p.status, SITE_BWD_DS_FULL);
@@ -255,9 +271,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
           issue_acc(tm_a, tm_t2, dun1, it > 0);  // dK += dS^T Q   /   dQ += dS K
           tc_commit_elect(&empty[cs]);
           if (more) {
-            if (DQ) {  // no MMA consumes P here: T1 is free once the compute warps have read it (ds_full)
-              issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
-              tc_commit_elect(t1_full);
+            if (DQ && !DB) {  // no MMA consumes P here: T1 is free once the compute warps have read it (ds_full)
+              issue_t(t1_addr(cnt + 1), dr0, du0 + ns * (STAGE >> 4));
+              tc_commit_elect(t1_bar(cnt + 1));
             }
             issue_t(tm_t2, dr0 + (TILE >> 4), du0 + ns * (STAGE >> 4) + (TILE >> 4));
             tc_commit_elect(t2_full);
@@ -313,7 +329,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         const bool diag = p.causal && (t == blk);
         const bool traced = warp == 0 && lane == 0;  // used by trace builds only
         if (traced) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 0x100 | steps);
-        mbar_wait(t1_full, cnt & 1u, p.status, SITE_BWD_S_FULL);
+        const uint32_t tm_t1 = t1_addr(cnt);
+        mbar_wait(t1_bar(cnt), t1_parity(cnt), p.status, SITE_BWD_S_FULL);
         if (traced) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 1);
         tc_fence_after();
         uint32_t pr[HC];  // P as fp32 bits
