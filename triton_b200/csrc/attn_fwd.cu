@@ -22,7 +22,9 @@
 // The kernel is persistent: one CTA per SM takes work items (256 query rows of one head) from an
 // atomic counter, head-major and heavy-first, so a head's K/V stay in L2, causal work balances, and
 // the epilogue of one item overlaps the loads and first MMAs of the next.
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_i = first 64 columns of S_i.
+// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_i = first 64 columns of S_i
+// at head dim 128, and columns [320,384) / [448,512) at head dim 64 (16-bit), where S_i of the next
+// block is then issued before P_i V of this one.
 #include <cmath>
 #include <cstdlib>
 
@@ -60,7 +62,7 @@ struct FwdCfg {
   static constexpr int KV_STAGES = (D == 128 && !FP8) ? 4 : 8;
   // tiles + barriers + TMEM slot + scheduler slots + alignment slack
   static constexpr int STG_BYTES = 32 * 128;  // epilogue staging of one softmax warp: 32 rows x 64 columns
-  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + 8 * STG_BYTES + (2 * KV_STAGES + 18) * 8 + 32 + 1024;
+  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + 8 * STG_BYTES + (2 * KV_STAGES + 22) * 8 + 32 + 1024;
 };
 
 // one Q tile or K / V block of 128 rows: boxes of 128 bytes x 128 rows.  `along_rows`: the 8-bit V,
@@ -120,7 +122,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   uint64_t* q_empty = o_full + 2;      // [1] every S MMA of the item has read the Q tiles
   uint64_t* sched_full = q_empty + 1;  // [2] an item id was published
   uint64_t* sched_empty = sched_full + 2;  // [2] all 9 readers have taken it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + 2);
+  uint64_t* s_free = sched_empty + 2;      // [2] (head dim 64) the softmax warps of tile i hold S_i(j) in registers
+  uint64_t* pv_done = s_free + 2;          // [2] (head dim 64) P_i(j) V_j is complete: O_i and the P buffer may be touched
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
   volatile int* sched_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -133,6 +137,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&p_full[2 * i], 128);
       mbar_init(&p_full[2 * i + 1], 128);
       mbar_init(&o_full[i], 1);
+      mbar_init(&s_free[i], 4);  // one arrival per softmax warp of the tile
+      mbar_init(&pv_done[i], 1);
       mbar_init(&sched_full[i], 1);
       mbar_init(&sched_empty[i], 9);  // MMA warp + one lane of each softmax warp
     }
@@ -157,6 +163,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const uint32_t tm_s[2] = {tmem_base, tmem_base + 128};
   const uint32_t tm_o[2] = {tmem_base + 256, tmem_base + 384};
+  // At head dim 64 the O accumulators leave 2 x 64 columns free, which hold P: with P out of the
+  // S buffer, S_i(j+1) is issued as soon as the softmax warps have S_i(j) in registers instead of
+  // after P_i(j) V_j, so the scores of the next block are ready when a tile's softmax comes back
+  // for them.  (At head dim 128 TMEM is full and P overwrites S.)
+  constexpr bool SEP_P = (D == 64) && !FP8;
+  auto tm_p = [&](int i) { return SEP_P ? tmem_base + (i ? 448u : 320u) : tm_s[i]; };
 
   if (warp == TMA_WARP) {
     // ------------------------------------------------------------------ scheduler + TMA producer
@@ -200,6 +212,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint64_t dv0 = smem_desc_sw128(smem_u32(skv), FP8 ? 0 : BLK * 128, 1024);  // LBO: next 64-column box
       uint32_t s = 0, ph = 0;        // ring position of the next unconsumed K / V block
       uint32_t pcnt[2] = {0, 0};     // blocks of tile i whose P has been consumed (parity of p_full)
+      [[maybe_unused]] uint32_t fcnt[2] = {0, 0};  // (head dim 64) blocks of tile i so far, across items (parity of s_free)
 
       auto issue_s = [&](int i, uint32_t stage) {  // S_i = Q_i K^T, D/16 MMAs
         const uint64_t dq = dq0 + i * (TILE >> 4), dk = dk0 + stage * (TILE >> 4);
@@ -229,11 +242,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if constexpr (FP8) {
 #pragma unroll
             for (int kk = 2 * h; kk < 2 * h + 2; ++kk)  // 32 keys per MMA: 8 TMEM columns of P, 32 B of the V rows
-              umma_ts_f8_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * 2, IDESC_O, (accum | kk) != 0);
+              umma_ts_f8_elect(tm_o[i], tm_p(i) + kk * 8, dv + kk * 2, IDESC_O, (accum | kk) != 0);
           } else {
 #pragma unroll
             for (int kk = 4 * h; kk < 4 * h + 4; ++kk)
-              umma_ts_f16_elect(tm_o[i], tm_s[i] + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
+              umma_ts_f16_elect(tm_o[i], tm_p(i) + kk * 8, dv + kk * ((16 * 128) >> 4), IDESC_O, (accum | kk) != 0);
           }
         }
       };
@@ -263,6 +276,41 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           advance();
           const uint32_t ks = s, kph = ph;  // K_{j+1} (if any)
           const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
+          if constexpr (SEP_P) {
+            // the next scores first: S_i(j+1) only needs the S buffer, which is free once the
+            // softmax warps have loaded S_i(j)
+            if (more0) {
+              mbar_wait(&s_free[0], fcnt[0]++ & 1u, p.status, SITE_FWD_S_EMPTY);
+              tc_fence_after();
+              mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+              issue_s(0, ks);
+            } else if (j < n0) {
+              ++fcnt[0];  // the tile's last block: its arrival is not waited for, the count goes on
+            }
+            if (more1) {
+              mbar_wait(&s_free[1], fcnt[1]++ & 1u, p.status, SITE_FWD_S_EMPTY);
+              tc_fence_after();
+              mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+              issue_s(1, ks);
+              tc_commit_elect(&kv_empty[ks]);
+              if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
+            } else {
+              ++fcnt[1];
+            }
+            if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
+            mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
+            if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x60);
+            if (j < n0) {
+              issue_pv(0, vs, j > 0, pcnt[0]++ & 1u);
+              tc_commit_elect(&pv_done[0]);
+              if (j == n0 - 1) tc_commit_elect(&o_full[0]);
+            }
+            issue_pv(1, vs, j > 0, pcnt[1]++ & 1u);
+            tc_commit_elect(&kv_empty[vs]);
+            tc_commit_elect(&pv_done[1]);
+            if (j == n1 - 1) tc_commit_elect(&o_full[1]);
+            if (more1) advance();
+          } else {
           if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
           mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
           if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x60);
@@ -283,6 +331,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_commit_elect(&kv_empty[ks]);
             if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
             advance();
+          }
           }
         }
       }
@@ -350,6 +399,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(max3(mx4[u], mx4[u + 4], mx4[u + 8]), mx4[u + 12]);
         const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        if constexpr (SEP_P) {
+          // S_i(j) is in registers: the S buffer may take S_i(j+1)
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&s_free[i]);
+        }
+        // (head dim 64) before O_i or the P buffer is touched, P_i(j-1) V must be complete; on an
+        // item's first block the epilogue's wait for the last P V of the previous item has seen to that
+        auto wait_pv = [&]() {
+          if (SEP_P && j > 0) {
+            mbar_wait(&pv_done[i], (scnt - 1u) & 1u, p.status, SITE_FWD_O_READY);
+            tc_fence_after();
+          }
+        };
         if (traced) B200_TRACE_EVENT(p.status, i, 2);
         // mx is finite: every row sees at least one valid column in every block it visits
         const float m_new = fmaxf(m_ref, mx * scale);
@@ -362,6 +425,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
           if (grow) { m_ref = m_new; l *= alpha; }
           if (j > 0) {
+            wait_pv();
 #pragma unroll 1
             for (int c = 0; c < D; c += 32) {
               uint32_t o[32];
@@ -398,7 +462,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                  __uint_as_float(r[c + 4 * k + 2]), __uint_as_float(r[c + 4 * k + 3]));
             tmem_st8(tm_s[i] + lane_addr + (c >> 2), wv);
           } else {
-            tmem_st16(tm_s[i] + lane_addr + (c >> 1), wv);
+            if (c == 0) wait_pv();  // as late as possible: the first 32 exponentials are done
+            tmem_st16(tm_p(i) + lane_addr + (c >> 1), wv);
           }
           if (c == 32 || c == 96) {  // a half of P is complete: its four P V MMAs may start
             tmem_st_wait();
