@@ -159,10 +159,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const uint32_t tm_t2 = tmem_base + 128, tm_a = tmem_base + 256, tm_b = tmem_base + 256 + D;
-  // At head dim 64 the accumulators leave 128 TMEM columns free: a second T1 buffer, so that the
-  // scores of step t+1 are computed while the compute warps still work on step t (P / dS overwrite
-  // T1 / T2 in place, so with one buffer T1(t+1) has to wait until P(t) has been consumed).
-  constexpr bool DB = (D == 64);
+  // At head dim 64, and in the dQ kernel (one accumulator) at either head dim, the accumulators
+  // leave 128 TMEM columns free: a second T1 buffer, so that the scores of step t+1 are computed
+  // while the compute warps still work on step t (P / dS overwrite T1 / T2 in place, so with one
+  // buffer T1(t+1) has to wait until P(t) has been consumed).
+  constexpr bool DB = (D == 64) || DQ;
   auto t1_addr = [&](uint32_t step) { return tmem_base + ((DB && (step & 1u)) ? 384u : 0u); };
   auto t1_bar = [&](uint32_t step) { return &t1_full[DB ? (step & 1u) : 0u]; };
   auto t1_parity = [&](uint32_t step) { return DB ? ((step >> 1) & 1u) : (step & 1u); };
