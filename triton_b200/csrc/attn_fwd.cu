@@ -440,14 +440,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (traced) B200_TRACE_EVENT(p.status, i, 3);
         const float neg_m = -m_ref;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+        [[maybe_unused]] uint64_t sum2[2] = {pk2(0.f, 0.f), pk2(0.f, 0.f)};
+        [[maybe_unused]] const uint64_t scale2 = pk2(scale, scale), neg_m2 = pk2(neg_m, neg_m);
 #pragma unroll
         for (int c = 0; c < BLK; c += 32) {
           uint32_t wv[16];
 #pragma unroll
           for (int k = 0; k < 16; ++k) {
-            const float p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));
-            sum4[k & 3] += p0 + p1;
+            float p0, p1;
+            if constexpr (SEP_P) {
+              // head dim 64 is bound by instruction issue: packed fp32 arithmetic for the scaling
+              // and the row sum (one issue slot per column pair)
+              float x0, x1;
+              upk2(fma2(pk2(__uint_as_float(r[c + 2 * k]), __uint_as_float(r[c + 2 * k + 1])), scale2, neg_m2), x0, x1);
+              p0 = ex2(x0);
+              p1 = ex2(x1);
+              sum2[k & 1] = add2(sum2[k & 1], pk2(p0, p1));
+            } else {
+              p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
+              p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));
+              sum4[k & 3] += p0 + p1;
+            }
             if constexpr (FP8) {  // keep the values; four are packed into one column below
               r[c + 2 * k] = __float_as_uint(p0);
               r[c + 2 * k + 1] = __float_as_uint(p1);
@@ -471,7 +484,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             mbar_arrive(&p_full[2 * i + (c >> 6)]);
           }
         }
-        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        if constexpr (SEP_P) {
+          float a0, a1, b0, b1;
+          upk2(sum2[0], a0, a1);
+          upk2(sum2[1], b0, b1);
+          l += (a0 + a1) + (b0 + b1);
+        } else {
+          l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        }
         if (traced) B200_TRACE_EVENT(p.status, i, 4);
       }
 
