@@ -343,10 +343,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
           // column statistics: one 16-byte broadcast load for four columns
           const float4 m4 = DQ ? make_float4(m_row, m_row, m_row, m_row) : *reinterpret_cast<const float4*>(sm + c4);
           const float mq[4] = {m4.x, m4.y, m4.z, m4.w};
+          // packed fp32 arithmetic (one issue slot per column pair) for the scaling
+          float xs[4];
+          upk2(fma2(pk2(__uint_as_float(pr[c4]), __uint_as_float(pr[c4 + 1])), pk2(scale, scale), pk2(-mq[0], -mq[1])), xs[0], xs[1]);
+          upk2(fma2(pk2(__uint_as_float(pr[c4 + 2]), __uint_as_float(pr[c4 + 3])), pk2(scale, scale), pk2(-mq[2], -mq[3])), xs[2], xs[3]);
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int c = c4 + u;
-            float pv = ex2(fmaf(__uint_as_float(pr[c]), scale, -mq[u]));
+            float pv = ex2(xs[u]);
             // dK/dV kernel: row = kv, column = q, keep q >= kv.   dQ kernel: row = q, column = kv, keep kv <= q.
             const int cc = half * HC + c;
             if (diag && (DQ ? (cc > r) : (cc < r))) pv = 0.f;
@@ -378,10 +382,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
 #pragma unroll
           for (int k4 = 0; k4 < 32; k4 += 4) {
             const float4 d4 = DQ ? make_float4(d_row, d_row, d_row, d_row) : *reinterpret_cast<const float4*>(sd + c + k4);
-            const float ds0 = __uint_as_float(pr[c + k4]) * (__uint_as_float(dp[k4]) - d4.x);
-            const float ds1 = __uint_as_float(pr[c + k4 + 1]) * (__uint_as_float(dp[k4 + 1]) - d4.y);
-            const float ds2 = __uint_as_float(pr[c + k4 + 2]) * (__uint_as_float(dp[k4 + 2]) - d4.z);
-            const float ds3 = __uint_as_float(pr[c + k4 + 3]) * (__uint_as_float(dp[k4 + 3]) - d4.w);
+            float ds0, ds1, ds2, ds3;  // dS = P (dP - delta), two columns per instruction
+            upk2(mul2(pk2(__uint_as_float(pr[c + k4]), __uint_as_float(pr[c + k4 + 1])),
+                      sub2(pk2(__uint_as_float(dp[k4]), __uint_as_float(dp[k4 + 1])), pk2(d4.x, d4.y))), ds0, ds1);
+            upk2(mul2(pk2(__uint_as_float(pr[c + k4 + 2]), __uint_as_float(pr[c + k4 + 3])),
+                      sub2(pk2(__uint_as_float(dp[k4 + 2]), __uint_as_float(dp[k4 + 3])), pk2(d4.z, d4.w))), ds2, ds3);
             dsw[((c + k4) >> 1)] = pack2<BF16>(ds0, ds1);
             dsw[((c + k4) >> 1) + 1] = pack2<BF16>(ds2, ds3);
           }
