@@ -10,6 +10,7 @@ Tensors are torch CUDA tensors (torch supplies device memory, streams and autogr
 plumbing); the arithmetic is done by the library's sm_100a kernels through the C ABI.
 """
 import ctypes
+import os
 
 import torch
 
@@ -23,8 +24,47 @@ if hasattr(torch, "float8_e5m2"):
 _ACT = {"": _lib.ACT_NONE, None: _lib.ACT_NONE, "leaky_relu": _lib.ACT_LEAKY_RELU, "softmax": _lib.ACT_SOFTMAX}
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t):
+    """The current stream of the tensor's device, as the handle the C ABI takes."""
+    if _raw_stream is not None:  # the call the reference's launcher uses too (driver.py:24-31); no Stream object is built
+        return _raw_stream(t.device.index)
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+class _on_device:
+    """`with torch.cuda.device(dev)` that costs nothing when dev is already current."""
+
+    __slots__ = ("ctx",)
+
+    def __init__(self, dev):
+        self.ctx = None if torch.cuda.current_device() == dev.index else torch.cuda.device(dev)
+
+    def __enter__(self):
+        if self.ctx is not None:
+            self.ctx.__enter__()
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        return False
+
+
+_plan_cache = {}  # (M, N, K, dtype, device, B200_GEMM_SPLITK) -> (splits, workspace bytes)
+
+
+def _matmul_plan(M, N, K, dt):
+    key = (M, N, K, dt, torch.cuda.current_device(), os.environ.get("B200_GEMM_SPLITK"))
+    hit = _plan_cache.get(key)
+    if hit is None:
+        splits, ws_bytes = ctypes.c_int(1), ctypes.c_size_t(0)
+        _lib.check(_lib.lib().b200_matmul_plan(M, N, K, dt, ctypes.byref(splits), ctypes.byref(ws_bytes)), "matmul_plan")
+        hit = _plan_cache[key] = (splits.value, ws_bytes.value)
+        if len(_plan_cache) > 4096:
+            _plan_cache.clear()
+    return hit
 
 
 def _require_cuda(*ts):
@@ -64,7 +104,7 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
     _, N = b.shape
     if out_dtype is None:
         out_dtype = torch.float16 if a.dtype == torch.float16 else torch.bfloat16
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         c = out if out is not None else torch.empty((M, N), device=dev, dtype=out_dtype)
         assert c.shape == (M, N) and c.dtype == out_dtype and c.stride(1) == 1 or N == 1
 
@@ -91,16 +131,13 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
                 raise AssertionError(f"bias shape {tuple(bias.shape)} is not [M, N], [M, 1] or [1, N]")
             bias_ptr, bias_sm, bias_sn = bias.data_ptr(), bias.stride(0), bias.stride(1)
         # skinny problems (few tiles, long K) are split along K; the fp32 partial tiles need scratch
-        splits, ws_bytes = ctypes.c_int(1), ctypes.c_size_t(0)
-        if activation != "softmax":  # the row softmax needs the whole K range in one tile
-            _lib.check(_lib.lib().b200_matmul_plan(M, N, K, _DT[a.dtype], ctypes.byref(splits), ctypes.byref(ws_bytes)),
-                       "matmul_plan")
-        ws = torch.empty(ws_bytes.value // 4, device=dev, dtype=torch.float32) if splits.value > 1 else None
+        splits, ws_bytes = (1, 0) if activation == "softmax" else _matmul_plan(M, N, K, _DT[a.dtype])  # the row softmax needs the whole K range in one tile
+        ws = torch.empty(ws_bytes // 4, device=dev, dtype=torch.float32) if splits > 1 else None
         code = _lib.lib().b200_matmul_bias(
             _stream(a), a.data_ptr(), b.data_ptr(), c.data_ptr(), M, N, K,
             a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
             _DT[a.dtype], _DT[out_dtype], _ACT[activation], pa, pb, bias_ptr, bias_mode, bias_sm, bias_sn,
-            splits.value, ws.data_ptr() if ws is not None else None)
+            splits, ws.data_ptr() if ws is not None else None)
         _lib.check(code, "matmul")
     return c
 
@@ -118,7 +155,7 @@ def matmul_chain(a, b, w, *, out_dtype=None):
     N, N2 = w.shape
     if out_dtype is None:
         out_dtype = a.dtype
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         c = torch.empty((M, N2), device=dev, dtype=out_dtype)
         code = _lib.lib().b200_matmul_chain(
             _stream(a), a.data_ptr(), b.data_ptr(), w.data_ptr(), c.data_ptr(), M, N, K, N2,
@@ -257,7 +294,7 @@ def attention_forward(q, k, v, causal, sm_scale):
         qp, kp, vp = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v))
         o, M = attention_forward(qp, kp, vp, causal, sm_scale)
         return o[..., :D].contiguous(), M
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         if fp8:
             # the reference's fp8 forward (06-fused-attention.py:609-615) is given V with the key
             # dimension contiguous; any other V is brought into that layout first
@@ -286,7 +323,7 @@ def attention_backward(q, k, v, o, M, do, causal, sm_scale):
     if D in (16, 32):  # as in attention_forward: zero-padded to the kernels' head dim 64
         qp, kp, vp, op, dop = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v, o, do))
         return tuple(g[..., :D].contiguous() for g in attention_backward(qp, kp, vp, op, M, dop, causal, sm_scale))
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)
