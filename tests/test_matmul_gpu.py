@@ -306,6 +306,17 @@ def test_host_matmul_pipeline_matches_device_matmul():
         torch.cuda.synchronize()
         want = triton_b200.matmul(a_h.to(DEV), b_h.to(DEV), activation="leaky_relu")
         np.testing.assert_allclose(f32(c_h), f32(want), rtol=1e-2, atol=1e-2)
+    # back-to-back calls without a synchronisation in between reuse the device buffers in stream
+    # order: every call has its own host operands and result
+    ins = [(torch.randn(M, K, generator=g).half().pin_memory(), torch.randn(K, N, generator=g).half().pin_memory())
+           for _ in range(5)]
+    outs = [torch.empty(M, N, dtype=torch.float16).pin_memory() for _ in range(5)]
+    for (ah, bh), ch in zip(ins, outs):
+        hm.run(ah, bh, ch)
+    torch.cuda.synchronize()
+    for (ah, bh), ch in zip(ins, outs):
+        want = triton_b200.matmul(ah.to(DEV), bh.to(DEV))
+        np.testing.assert_allclose(f32(ch), f32(want), rtol=1e-2, atol=1e-2)
     status_ok()
 
 
