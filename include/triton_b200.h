@@ -49,8 +49,21 @@ B200_API const char* b200_last_error(void);
 
 /* Device status word of the current device: 0 when every kernel since the last clear ran
  * to completion normally; otherwise the code of the first bounded wait that gave up
- * (site | parity << 8 | block << 16).  Synchronises the device.  `clear` != 0 resets it. */
+ * (site | parity << 8 | block << 16).  Synchronises the device.  `clear` != 0 resets it.
+ * Every wait inside the kernels has a time limit (250 ms); a kernel whose wait runs out records
+ * the code, finishes without faulting and leaves its outputs incomplete.  The code is mirrored
+ * into pinned host memory, and from then on every entry point that would launch work on that
+ * device returns B200_ERR_KERNEL without launching, until b200_status(&v, 1) has cleared it
+ * (no device synchronisation is involved in that check). */
 B200_API int b200_status(unsigned* value, int clear);
+
+/* Exercises the give-up path described above without any faulty input: launches one small
+ * kernel that allocates tensor memory and waits, for at most `limit_us` microseconds (1 ..
+ * 250000), on a barrier that nothing arrives on.  The kernel records its failure code
+ * (site 99), frees what it holds and exits normally; afterwards the device is in the state
+ * b200_status documents (compute entry points return B200_ERR_KERNEL until it is cleared).
+ * No counterpart in the reference, whose kernels wait without limits. */
+B200_API int b200_selftest_wait_timeout(b200_stream_t stream, unsigned limit_us);
 
 /* C[M,N] = act(A[M,K] @ B[K,N]) with fp32 accumulation.
  * Replaces matmul_kernel + its launch in python/tutorials/03-matrix-multiplication.py:241-348
@@ -62,7 +75,7 @@ B200_API int b200_status(unsigned* value, int clear);
  * A and B may have any strides; C must have stride_cn == 1.  The tensor-core path needs one unit
  * stride per operand, 16-byte aligned base addresses and non-unit strides that are multiples of
  * 16 bytes (what TMA can address); other layouts run on a plain CUDA-core kernel, correct but slow.
- * in_dtype: F16, BF16 or E4M3 (both operands); out_dtype: F16, BF16 or F32. */
+ * in_dtype: F16, BF16 or E4M3 (both operands); out_dtype: F16, BF16, F32 or E4M3 (see b200_matmul_bias). */
 B200_API int b200_matmul(b200_stream_t stream, const void* a, const void* b, void* c, int M, int N, int K,
                 int64_t stride_am, int64_t stride_ak, int64_t stride_bk, int64_t stride_bn,
                 int64_t stride_cm, int64_t stride_cn, int in_dtype, int out_dtype, int activation,
@@ -160,6 +173,18 @@ B200_API int b200_attention_fwd(b200_stream_t stream, const void* q, const void*
                                 int Z, int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
                                 const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal,
                                 int dtype);
+
+/* b200_attention_fwd that also returns the row maximum: row_max[Z,H,N] (fp32, contiguous, may be
+ * NULL) = max over the (unmasked) keys of q.k * sm_scale * log2(e), the base-2 counterpart of `m`.
+ * The reference's older forward kernel (python/test/unit/hopper/test_flashattention.py:36-131)
+ * stores its statistics as two tensors, the row maximum M and the row sum L of exp(score - M)
+ * (:128-131); they follow from the two outputs here as M = row_max * ln 2 and
+ * L = 2^(m - row_max). */
+B200_API int b200_attention_fwd_stats(b200_stream_t stream, const void* q, const void* k, const void* v, void* o,
+                                      float* m, float* row_max, int Z, int H, int N, int D,
+                                      const int64_t stride_q[4], const int64_t stride_k[4],
+                                      const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale,
+                                      int causal, int dtype);
 
 /* Flash-attention backward: dQ, dK, dV from Q, K, V, O, dO and the forward's statistics M.
  * Replaces _attn_bwd_preprocess, _attn_bwd and their launches in _attention.backward,

@@ -118,7 +118,20 @@ def add_bias(c, bias, out):
 # ----------------------------------------------------------------------------- matmul
 
 
-def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8, bias=None):
+def matmul_tile_origin(M, N, pid, BM=128, BN=256, GROUP_M=8):
+    """(row, column) of the first element of program `pid`'s tile: the grouped ordering of
+    python/tutorials/03-matrix-multiplication.py:265-273."""
+    num_pid_m, num_pid_n = -(-M // BM), -(-N // BN)
+    num_pid_in_group = GROUP_M * num_pid_n
+    group_id = pid // num_pid_in_group
+    first_pid_m = group_id * GROUP_M
+    group_size_m = min(num_pid_m - first_pid_m, GROUP_M)
+    pid_m = first_pid_m + ((pid % num_pid_in_group) % group_size_m)
+    pid_n = (pid % num_pid_in_group) // group_size_m
+    return pid_m * BM, pid_n * BN
+
+
+def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8, bias=None, pids=None):
     """C = A @ B, tile by tile.
 
     Follows matmul_kernel, python/tutorials/03-matrix-multiplication.py:241-316:
@@ -126,7 +139,8 @@ def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8, bi
     (:282-283), K loop with zero fill past K and an fp32 accumulator (:293-303),
     optional leaky_relu (:306-307, 320-322), one rounding to the output type (:308),
     store masked to M x N (:312-316).  `a`, `b` are fp32 arrays holding values that are
-    exact in the storage type.
+    exact in the storage type.  `pids`: run only these programs of the launch grid (the other
+    tiles of the result stay zero; matmul_tile_origin says where a program's tile lies).
     """
     a = np.asarray(a, dtype=np.float32)
     b = np.asarray(b, dtype=np.float32)
@@ -136,7 +150,7 @@ def matmul(a, b, activation="", out="fp16", BM=128, BN=256, BK=64, GROUP_M=8, bi
     c = np.zeros((M, N), dtype=np.float32)
     num_pid_m, num_pid_n = -(-M // BM), -(-N // BN)
     num_pid_in_group = GROUP_M * num_pid_n
-    for pid in range(num_pid_m * num_pid_n):
+    for pid in (range(num_pid_m * num_pid_n) if pids is None else pids):
         group_id = pid // num_pid_in_group
         first_pid_m = group_id * GROUP_M
         group_size_m = min(num_pid_m - first_pid_m, GROUP_M)
@@ -194,7 +208,7 @@ def matmul_chain(a, b, w, out="fp16", storage="fp16", BM=128, BK=64):
     return c
 
 
-def matmul_fp8(a_bits, b_bits, scale_a=None, scale_b=None, out="bf16", BM=128, BN=256, BK=128):
+def matmul_fp8(a_bits, b_bits, scale_a=None, scale_b=None, out="bf16", BM=128, BN=256, BK=128, pids=None):
     """e4m3 x e4m3 -> fp32 accumulator -> (acc * scale_a * scale_b) -> `out`.
 
     The accumulator part follows the fp8 matmul_kernel of
@@ -202,7 +216,8 @@ def matmul_fp8(a_bits, b_bits, scale_a=None, scale_b=None, out="bf16", BM=128, B
     unmasked loads so M, N, K must divide the tile, fp32 store); the interpreter widens
     fp8 operands before the product (interpreter.py:545-548), as done here.  The scale
     epilogue has no reference kernel; it is one fp32 multiply by (scale_a*scale_b) and
-    one rounding.  out="fp32" with no scales returns the accumulator itself.
+    one rounding.  out="fp32" with no scales returns the accumulator itself.  `pids`: run only
+    these programs (tile of program pid: rows (pid % (M/BM)) * BM, columns (pid // (M/BM)) * BN).
     """
     a = decode_e4m3(a_bits)
     b = decode_e4m3(b_bits)
@@ -212,7 +227,7 @@ def matmul_fp8(a_bits, b_bits, scale_a=None, scale_b=None, out="bf16", BM=128, B
     assert M % BM == 0 and N % BN == 0 and K % BK == 0
     c = np.zeros((M, N), dtype=np.float32)
     num_pid_m = M // BM
-    for pid in range(num_pid_m * (N // BN)):
+    for pid in (range(num_pid_m * (N // BN)) if pids is None else pids):
         pid_m, pid_n = pid % num_pid_m, pid // num_pid_m
         acc = np.zeros((BM, BN), dtype=np.float32)
         for k0 in range(0, K, BK):

@@ -59,7 +59,7 @@ ATTN_CASES = {
                        old_style=True),
     "full_d64": dict(Z=1, H=2, N=256, D=64, causal=False, sm_scale=0.5, dtype="fp16", bwd=False, seed=21),
     "causal_d128": dict(Z=1, H=1, N=512, D=128, causal=True, sm_scale=128 ** -0.5, dtype="fp16", bwd=True,
-                        seed=22),
+                        seed=22, old_style=True),
     "full_d128": dict(Z=1, H=1, N=384, D=128, causal=False, sm_scale=128 ** -0.5, dtype="fp16", bwd=False,
                       seed=23),
     # bf16 has no interpreter fixture (its dot is invalid for bf16 tiles); the numpy oracle covers it

@@ -215,6 +215,11 @@ def gen_attn_old(ref_root, out):
         q.requires_grad_(True), k.requires_grad_(True), v.requires_grad_(True)
         t0 = time.time()
         o = attention(q, k, v, c["sm_scale"])
+        # the wrapper saves (q, k, v, o, L, m) for its backward (test_flashattention.py:323): the two
+        # statistics tensors of this kernel variant, row sum L and row maximum M, [Z*H, N] fp32
+        saved = o.grad_fn.saved_tensors
+        out[f"attn_old.{name}.l"] = saved[4].detach().numpy().copy()
+        out[f"attn_old.{name}.m"] = saved[5].detach().numpy().copy()
         o.backward(do)
         print(f"attn-old {name}: {time.time()-t0:.2f}s")
         out[f"attn_old.{name}.o"] = o.detach().numpy()

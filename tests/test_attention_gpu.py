@@ -59,6 +59,31 @@ def test_attention_parity_with_oracle(golden, name):
                                            atol=1e-2, err_msg="golden " + key)
 
 
+@pytest.mark.parametrize("name", [n for n, c in cases.ATTN_CASES.items() if c.get("old_style")])
+def test_old_style_attention_against_its_interpreter_fixture(golden, name):
+    """The reference's older flash attention, `attention(q, k, v, sm_scale)` (always causal;
+    python/test/unit/hopper/test_flashattention.py:294-358): output and the three gradients against the
+    fixture its own kernels produced under the interpreter, at that test's tolerance (atol 1e-2, :399-403),
+    and the two statistics tensors it keeps - row sum L and row maximum M (:128-131)."""
+    c = cases.ATTN_CASES[name]
+    q, k, v, do = cases.attn_inputs(c)
+    qd, kd, vd = (t.to(DEV).requires_grad_(True) for t in (q, k, v))
+    o = triton_b200.attention_old(qd, kd, vd, c["sm_scale"])
+    o.backward(do.to(DEV))
+    status_ok()
+    np.testing.assert_allclose(f32(o), golden[f"attn_old.{name}.o"].astype(np.float32), atol=1e-2, rtol=0)
+    for got, key in ((qd.grad, "dq"), (kd.grad, "dk"), (vd.grad, "dv")):
+        np.testing.assert_allclose(f32(got), golden[f"attn_old.{name}.{key}"].astype(np.float32), atol=1e-2, rtol=0,
+                                   err_msg=key)
+    o2, L, M = triton_b200.attention_old_forward(qd.detach(), kd.detach(), vd.detach(), c["sm_scale"])
+    assert torch.equal(o2, o.detach()) and L.shape == (c["Z"] * c["H"], c["N"]) and M.shape == L.shape
+    np.testing.assert_allclose(f32(M), golden[f"attn_old.{name}.m"], rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(f32(L), golden[f"attn_old.{name}.l"], rtol=1e-3, atol=1e-4)
+    with pytest.raises(AssertionError):
+        big = torch.zeros(1, 1, 128, 256, dtype=torch.float16, device=DEV)
+        triton_b200.attention_old(big, big, big, 0.5)  # the older wrapper's head dims end at 128 (:303)
+
+
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("D", [64, 128])
 @pytest.mark.parametrize("N", [128, 200, 384, 1000])
@@ -90,10 +115,12 @@ def test_forward_ragged_lengths(dtype, D, N, causal):
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("where", ["first_half", "second_half", "growing", "one_row"])
 def test_forward_scores_far_above_the_first_block(dtype, D, causal, where):
-    """The 16-bit forward takes the row maximum on a row's first block only and moves the reference
-    point of a row when a later half block's probabilities sum too high; these inputs make that
-    happen in the first half of a block, in the second half (after the P V MMAs on the first half
-    were issued), in every block, and for a single row of a warp."""
+    """The 16-bit forward rescales its accumulator lazily: the running maximum of a row is followed
+    exactly, but O and l are only multiplied through when it has grown by more than 2^8 since the
+    last rescale.  These inputs make scores jump far above everything seen before - in the first
+    half of a block, in the second half (after the P V MMAs on the first half were issued), in
+    every block, and for a single row of a warp - so both the rescale and the no-rescale branch
+    run with large factors."""
     N = 768
     c = dict(Z=1, H=2, N=N, D=D, dtype=dtype, seed=7 * D + len(where))
     q, k, v, _ = cases.attn_inputs(c)
@@ -332,6 +359,39 @@ def test_ops_replay_from_a_cuda_graph():
     # the older six-argument signature
     o6 = triton_b200.attention(q, k, v, True, 0.125, True)
     assert torch.equal(o6, eager[0])
+
+
+def test_graph_replay_beside_eager_launches_on_another_stream():
+    """A captured launch keeps the work counter it was captured with.  Eager launches on another
+    stream walk through the whole ring of eager counters several times while the graph is replayed:
+    every replay and every eager result must stay bit-identical (captured launches draw their
+    counters from a pool that eager launches never use)."""
+    Z, H, N, D = 2, 4, 1024, 64
+    g = torch.Generator(device=DEV).manual_seed(8)
+    q, k, v, do = ((torch.randn(Z, H, N, D, generator=g, device=DEV) * 0.5).half() for _ in range(4))
+    q2, k2, v2 = ((torch.randn(1, 8, 512, 128, generator=g, device=DEV) * 0.5).half() for _ in range(3))
+    o_ref, M_ref = triton_b200.attention_forward(q, k, v, True, 0.125)
+    grads_ref = triton_b200.attention_backward(q, k, v, o_ref, M_ref, do, True, 0.125)
+    o2_ref, _ = triton_b200.attention_forward(q2, k2, v2, False, 0.09)
+    torch.cuda.synchronize()
+    cap, eager = torch.cuda.Stream(), torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=cap):
+        o_g, M_g = triton_b200.attention_forward(q, k, v, True, 0.125)
+        grads_g = triton_b200.attention_backward(q, k, v, o_g, M_g, do, True, 0.125)
+    bad = 0
+    for rnd in range(6):
+        with torch.cuda.stream(eager):
+            outs = [triton_b200.attention_forward(q2, k2, v2, False, 0.09)[0] for _ in range(120)]  # 720 in all: the ring has 256 slots
+        with torch.cuda.stream(cap):
+            for _ in range(10):
+                o_g.zero_()
+                graph.replay()
+        torch.cuda.synchronize()
+        bad += sum(0 if torch.equal(o, o2_ref) else 1 for o in outs)
+        bad += 0 if torch.equal(o_g, o_ref) and all(torch.equal(x, y) for x, y in zip(grads_g, grads_ref)) else 1
+    assert bad == 0
+    status_ok()
 
 
 def test_two_streams_and_two_host_threads():

@@ -26,6 +26,23 @@ def test_matmul_asserts_match_reference_wrapper():
         triton_b200.matmul(a, b.t(), activation="gelu")
 
 
+def test_out_tensor_is_checked_for_every_n():
+    """A wrong-shape or wrong-type `out=` must be refused also when N == 1 (where a column
+    stride other than 1 is allowed): the kernel would write M rows through it."""
+    from triton_b200.ops import _check_out
+    cpu = torch.device("cpu")
+    _check_out(torch.zeros(5, 1, dtype=torch.float16), 5, 1, torch.float16, cpu)
+    _check_out(torch.zeros(5, 2, dtype=torch.float16)[:, :1], 5, 1, torch.float16, cpu)  # N == 1: any column stride
+    with pytest.raises(AssertionError):
+        _check_out(torch.zeros(3, 1, dtype=torch.float16), 5, 1, torch.float16, cpu)  # too few rows
+    with pytest.raises(AssertionError):
+        _check_out(torch.zeros(5, 1, dtype=torch.float32), 5, 1, torch.float16, cpu)  # wrong type
+    with pytest.raises(AssertionError):
+        _check_out(torch.zeros(5, 8, dtype=torch.float16)[:, ::2], 5, 4, torch.float16, cpu)  # strided columns
+    with pytest.raises(AssertionError):
+        _check_out(torch.zeros(5, 4, dtype=torch.float16, device="meta"), 5, 4, torch.float16, cpu)  # other device
+
+
 def test_attention_asserts_match_reference_wrapper():
     q = torch.zeros(1, 2, 128, 64, dtype=torch.float16)
     k = torch.zeros(1, 2, 128, 32, dtype=torch.float16)

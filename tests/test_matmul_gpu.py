@@ -292,6 +292,42 @@ def test_full_size_fp8_properties():
     assert np.linalg.norm(g - want) / np.linalg.norm(want) < 2e-2
 
 
+def test_full_size_configs_against_the_oracle_on_sampled_programs():
+    """Configs 2 and 3 at full size against the ORACLE: the reference launches 64 x 32 programs of
+    128 x 256 (python/tutorials/03-matrix-multiplication.py:169-170) over an 8192^3 problem; the
+    oracle runs a handful of them (first, last, both edges of a rasterisation group, two interior)
+    over the full K range and those tiles of the CUDA result must agree - rtol = atol = 1e-2
+    for fp16, relative Frobenius error <= 2e-2 per tile for e4m3 with scales."""
+    BM, BN = 128, 256
+    n = 8192
+    pids = [0, 7, 8 * 32 - 1, 8 * 32, 1000, 1337, 64 * 32 - 1]
+    a, b = _full_size_inputs(torch.float16)
+    ah, bh = a.half(), b.half()
+    got = triton_b200.matmul(ah.to(DEV), bh.to(DEV))
+    status_ok()
+    want = R.matmul(ah.float().numpy(), bh.float().numpy(), pids=pids)
+    seen = set()
+    for pid in pids:
+        m0, n0 = R.matmul_tile_origin(n, n, pid)
+        seen.add((m0, n0))
+        np.testing.assert_allclose(got[m0:m0 + BM, n0:n0 + BN].float().cpu().numpy(), want[m0:m0 + BM, n0:n0 + BN],
+                                   rtol=1e-2, atol=1e-2, err_msg=f"program {pid}")
+    assert len(seen) == len(pids) and (0, 0) in seen and (n - BM, n - BN) in seen
+    del got
+    # config 3: e4m3 with per-tensor scales, bf16 output; the fp8 kernel's programs run column-major
+    a8, sa = cases.quantize_e4m3(a * n ** 0.5)
+    b8, sb = cases.quantize_e4m3(b * n ** 0.5)
+    got8 = triton_b200.matmul(a8.to(DEV), b8.to(DEV), scale_a=sa, scale_b=sb)
+    status_ok()
+    pids8 = [0, 63, 64, 1000, 64 * 32 - 1]
+    want8 = R.matmul_fp8(a8.view(torch.uint8).numpy(), b8.view(torch.uint8).numpy(), float(sa), float(sb), pids=pids8)
+    for pid in pids8:
+        m0, n0 = (pid % 64) * BM, (pid // 64) * BN
+        g, w = got8[m0:m0 + BM, n0:n0 + BN].float().cpu().numpy(), want8[m0:m0 + BM, n0:n0 + BN]
+        assert np.linalg.norm(g - w) / np.linalg.norm(w) < 2e-2, f"program {pid}"
+        np.testing.assert_allclose(g, w, rtol=2e-2, atol=2e-2, err_msg=f"program {pid}")
+
+
 def test_host_matmul_pipeline_matches_device_matmul():
     """HostMatmul (pinned host operands, row blocks pipelined over two copy streams) gives the
     device-resident matmul's result, also for a row count that the blocks do not divide."""

@@ -90,9 +90,9 @@ def test_attention_bwd_matches_interpreter(golden, name):
         np.testing.assert_allclose(a_, b_, atol=1e-2, rtol=1e-2)
 
 
-def test_attention_old_style_second_opinion(golden):
+@pytest.mark.parametrize("name", [n for n, c in cases.ATTN_CASES.items() if c.get("old_style")])
+def test_attention_old_style_second_opinion(golden, name):
     # python/test/unit/hopper/test_flashattention.py:361-403 (atol 1e-2)
-    name = "causal_d64"
     c = cases.ATTN_CASES[name]
     q, k, v, do = cases.attn_inputs(c)
     o, M = R.attention_fwd(f32(q), f32(k), f32(v), True, c["sm_scale"], "fp16")
@@ -100,6 +100,13 @@ def test_attention_old_style_second_opinion(golden):
     dq, dk, dv = R.attention_bwd(f32(q), f32(k), f32(v), o, f32(do), M, c["sm_scale"], "fp16")
     for got, key in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
         np.testing.assert_allclose(got, golden[f"attn_old.{name}.{key}"].astype(np.float32), atol=1e-2, rtol=0)
+    # the older kernel's two statistics tensors (row sum L, row maximum M, natural base, :128-131)
+    # against the newer kernel's one (base-2 log-sum-exp): lse2 = (M + ln L) / ln 2
+    L, m = golden[f"attn_old.{name}.l"], golden[f"attn_old.{name}.m"]
+    np.testing.assert_allclose((m + np.log(L)) / np.log(2.0), M.reshape(L.shape), rtol=1e-5, atol=1e-4)
+    s = np.einsum("zhnd,zhmd->zhnm", f32(q), f32(k)) * c["sm_scale"]
+    s = np.where(np.tril(np.ones(s.shape[-2:], dtype=bool)), s, -np.inf)
+    np.testing.assert_allclose(m, s.max(-1).reshape(m.shape), rtol=1e-5, atol=1e-5)
 
 
 def _torch_reference(q, k, v, do, causal, sm_scale):

@@ -11,6 +11,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libtriton_b200.so")
 
 F16, BF16, E4M3, F32, E5M2 = 0, 1, 2, 3, 4
+ERR_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_KERNEL = 1, 2, 3, 4, 5
 ACT_NONE, ACT_LEAKY_RELU, ACT_SOFTMAX = 0, 1, 2
 BIAS_NONE, BIAS_MATRIX, BIAS_ROWS, BIAS_COLS = 0, 1, 2, 3
 
@@ -22,6 +23,7 @@ SIGNATURES = {
     "b200_version": [],
     "b200_last_error": [],
     "b200_status": [ctypes.POINTER(ctypes.c_uint), _i],
+    "b200_selftest_wait_timeout": [_p, ctypes.c_uint],
     "b200_matmul": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p],
     "b200_matmul_plan": [_i, _i, _i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_size_t)],
     "b200_matmul_splitk": [_p, _p, _p, _p, _i, _i, _i, _i64, _i64, _i64, _i64, _i64, _i64, _i, _i, _i, _p, _p, _i, _p],
@@ -33,6 +35,7 @@ SIGNATURES = {
     "b200_grouped_matmul_prepare": [_p, _i, _p, _p, _p, _p, _p, _i, _i, _p, ctypes.POINTER(ctypes.c_int)],
     "b200_grouped_matmul_run": [_p, _p, _i, _i, _i],
     "b200_attention_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
+    "b200_attention_fwd_stats": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
     "b200_attention_bwd": [_p] + [_p] * 10 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
     "b200_attention_bwd_noalloc": [_p] + [_p] * 9 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
     "b200_attention_bwd_noalloc_capacity": [],

@@ -46,7 +46,7 @@ struct BwdParams {
   float scale_log2;  // sm_scale * log2(e)
   float sm_scale;
   int total_items;     // (N / 128) * Z * H
-  int* sched_counter;  // work counter of this launch (zeroed before the launch)
+  int* sched_counter;  // work counter of this launch: zero at launch, put back to zero by the last CTA
   int out_tma;         // gradients are written through shared-memory staging and TMA stores
   unsigned* status;
 };
@@ -178,6 +178,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
         mbar_wait(&sched_empty[slot], sph ^ 1u, p.status, SITE_BWD_SCHED);
         sched_item[slot] = w;
         mbar_arrive(&sched_full[slot]);
+        // every CTA draws exactly one ticket past the end: the last of them puts the zero back for the
+        // next launch that is handed this counter
+        if (w == p.total_items + (int)gridDim.x - 1) atomicExch(p.sched_counter, 0);
         if (w >= p.total_items) break;
         const BwdItem<DQ> it(p, w);
         mbar_wait(r_empty, (n & 1u) ^ 1u, p.status, SITE_BWD_KV);  // the previous item no longer reads R1, R2
@@ -532,14 +535,9 @@ template <int D, bool BF16, bool DQ>
 int launch_bwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& r1, const CUtensorMap& r2,
                  const CUtensorMap& u1, const CUtensorMap& u2, const CUtensorMap& oa, const CUtensorMap& ob,
                  const BwdParams& p) {
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];
   constexpr size_t smem = BwdCfg<D>::SMEM;
-  if (!attr_done[ctx->device]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(attn_bwd_kernel<D, BF16, DQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(attn bwd): %s", cudaGetErrorString(e));
-    attr_done[ctx->device] = true;
-  }
+  if (int rc = ensure_dynamic_smem(attn_bwd_kernel<D, BF16, DQ>, smem, ctx->device, attr_done, "attn bwd")) return rc;
   BwdParams q = p;
   q.total_items = (p.N / BLK) * p.Z * p.H;
   q.sched_counter = next_sched_counter(ctx, stream);

@@ -28,6 +28,7 @@
 #include <cmath>
 #include <cstdlib>
 
+#define B200_INLINE_WAIT_SLOW  // this kernel re-divides registers between its warpgroups
 #include "common.cuh"
 #include "host.h"
 
@@ -36,19 +37,20 @@ namespace tb {
 namespace {
 
 constexpr int BLK = 128;           // rows of a Q tile and of a K/V block
-constexpr int FWD_THREADS = 320;   // 8 softmax warps + MMA warp + TMA warp
+constexpr int FWD_THREADS = 512;   // 8 softmax warps, MMA warp, TMA warp, 6 warps that only lend their registers
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdParams {
   void* o;
   float* m;  // [Z*H, N] base-2 log-sum-exp of the scaled scores
+  float* row_max;  // optional [Z*H, N]: base-2 row maximum of the scaled scores (the old-style kernels' M / ln 2)
   long long o_sz, o_sh, o_sn;  // element strides of O
   int Z, H, N;
   int causal;
   float scale_log2;  // sm_scale * log2(e)
   int num_qb;        // 256-row query blocks per head
   int total_items;   // num_qb * Z * H
-  int* sched_counter;  // work counter of this launch (zeroed before the launch)
+  int* sched_counter;  // work counter of this launch: zero at launch, put back to zero by the last CTA
   int o_tma;           // O is written through shared-memory staging and TMA stores
   unsigned* status;
 };
@@ -170,7 +172,33 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr bool SEP_P = (D == 64) && !FP8;
   auto tm_p = [&](int i) { return SEP_P ? tmem_base + (i ? 448u : 320u) : tm_s[i]; };
 
-  if (warp == TMA_WARP) {
+  // Register budget: 512 threads start with 128 registers each.  A softmax thread holds a whole
+  // 128-column score row (and its packed probabilities) and needs about 200; the MMA and TMA
+  // warps need few, warps 10-15 none: they give theirs back and the softmax warpgroups take them.
+  // Per scheduler (one warp of every warpgroup): 208 + 208 + 72 + 24 = 512 registers per lane.
+  // Every role ends with its own copy of the teardown and returns: no code is shared after the
+  // register budgets have diverged (values live across a join would have to sit in registers that
+  // every budget has).
+  auto teardown = [&](bool owner) {
+    // after a recorded failure give copies in flight time to land before the CTA exits
+    if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+    tc_fence_before();
+    __syncthreads();
+    if (owner) {
+      tc_fence_after();
+      tmem_dealloc(tmem_base, 512);
+    }
+  };
+  if (warp >= 12) {
+    reg_dec<24>();  // nothing else: these warps only take part in the barriers at both ends of the kernel
+    teardown(false);
+    return;
+  } else if (warp >= 10) {
+    reg_dec<72>();
+    teardown(false);
+    return;
+  } else if (warp == TMA_WARP) {
+    reg_dec<72>();
     // ------------------------------------------------------------------ scheduler + TMA producer
     if (lane == 0) {
       uint32_t s = 0, ph = 0;  // K/V ring position, runs on across items
@@ -180,6 +208,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_wait(&sched_empty[slot], sph ^ 1u, p.status, SITE_FWD_SCHED);
         sched_item[slot] = w;
         mbar_arrive(&sched_full[slot]);
+        // every CTA draws exactly one ticket past the end: the last of them puts the zero back for the
+        // next launch that is handed this counter
+        if (w == p.total_items + (int)gridDim.x - 1) atomicExch(p.sched_counter, 0);
         if (w >= p.total_items) break;
         const Item it = decode_item(p, w);
         mbar_wait(q_empty, (n & 1u) ^ 1u, p.status, SITE_FWD_Q);  // previous item's S MMAs are done with Q
@@ -198,7 +229,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     __syncwarp();
+    teardown(false);
+    return;
   } else if (warp == MMA_WARP) {
+    reg_dec<72>();
     // ------------------------------------------------------------------ MMA issuer
     // The warp stays converged and an elected lane issues, for both tiles.  (Two issuing threads,
     // one per tile, were measured 20 % slower: MMAs of different threads interleave in the pipe
@@ -337,7 +371,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     __syncwarp();
+    teardown(true);
+    return;
   } else {
+    reg_inc<208>();
     // ------------------------------------------------------------------ softmax + epilogue
     // 4 warps per tile, one thread per query row.
     const int i = warp >> 2;                 // tile
@@ -364,6 +401,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int row = qb * 256 + i * BLK + row_in_tile;  // query index
       const int nb = i ? it.n1 : it.n0;
       float m_ref = -INFINITY, l = 0.f;
+      float m_true = -INFINITY;  // the exact running maximum (m_ref lags it by up to the rescale threshold)
       const bool traced = quarter == 0 && lane == 0;  // used by trace builds only
       if (traced) B200_TRACE_EVENT(p.status, i, 0x100 | nb);
 
@@ -416,6 +454,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (traced) B200_TRACE_EVENT(p.status, i, 2);
         // mx is finite: every row sees at least one valid column in every block it visits
         const float m_new = fmaxf(m_ref, mx * scale);
+        m_true = fmaxf(m_true, mx * scale);
         // lazy rescale of the accumulator (the ld/st below are warp collectives, so the warp
         // rescales if any of its rows has to)
         // true on the first block (m_ref = -inf).  The 8-bit forward follows the exact running maximum,
@@ -599,30 +638,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
       }
       if (valid) p.m[(long long)it.zh * p.N + row] = m_ref + log2f(l);
+      if (valid && p.row_max) p.row_max[(long long)it.zh * p.N + row] = m_true;
       if (traced) B200_TRACE_EVENT(p.status, i, 9);
     }
     if (p.o_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
-  }
-
-  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
-  tc_fence_before();
-  __syncthreads();
-  if (warp == MMA_WARP) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    teardown(false);
   }
 }
 
 template <int D, bool BF16, bool FP8 = false>
 int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, const CUtensorMap& tk,
                  const CUtensorMap& tv, const CUtensorMap& to, const FwdParams& p) {
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];
   constexpr size_t smem = FwdCfg<D, FP8>::SMEM;
-  if (!attr_done[ctx->device]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<D, BF16, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(attn fwd): %s", cudaGetErrorString(e));
-    attr_done[ctx->device] = true;
-  }
+  if (int rc = ensure_dynamic_smem(attn_fwd_kernel<D, BF16, FP8>, smem, ctx->device, attr_done, "attn fwd")) return rc;
   const int grid = p.total_items < ctx->sm_count ? p.total_items : ctx->sm_count;
   attn_fwd_kernel<D, BF16, FP8><<<grid, FWD_THREADS, smem, stream>>>(tq, tk, tv, to, p);
   cudaError_t e = cudaGetLastError();
@@ -648,7 +677,7 @@ bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H,
 }
 
 int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,
-                    float* m, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
+                    float* m, float* row_max, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
                     const int64_t* so, float sm_scale, int causal, int dtype) {
   if (dtype == B200_E5M2) {
     // 8-bit forward: rows of 128 bytes; V is addressed as [D rows][N keys] (keys contiguous)
@@ -663,7 +692,7 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
     FwdParams p8{};
     p8.o_tma = encode_rows_map(&to8, dtype, o, Z, H, N, D, so[0], so[1], so[2], 128, 32, true) ? 1 : 0;
     if (!p8.o_tma) to8 = tq8;
-    p8.o = o; p8.m = m;
+    p8.o = o; p8.m = m; p8.row_max = row_max;
     p8.o_sz = so[0]; p8.o_sh = so[1]; p8.o_sn = so[2];
     p8.Z = Z; p8.H = H; p8.N = N; p8.causal = causal;
     p8.scale_log2 = sm_scale * 1.44269504f;
@@ -683,7 +712,7 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
   // O through TMA stores (boxes of 32 rows x 64 columns) when its layout allows, else direct stores
   p.o_tma = encode_qkv_map(&to, dtype, o, Z, H, N, D, so[0], so[1], so[2], 32) ? 1 : 0;
   if (!p.o_tma) to = tq;
-  p.o = o; p.m = m;
+  p.o = o; p.m = m; p.row_max = row_max;
   p.o_sz = so[0]; p.o_sh = so[1]; p.o_sn = so[2];
   p.Z = Z; p.H = H; p.N = N; p.causal = causal;
   p.scale_log2 = sm_scale * 1.44269504f;  // the reference's constant (06-fused-attention.py:161)

@@ -5,25 +5,39 @@
 #include <cstring>
 #include <mutex>
 
+#include "common.cuh"
 #include "host.h"
 
 namespace tb {
 
 // Status word read by b200_status(); kernels receive its device address as a parameter.
+// Word 0: the status; words 2-3: device-visible address of this device's word in the pinned host
+// mirror below (0 when the page could not be registered).
 #ifdef B200_TRACE
-__device__ unsigned g_status_word[4 + 2 * tb::kTraceRegions * tb::kTraceEvents];  // status word + trace buffer
+__device__ __align__(16) unsigned g_status_word[4 + 2 * tb::kTraceRegions * tb::kTraceEvents];  // + trace buffer
 #else
-__device__ unsigned g_status_word[4];
+__device__ __align__(16) unsigned g_status_word[4];
 #endif
-// Work counters of the persistent attention kernels: each launch takes the next word of this ring
-// and zeroes it on its stream, so launches in flight on different streams do not share one (more
-// than 256 attention launches in flight at once would).
-__device__ int g_sched_ring[256];
+// Work counters of the persistent attention kernels.  A counter is zero between launches: the CTA
+// that takes the last ticket of a launch puts the zero back, so no reset precedes a launch.
+// Eager launches take the next word of a ring, so launches in flight on different streams do not
+// share one (more than kSchedRing attention launches in flight at once on one device would).
+// Launches captured into a CUDA graph keep their counter for as long as the graph may be
+// replayed, so they take words of a pool that is never recycled: a replay can then never meet
+// an eager launch, or another graph, on its counter.
+constexpr unsigned kSchedRing = 256, kSchedGraphPool = 4096;
+__device__ int g_sched_ring[kSchedRing + kSchedGraphPool];
 
 namespace {
 thread_local char g_err[512] = "";
+thread_local int g_err_code = B200_OK;  // code of the last fail() on this thread
 std::mutex g_mu;
 DeviceCtx g_ctx[64];
+// One word per device (64 bytes apart) in a page of the library's own static memory, pinned and
+// mapped on first use (cudaHostRegister: nothing is allocated).  A kernel whose bounded wait runs
+// out stores its failure code here as well as in the device status word.
+alignas(4096) unsigned g_host_status[1024];
+bool g_host_status_registered = false, g_host_status_tried = false;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -36,6 +50,7 @@ int fail(int code, const char* fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
+  g_err_code = code;
   return code;
 }
 
@@ -86,35 +101,74 @@ DeviceCtx* current_ctx() {
     return nullptr;
   }
   c.status = static_cast<unsigned*>(st);
+  // host mirror of the status word (optional: without it a failure is still seen by b200_status)
+  c.host_status = nullptr;
+  if (!g_host_status_tried) {
+    g_host_status_tried = true;
+    g_host_status_registered =
+        cudaHostRegister(g_host_status, sizeof(g_host_status), cudaHostRegisterPortable | cudaHostRegisterMapped) == cudaSuccess;
+    if (!g_host_status_registered) cudaGetLastError();
+  }
+  if (g_host_status_registered) {
+    void* dptr = nullptr;
+    unsigned* hword = &g_host_status[dev * 16];
+    if (cudaHostGetDevicePointer(&dptr, hword, 0) == cudaSuccess && dptr) {
+      *hword = 0;
+      unsigned long long addr = reinterpret_cast<unsigned long long>(dptr);
+      if (cudaMemcpy(c.status + 2, &addr, sizeof(addr), cudaMemcpyHostToDevice) == cudaSuccess) c.host_status = hword;
+    }
+    if (!c.host_status) cudaGetLastError();
+  }
   c.sm_count = prop.multiProcessorCount;
   c.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
   c.device = dev;
   return &c;
 }
 
+DeviceCtx* ready_ctx() {
+  DeviceCtx* ctx = current_ctx();
+  if (!ctx) return nullptr;
+  if (ctx->host_status) {
+    const unsigned v = *reinterpret_cast<volatile unsigned*>(ctx->host_status);
+    if (v != 0) {
+      fail(B200_ERR_KERNEL,
+           "an earlier kernel on device %d gave up a bounded wait (status 0x%08x: site %u, block %u); results "
+           "since then are invalid and nothing more is launched until b200_status(&v, 1) clears it",
+           ctx->device, v, v & 0xFFu, v >> 16);
+      return nullptr;
+    }
+  }
+  return ctx;
+}
+
 int* next_sched_counter(DeviceCtx* ctx, cudaStream_t stream) {
   static int* base[64] = {};
-  static unsigned next[64] = {};
-  int* slot = nullptr;
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (!base[ctx->device]) {
-      void* ptr = nullptr;
-      cudaError_t e = cudaGetSymbolAddress(&ptr, g_sched_ring);
-      if (e != cudaSuccess) {
-        fail(B200_ERR_CUDA, "cudaGetSymbolAddress(scheduler ring): %s", cudaGetErrorString(e));
-        return nullptr;
-      }
-      base[ctx->device] = static_cast<int*>(ptr);
-    }
-    slot = base[ctx->device] + (next[ctx->device]++ % 256);
-  }
-  cudaError_t e = cudaMemsetAsync(slot, 0, sizeof(int), stream);
+  static unsigned next_eager[64] = {}, next_graph[64] = {};
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  cudaError_t e = cudaStreamIsCapturing(stream, &cap);
   if (e != cudaSuccess) {
-    fail(B200_ERR_CUDA, "scheduler counter reset: %s", cudaGetErrorString(e));
+    fail(B200_ERR_CUDA, "cudaStreamIsCapturing: %s", cudaGetErrorString(e));
     return nullptr;
   }
-  return slot;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!base[ctx->device]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_sched_ring);
+    if (e != cudaSuccess) {
+      fail(B200_ERR_CUDA, "cudaGetSymbolAddress(scheduler ring): %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    base[ctx->device] = static_cast<int*>(ptr);
+  }
+  if (cap == cudaStreamCaptureStatusNone) return base[ctx->device] + (next_eager[ctx->device]++ % kSchedRing);
+  if (next_graph[ctx->device] >= kSchedGraphPool) {
+    fail(B200_ERR_UNSUPPORTED,
+         "this process has captured %u attention launches into CUDA graphs on device %d; each keeps its work "
+         "counter for the life of the process and the pool holds no more",
+         kSchedGraphPool, ctx->device);
+    return nullptr;
+  }
+  return base[ctx->device] + kSchedRing + next_graph[ctx->device]++;
 }
 
 bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
@@ -167,6 +221,39 @@ bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const 
   return true;
 }
 
+// b200_selftest_wait_timeout: the give-up path of the kernels' bounded waits, on a barrier that
+// nothing ever arrives on.  Same shape as the real kernels: TMEM is allocated, one thread waits
+// (with the limit passed in instead of the kernels' 250 ms), the failure is recorded, the CTA
+// tears down in the usual order and frees its TMEM.  It faults nothing and returns by itself.
+__global__ void __launch_bounds__(64, 1) wait_timeout_selftest_kernel(unsigned* status, unsigned long long limit_ns) {
+  __shared__ uint64_t never;  // an mbarrier with one expected arrival that never comes
+  __shared__ uint32_t tmem_slot;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(&never, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(&tmem_slot, 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(&tmem_slot);
+  if (warp == 1 && lane == 0) {
+    if (!mbar_try_wait(&never, 0)) mbar_wait_slow(&never, 0, status, SITE_SELFTEST, limit_ns);
+  }
+  __syncwarp();
+  if (*(volatile unsigned*)status != 0) __nanosleep(100000);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 32);
+  }
+}
+
 }  // namespace tb
 
 using namespace tb;
@@ -197,7 +284,7 @@ extern "C" B200_API int b200_trace_read(void* dst, size_t bytes) {
 
 int b200_status(unsigned* value, int clear) {
   DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  if (!ctx) return g_err_code;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
   unsigned v = 0;
@@ -207,7 +294,23 @@ int b200_status(unsigned* value, int clear) {
   if (clear && v != 0) {
     e = cudaMemset(ctx->status, 0, sizeof(unsigned));
     if (e != cudaSuccess) return fail(B200_ERR_CUDA, "status clear: %s", cudaGetErrorString(e));
+    if (ctx->host_status) *reinterpret_cast<volatile unsigned*>(ctx->host_status) = 0;
+    // a kernel that gave up may have left its work counter non-zero
+    void* ring = nullptr;
+    e = cudaGetSymbolAddress(&ring, g_sched_ring);
+    if (e == cudaSuccess) e = cudaMemset(ring, 0, sizeof(int) * (kSchedRing + kSchedGraphPool));
+    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "work counter clear: %s", cudaGetErrorString(e));
   }
+  return B200_OK;
+}
+
+int b200_selftest_wait_timeout(b200_stream_t stream, unsigned limit_us) {
+  if (limit_us == 0 || limit_us > 250000u) return fail(B200_ERR_ARG, "limit_us must be in [1, 250000]");
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
+  wait_timeout_selftest_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ctx->status, 1000ull * limit_us);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "self-test launch: %s", cudaGetErrorString(e));
   return B200_OK;
 }
 
@@ -223,7 +326,7 @@ int b200_matmul_plan(int M, int N, int K, int in_dtype, int* splits, size_t* wor
   if (in_dtype != B200_F16 && in_dtype != B200_BF16 && in_dtype != B200_E4M3)
     return fail(B200_ERR_ARG, "in_dtype must be F16, BF16 or E4M3");
   DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  if (!ctx) return g_err_code;
   *splits = (M == 0 || N == 0 || K == 0) ? 1 : gemm_plan_splits(ctx, M, N, K, in_dtype);
   *workspace_bytes = *splits > 1 ? (size_t)*splits * M * N * sizeof(float) : 0;
   return B200_OK;
@@ -248,8 +351,8 @@ int b200_matmul_chain(b200_stream_t stream, const void* a, const void* b, const 
     return fail(B200_ERR_ARG, "chain-dot: out_dtype must be F16, BF16 or F32");
   if (N > 128 || N2 > 128)
     return fail(B200_ERR_UNSUPPORTED, "chain-dot keeps a whole row of A B in one tile: N and N2 must be at most 128");
-  DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
   if (M == 0 || N2 == 0) return B200_OK;
   if (!c || (N > 0 && !w) || (N > 0 && K > 0 && (!a || !b))) return fail(B200_ERR_ARG, "null pointer");
   if (stride_cn != 1 && N2 != 1) return fail(B200_ERR_UNSUPPORTED, "C must have stride_cn == 1");
@@ -289,8 +392,8 @@ int b200_matmul_bias(b200_stream_t stream, const void* a, const void* b, void* c
       return fail(B200_ERR_ARG, "the softmax epilogue takes no bias, no split-K and a 16- or 32-bit output");
     if (K == 0) return fail(B200_ERR_UNSUPPORTED, "softmax epilogue with K == 0");
   }
-  DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
   if (M == 0 || N == 0) return B200_OK;
   if (!c || (K > 0 && (!a || !b))) return fail(B200_ERR_ARG, "null pointer");
   if (stride_cn != 1 && N != 1) return fail(B200_ERR_UNSUPPORTED, "C must have stride_cn == 1");
@@ -326,8 +429,8 @@ int b200_grouped_matmul_prepare(b200_stream_t stream, int group_count, const voi
   if (group_count == 0) return B200_OK;
   if (!a || !b || !c || !sizes || !lds) return fail(B200_ERR_ARG, "null array");
   if (int rc = grouped_args_ok(in_dtype, out_dtype)) return rc;
-  DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
   return prepare_gemm_grouped(ctx, reinterpret_cast<cudaStream_t>(stream), group_count, a, b, c, sizes, lds, in_dtype,
                               out_dtype, workspace, total_tiles);
 }
@@ -337,8 +440,8 @@ int b200_grouped_matmul_run(b200_stream_t stream, const void* workspace, int tot
   if (total_tiles == 0) return B200_OK;
   if (!workspace) return fail(B200_ERR_ARG, "null workspace");
   if (int rc = grouped_args_ok(in_dtype, out_dtype)) return rc;
-  DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
   return launch_gemm_grouped(ctx, reinterpret_cast<cudaStream_t>(stream), workspace, total_tiles, in_dtype, out_dtype);
 }
 
@@ -352,9 +455,10 @@ int b200_grouped_matmul(b200_stream_t stream, int group_count, const void* const
   return b200_grouped_matmul_run(stream, workspace, total_tiles, in_dtype, out_dtype);
 }
 
-int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m, int Z,
-                       int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
-                       const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal, int dtype) {
+int b200_attention_fwd_stats(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m,
+                             float* row_max, int Z, int H, int N, int D, const int64_t stride_q[4],
+                             const int64_t stride_k[4], const int64_t stride_v[4], const int64_t stride_o[4],
+                             float sm_scale, int causal, int dtype) {
   if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
   if (dtype != B200_F16 && dtype != B200_BF16 && dtype != B200_E5M2)
     return fail(B200_ERR_ARG, "forward attention dtype must be F16, BF16 or E5M2");
@@ -363,13 +467,20 @@ int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const
   if (!stride_q || !stride_k || !stride_v || !stride_o) return fail(B200_ERR_ARG, "null stride array");
   if (dtype != B200_E5M2 && (stride_q[3] != 1 || stride_k[3] != 1 || stride_v[3] != 1 || stride_o[3] != 1))
     return fail(B200_ERR_UNSUPPORTED, "the head dimension must be contiguous");
-  DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
   if (Z == 0 || H == 0 || N == 0) return B200_OK;
   if (!q || !k || !v || !o || !m) return fail(B200_ERR_ARG, "null pointer");
   if ((long long)Z * H * ((N + 127) / 128) > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "too many work items");
-  return launch_attn_fwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, m, Z, H, N, D, stride_q, stride_k,
-                         stride_v, stride_o, sm_scale, causal, dtype);
+  return launch_attn_fwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, m, row_max, Z, H, N, D, stride_q,
+                         stride_k, stride_v, stride_o, sm_scale, causal, dtype);
+}
+
+int b200_attention_fwd(b200_stream_t stream, const void* q, const void* k, const void* v, void* o, float* m, int Z,
+                       int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
+                       const int64_t stride_v[4], const int64_t stride_o[4], float sm_scale, int causal, int dtype) {
+  return b200_attention_fwd_stats(stream, q, k, v, o, m, nullptr, Z, H, N, D, stride_q, stride_k, stride_v, stride_o,
+                                  sm_scale, causal, dtype);
 }
 
 int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const void* v, const void* o,
@@ -387,8 +498,8 @@ int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const
     if (!st) return fail(B200_ERR_ARG, "null stride array");
     if (st[3] != 1) return fail(B200_ERR_UNSUPPORTED, "the head dimension must be contiguous");
   }
-  DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
   if (Z == 0 || H == 0 || N == 0) return B200_OK;
   if (!q || !k || !v || !o || !d_o || !m || !delta || !dq || !dk || !dv) return fail(B200_ERR_ARG, "null pointer");
   if ((long long)Z * H * ((N + 127) / 128) > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "too many work items");
@@ -408,17 +519,21 @@ int b200_attention_bwd_noalloc(b200_stream_t stream, const void* q, const void* 
                                const int64_t stride_dk[4], const int64_t stride_dv[4], float sm_scale, int causal,
                                int dtype) {
   if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
-  const long long rows = (long long)Z * H * N;
-  if (rows > attn_bwd_scratch_capacity())
+  // Z*H is checked first so that the row count cannot overflow: Z*H <= 2^20 and N < 2^31
+  const long long cap = attn_bwd_scratch_capacity(), zh = (long long)Z * H;
+  const long long rows = (zh > cap) ? cap + 1 : zh * N;
+  if (rows > cap)
     return fail(B200_ERR_UNSUPPORTED,
-                "Z*H*N = %lld rows exceed the built-in scratch of %lld rows; use b200_attention_bwd with caller "
+                "Z*H*N = %lld * %d rows exceed the built-in scratch of %lld rows; use b200_attention_bwd with caller "
                 "scratch for this size",
-                rows, attn_bwd_scratch_capacity());
-  if (rows == 0) return B200_OK;
-  DeviceCtx* ctx = current_ctx();
-  if (!ctx) return B200_ERR_DEVICE;
-  float* delta = attn_bwd_scratch(ctx);
-  if (!delta) return B200_ERR_CUDA;
+                zh, N, cap);
+  float* delta = nullptr;
+  if (rows > 0) {  // (an empty problem still goes through the same argument validation below)
+    DeviceCtx* ctx = ready_ctx();
+    if (!ctx) return g_err_code;
+    delta = attn_bwd_scratch(ctx);
+    if (!delta) return B200_ERR_CUDA;
+  }
   // same validation and launches as the caller-scratch entry point, on the built-in array
   return b200_attention_bwd(stream, q, k, v, o, d_o, m, delta, dq, dk, dv, Z, H, N, D, stride_q, stride_k, stride_v,
                             stride_o, stride_do, stride_dq, stride_dk, stride_dv, sm_scale, causal, dtype);

@@ -26,6 +26,7 @@ enum WaitSite : unsigned {
   SITE_FWD_O_FULL = 15, SITE_FWD_S_EMPTY = 16, SITE_FWD_O_READY = 17, SITE_FWD_SCHED = 18,
   SITE_BWD_LOAD_EMPTY = 20, SITE_BWD_LOAD_FULL = 21, SITE_BWD_S_FULL = 22, SITE_BWD_P_FULL = 23,
   SITE_BWD_DP_FULL = 24, SITE_BWD_DS_FULL = 25, SITE_BWD_ACC_FULL = 26, SITE_BWD_FREE = 27, SITE_BWD_KV = 28, SITE_BWD_SCHED = 29,
+  SITE_SELFTEST = 99,  // b200_selftest_wait_timeout: a barrier that nothing arrives on
 };
 
 __device__ __forceinline__ unsigned long long gtimer_ns() {
@@ -60,17 +61,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Records the first failed wait.  The status word is followed (words 2-3, 8-byte aligned) by the
+// device-visible address of a word in pinned host memory, or 0: the first failure is mirrored
+// there so that the host side sees it at its next entry point without synchronising the device.
+__device__ __forceinline__ void record_wait_failure(unsigned* status, unsigned code) {
+  if (atomicCAS(status, 0u, code) == 0u) {
+    unsigned* mirror = *reinterpret_cast<unsigned* volatile*>(status + 2);
+    if (mirror) {
+      *reinterpret_cast<volatile unsigned*>(mirror) = code;
+      __threadfence_system();
+    }
+  }
+}
 // Bounded wait.  Returns false (and records `site`) when the limit is reached or another
-// thread already recorded a failure.
-static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, unsigned* status, unsigned site) {
+// thread already recorded a failure.  Out of line by default, so that the spin loop stays out of
+// the callers' hot paths; kernels that re-divide registers between warpgroups (setmaxnreg) define
+// B200_INLINE_WAIT_SLOW before including this header: ptxas cannot allocate registers across a
+// real call inside such a region.
+#ifdef B200_INLINE_WAIT_SLOW
+#define B200_WAIT_SLOW_ATTR __forceinline__
+#else
+#define B200_WAIT_SLOW_ATTR __noinline__
+#endif
+static __device__ B200_WAIT_SLOW_ATTR bool mbar_wait_slow(uint64_t* bar, uint32_t parity, unsigned* status, unsigned site,
+                                                   unsigned long long limit_ns = kWaitLimitNs) {
   if (*(volatile unsigned*)status != 0) return false;
   const unsigned long long t0 = gtimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63u) == 0) {
       if (*(volatile unsigned*)status != 0) return false;
-      if (gtimer_ns() - t0 > kWaitLimitNs) {
-        atomicCAS(status, 0u, site | ((parity & 1u) << 8) | ((blockIdx.x & 0xFFFFu) << 16));
+      if (gtimer_ns() - t0 > limit_ns) {
+        record_wait_failure(status, site | ((parity & 1u) << 8) | ((blockIdx.x & 0xFFFFu) << 16));
         return false;
       }
     }
@@ -409,6 +431,20 @@ __device__ __forceinline__ void umma_ss_pair_elect(uint32_t d_tmem, uint64_t ade
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
   }
+}
+
+// ------------------------------------------------------------------ register budget per warpgroup
+// setmaxnreg moves registers between the warpgroups (four consecutive warps) of a CTA at run
+// time: the kernel is launched with 64K / threads registers per thread, the warpgroups that need
+// few give some back (dec) and the ones that hold whole score rows take them (inc; blocks until
+// the registers are free).  Every warp of the warpgroup must execute the same instruction.
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 // ------------------------------------------------------------------ small helpers

@@ -1070,14 +1070,9 @@ constexpr size_t smem_bytes(int stages, int stage_bytes, int epilogue_warps) {
 template <int BM, int BN, int STAGES, bool EXT>
 int launch_tile_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
                 GemmParams& p) {
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];
   constexpr size_t smem = smem_bytes(STAGES, (BM + BN) * KBYTES, BM / 32);
-  if (!attr_done[ctx->device]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(gemm_kernel<BM, BN, STAGES, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(gemm): %s", cudaGetErrorString(e));
-    attr_done[ctx->device] = true;
-  }
+  if (int rc = ensure_dynamic_smem(gemm_kernel<BM, BN, STAGES, EXT>, smem, ctx->device, attr_done, "gemm")) return rc;
   const int work = p.num_tiles * p.splits;
   const int grid = work < ctx->sm_count ? work : ctx->sm_count;
   gemm_kernel<BM, BN, STAGES, EXT><<<grid, 64 + BM + (BM == 256 ? 32 : 0), smem, stream>>>(ta, tb_, tc, p);
@@ -1089,15 +1084,10 @@ int launch_tile_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, co
 template <int STAGES, int NB, bool EXT>
 int launch_pair_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& ta, const CUtensorMap& tb_, const CUtensorMap& tc,
                 GemmParams& p) {
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];
   constexpr size_t smem = smem_bytes(STAGES, (128 + 128 * NB) * KBYTES, pair_staging_warps(STAGES, NB));
   if (pair_staging_warps(STAGES, NB) == 0) p.c_tma = 0;
-  if (!attr_done[ctx->device]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<STAGES, NB, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem);
-    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(gemm pair): %s", cudaGetErrorString(e));
-    attr_done[ctx->device] = true;
-  }
+  if (int rc = ensure_dynamic_smem(gemm_pair_kernel<STAGES, NB, EXT>, smem, ctx->device, attr_done, "gemm pair")) return rc;
   int pairs = ctx->sm_count / 2;
   if (p.num_tiles < pairs) pairs = p.num_tiles;
   cudaLaunchConfig_t cfg = {};
@@ -1161,11 +1151,12 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   const bool b_mn = !(sbk == 1 || K == 1);
 
   // Can TMA address A and B?  (C is written with plain stores and has no such limit.)
-  auto tma_ok = [&](const void* base, int64_t row_stride) {
-    return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ((row_stride * elt) & 15) == 0;
+  // a single row (or column) has no row stride to speak of, but its base must still be aligned
+  auto tma_ok = [&](const void* base, int64_t row_stride, int64_t rows) {
+    return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && (rows == 1 || ((row_stride * elt) & 15) == 0);
   };
-  const bool a_ok = tma_ok(a, a_mn ? sak : sam) || (a_mn ? K : M) == 1;
-  const bool b_ok = tma_ok(b, b_mn ? sbk : sbn) || (b_mn ? K : N) == 1;
+  const bool a_ok = tma_ok(a, a_mn ? sak : sam, a_mn ? K : M);
+  const bool b_ok = tma_ok(b, b_mn ? sbk : sbn, b_mn ? K : N);
   if (!a_ok || !b_ok || (a_mn && sam != 1) || (b_mn && sbn != 1) || env_int("B200_GEMM_PLAIN", 0)) {
     if (activation == B200_ACT_SOFTMAX)
       return fail(B200_ERR_UNSUPPORTED, "the softmax epilogue needs operands that TMA can address");
@@ -1261,7 +1252,15 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     uint32_t box[2] = {64, 32};
     if (encode_tmap(&tcm, out_dtype, 2, c, dims, strides, box, true)) p.c_tma = 1;
   }
-  if (pair) return pair_nb == 2 ? launch_pair<4, 2>(ctx, stream, ta, tbm, tcm, p) : launch_pair<7, 1>(ctx, stream, ta, tbm, tcm, p);
+  if (pair) {
+    if (pair_nb == 2) return launch_pair<4, 2>(ctx, stream, ta, tbm, tcm, p);
+    switch (env_int("B200_GEMM_PAIR_STAGES", 6)) {
+      case 4: return launch_pair<4, 1>(ctx, stream, ta, tbm, tcm, p);
+      case 5: return launch_pair<5, 1>(ctx, stream, ta, tbm, tcm, p);
+      case 7: return launch_pair<7, 1>(ctx, stream, ta, tbm, tcm, p);
+      default: return launch_pair<6, 1>(ctx, stream, ta, tbm, tcm, p);
+    }
+  }
   int rc;
   switch (bn) {
     case 256:
@@ -1290,12 +1289,11 @@ int launch_gemm_chain(DeviceCtx* ctx, cudaStream_t stream, const void* a, const 
                       int64_t scm, int in_dtype, int out_dtype) {
   const int elt = 2, bk_elems = KBYTES / elt;
   const bool a_mn = !(sak == 1 || K == 1), b_mn = !(sbk == 1 || K == 1), w_mn = !(swk == 1 || N == 1);
-  auto tma_ok = [&](const void* base, int64_t row_stride) {
-    return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && ((row_stride * elt) & 15) == 0;
+  auto tma_ok = [&](const void* base, int64_t row_stride, int64_t rows) {
+    return (reinterpret_cast<uintptr_t>(base) & 15) == 0 && (rows == 1 || ((row_stride * elt) & 15) == 0);
   };
-  if (!(tma_ok(a, a_mn ? sak : sam) || (a_mn ? K : M) == 1) || !(tma_ok(b, b_mn ? sbk : sbn) || (b_mn ? K : N) == 1) ||
-      !(tma_ok(w, w_mn ? swk : swn) || (w_mn ? N : N2) == 1) || (a_mn && sam != 1) || (b_mn && sbn != 1) ||
-      (w_mn && swn != 1))
+  if (!tma_ok(a, a_mn ? sak : sam, a_mn ? K : M) || !tma_ok(b, b_mn ? sbk : sbn, b_mn ? K : N) ||
+      !tma_ok(w, w_mn ? swk : swn, w_mn ? N : N2) || (a_mn && sam != 1) || (b_mn && sbn != 1) || (w_mn && swn != 1))
     return fail(B200_ERR_UNSUPPORTED, "chain-dot needs A, B and W that TMA can address (16-byte aligned base and rows)");
   GemmParams p{};
   p.c = c; p.M = M; p.N = N2; p.K = K; p.ldc = scm;
@@ -1335,12 +1333,8 @@ int launch_gemm_chain(DeviceCtx* ctx, cudaStream_t stream, const void* a, const 
   }
   constexpr int STAGES = 4;
   constexpr size_t smem = (size_t)STAGES * 256 * KBYTES + 2 * 128 * KBYTES + 4 * STG_BYTES + (2 * STAGES + 6) * 8 + 16 + 1024;
-  static bool attr_done[64] = {};
-  if (!attr_done[ctx->device]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_chain_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(chain gemm): %s", cudaGetErrorString(e));
-    attr_done[ctx->device] = true;
-  }
+  static std::atomic<bool> attr_done[64];
+  if (int rc = ensure_dynamic_smem(gemm_chain_kernel<STAGES>, smem, ctx->device, attr_done, "chain gemm")) return rc;
   gemm_chain_kernel<STAGES><<<(M + 127) / 128, 192, smem, stream>>>(ta, tbm, tw, tcm, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "chain gemm launch: %s", cudaGetErrorString(e));
@@ -1421,13 +1415,9 @@ int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, const void* workspa
   p.idesc = make_idesc(fmt, fmt, 0, 1, BM, BN);
   p.ga = make_geom(false, BM, elt, bk_elems);
   p.gb = make_geom(true, BN, elt, bk_elems);
-  static bool attr_done[64] = {};
+  static std::atomic<bool> attr_done[64];
   constexpr size_t smem = smem_bytes(STAGES, (BM + BN) * KBYTES, BM / 32);
-  if (!attr_done[ctx->device]) {
-    e = cudaFuncSetAttribute(gemm_grouped_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(grouped gemm): %s", cudaGetErrorString(e));
-    attr_done[ctx->device] = true;
-  }
+  if (int rc = ensure_dynamic_smem(gemm_grouped_kernel<STAGES>, smem, ctx->device, attr_done, "grouped gemm")) return rc;
   const int grid = total_tiles < ctx->sm_count ? total_tiles : ctx->sm_count;
   gemm_grouped_kernel<STAGES><<<grid, 192, smem, stream>>>(reinterpret_cast<const GroupDesc*>(workspace), total_tiles, p);
   e = cudaGetLastError();

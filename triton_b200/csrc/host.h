@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/triton_b200.h"
 #include "trace.h"
 
@@ -15,13 +17,21 @@ struct DeviceCtx {
   int sm_count = 0;
   int max_smem_optin = 0;
   unsigned* status = nullptr;  // device address of the status word (a __device__ symbol, never cudaMalloc'd)
+  unsigned* host_status = nullptr;  // pinned host mirror of the status word (nullptr: none), written by a failing kernel
 };
 
 // Context of the CURRENT device; created on first use.  Returns nullptr (and sets the error
 // string) when no usable sm_100 device is current.
 DeviceCtx* current_ctx();
 
-// A zeroed work counter for one launch of a persistent kernel on `stream` (nullptr + error string on failure).
+// current_ctx() for an entry point that launches: additionally refuses (B200_ERR_KERNEL, nullptr)
+// while the device's status word records a bounded wait that ran out.  Reads the pinned host
+// mirror, so it costs no device synchronisation.
+DeviceCtx* ready_ctx();
+
+// A work counter (zero between launches: the kernel restores it) for one launch of a persistent kernel on
+// `stream`; launches under stream capture get counters that are never handed out again (nullptr + error
+// string on failure).
 int* next_sched_counter(DeviceCtx* ctx, cudaStream_t stream);
 
 // Record an error message for b200_last_error() and return `code`.
@@ -31,6 +41,18 @@ int fail(int code, const char* fmt, ...);
 // dimension 1 (dimension 0 is contiguous).  swizzle128: 128-byte swizzle when true, none otherwise.
 bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
                  const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize of `kernel`, set once per device; `done` is the
+// launcher's static per-device flag array.  Host threads may race here: setting the attribute twice
+// is harmless, the flags are atomics.
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, size_t smem, int device, std::atomic<bool>* done, const char* what) {
+  if (done[device].load(std::memory_order_acquire)) return B200_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaFuncSetAttribute(%s): %s", what, cudaGetErrorString(e));
+  done[device].store(true, std::memory_order_release);
+  return B200_OK;
+}
 
 inline int dtype_bytes(int dt) {
   switch (dt) {
@@ -60,7 +82,7 @@ int launch_gemm_grouped(DeviceCtx* ctx, cudaStream_t stream, const void* workspa
                         int out_dtype);
 
 int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, void* o,
-                    float* m, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
+                    float* m, float* row_max, int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
                     const int64_t* so, float sm_scale, int causal, int dtype);
 
 int launch_attn_bwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, const void* o,

@@ -67,6 +67,26 @@ def _matmul_plan(M, N, K, dt):
     return hit
 
 
+_scale_cache = {}  # (value, device) -> 1-element fp32 tensor: a python-float scale costs one H2D copy ever
+
+
+def _scale_tensor(value, dev):
+    key = (value, dev.index)
+    t = _scale_cache.get(key)
+    if t is None:
+        if len(_scale_cache) > 1024:
+            _scale_cache.clear()
+        t = _scale_cache[key] = torch.tensor([value], dtype=torch.float32, device=dev)
+    return t
+
+
+def _check_out(c, M, N, out_dtype, dev):
+    """The kernel writes M rows of N elements of `out_dtype` through `c`: anything else is an
+    out-of-bounds device write, so the shape, type and device must hold whatever N is."""
+    assert tuple(c.shape) == (M, N) and c.dtype == out_dtype and c.device == dev and (c.stride(1) == 1 or N == 1), \
+        "out= must be an [M, N] tensor of the output type on the operands' device with unit column stride"
+
+
 def _require_cuda(*ts):
     for t in ts:
         if not t.is_cuda:
@@ -106,13 +126,13 @@ def matmul(a, b, activation="", *, scale_a=None, scale_b=None, out_dtype=None, o
         out_dtype = torch.float16 if a.dtype == torch.float16 else torch.bfloat16
     with _on_device(dev):
         c = out if out is not None else torch.empty((M, N), device=dev, dtype=out_dtype)
-        assert c.shape == (M, N) and c.dtype == out_dtype and c.stride(1) == 1 or N == 1
+        _check_out(c, M, N, out_dtype, dev)
 
         def scale_ptr(s):
             if s is None:
                 return None, None
             if not torch.is_tensor(s):
-                s = torch.tensor([float(s)], dtype=torch.float32, device=dev)
+                s = _scale_tensor(float(s), dev)
             assert s.dtype == torch.float32 and s.numel() == 1 and s.device == dev
             return s.data_ptr(), s
 
@@ -276,10 +296,12 @@ def quantize_e4m3(x):
     return (x.float() * s).to(torch.float8_e4m3fn), (1.0 / s).reshape(1)
 
 
-def attention_forward(q, k, v, causal, sm_scale):
+def attention_forward(q, k, v, causal, sm_scale, return_row_max=False):
     """Forward only: returns (O, M).  M[Z,H,N] is the reference's saved statistics tensor, the
     base-2 log-sum-exp of the scores scaled by sm_scale*log2(e) (06-fused-attention.py:183-184);
-    the natural-log LSE is M * ln 2."""
+    the natural-log LSE is M * ln 2.  With return_row_max=True a third tensor follows: the base-2
+    row maximum of the scaled scores (what the older kernels' separate L and M are made of, see
+    attention_old_forward)."""
     HEAD_DIM_Q, HEAD_DIM_K, HEAD_DIM_V = q.shape[-1], k.shape[-1], v.shape[-1]
     assert q.dim() == 4 and k.shape == q.shape and v.shape == q.shape, "q, k, v must be [Z, H, N, D] of one shape"
     assert HEAD_DIM_Q == HEAD_DIM_K and HEAD_DIM_K == HEAD_DIM_V
@@ -292,8 +314,8 @@ def attention_forward(q, k, v, causal, sm_scale):
     if D in (16, 32) and not fp8:
         # head dims below the kernels' 64: zero columns change neither q k^T nor the kept columns of O
         qp, kp, vp = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v))
-        o, M = attention_forward(qp, kp, vp, causal, sm_scale)
-        return o[..., :D].contiguous(), M
+        o, *stats = attention_forward(qp, kp, vp, causal, sm_scale, return_row_max)
+        return (o[..., :D].contiguous(), *stats)
     with _on_device(dev):
         if fp8:
             # the reference's fp8 forward (06-fused-attention.py:609-615) is given V with the key
@@ -305,12 +327,14 @@ def attention_forward(q, k, v, causal, sm_scale):
         else:
             o = torch.empty_like(q)
         M = torch.empty((Z, H, N), device=dev, dtype=torch.float32)
-        code = _lib.lib().b200_attention_fwd(
-            _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), M.data_ptr(), Z, H, N, D,
+        row_max = torch.empty((Z, H, N), device=dev, dtype=torch.float32) if return_row_max else None
+        code = _lib.lib().b200_attention_fwd_stats(
+            _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), M.data_ptr(),
+            row_max.data_ptr() if return_row_max else None, Z, H, N, D,
             _lib.strides4(q), _lib.strides4(k), _lib.strides4(v), _lib.strides4(o),
             float(sm_scale), 1 if causal else 0, _DT[q.dtype])
         _lib.check(code, "attention_fwd")
-    return o, M
+    return (o, M, row_max) if return_row_max else (o, M)
 
 
 def attention_backward(q, k, v, o, M, do, causal, sm_scale):
@@ -363,3 +387,48 @@ def attention(q, k, v, causal, sm_scale, sequence_parallel=False):
     (python/test/regression/test_performance.py:194); it changes nothing here: both backward
     kernels are parallel over 128-row blocks of the sequence in either case."""
     return _attention.apply(q, k, v, causal, sm_scale)
+
+
+# ---------------------------------------------------------------------------------------------
+# The reference's older flash attention (python/test/unit/hopper/test_flashattention.py:294-358):
+# `attention(q, k, v, sm_scale)`, always causal, statistics kept as two tensors L and M.
+_LN2 = 0.6931471805599453
+
+
+def attention_old_forward(q, k, v, sm_scale):
+    """(O, L, M) of the older forward kernel (test_flashattention.py:36-131): M[Z*H, N] is the row
+    maximum of q.k * sm_scale over the causal range and L[Z*H, N] the row sum of exp(score - M)
+    (:128-131, natural base).  The same kernel as attention_forward computes them: it returns the
+    base-2 log-sum-exp and the base-2 row maximum, and L = 2^(lse2 - max2), M = max2 * ln 2."""
+    assert q.shape[-1] == k.shape[-1] == v.shape[-1] and q.shape[-1] in {16, 32, 64, 128}  # :301-303
+    o, lse2, max2 = attention_forward(q, k, v, True, sm_scale, return_row_max=True)
+    Z, H, N, _ = q.shape
+    L = torch.exp2(lse2 - max2).reshape(Z * H, N)
+    M = (max2 * _LN2).reshape(Z * H, N)
+    return o, L, M
+
+
+class _attention_old(torch.autograd.Function):
+    """Mirror of the older autograd wrapper (test_flashattention.py:294-358): saves
+    (q, k, v, o, L, m) as it does; the backward rebuilds the base-2 log-sum-exp from L and m."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, sm_scale):
+        o, L, m = attention_old_forward(q, k, v, sm_scale)
+        ctx.save_for_backward(q, k, v, o, L, m)
+        ctx.sm_scale = sm_scale
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, L, m = ctx.saved_tensors
+        Z, H, N, _ = q.shape
+        lse2 = ((m + torch.log(L)) * (1.0 / _LN2)).reshape(Z, H, N)
+        dq, dk, dv = attention_backward(q, k, v, o, lse2, do.contiguous(), True, ctx.sm_scale)
+        return dq, dk, dv, None
+
+
+def attention_old(q, k, v, sm_scale):
+    """The four-argument `attention = _attention.apply` of test_flashattention.py:358: causal
+    attention, differentiable with respect to q, k and v."""
+    return _attention_old.apply(q, k, v, sm_scale)
