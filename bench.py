@@ -12,9 +12,11 @@ workload on its own M-row block of a taller A (weak scaling, no data-path collec
 is the max over ranks.  The other four configurations of the path are timed briefly and
 reported under "configs" for context.
 
---impl reference times the CPU oracle (the numpy restatement of the reference's kernels; the
-reference's own CPU path is the Triton interpreter executing the same arithmetic) on the host
-cores, on a bounded sample of the same workload.
+--impl reference times the reference's CPU path on the host cores: the Triton interpreter
+(TRITON_INTERPRET=1, the pip `triton` package as executor) running the matmul tile program
+(oracle/interp_matmul.py, the reference kernel's algorithm restated in its own kernel language;
+the reference checkout itself does not exist on the GPU box) at the largest shape that fits the
+time budget; the numpy restatement of the same tile loop is timed beside it.
 """
 import argparse
 import json
@@ -142,31 +144,97 @@ def use_all_host_threads():
         pass
 
 
+PORT_ROWS = 2048  # rows of A in the numpy port's sample (every leg that times the port uses this sample)
+
+
+def port_baseline():
+    """The numpy restatement of the reference's tile loop on PORT_ROWS rows of A against all of B."""
+    use_all_host_threads()
+    time_oracle(128)  # BLAS thread pool and page faults out of the way
+    v, dt = time_oracle(PORT_ROWS)
+    return {"value": v, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
+            "sample": f"{PORT_ROWS} of {M} rows of A against all of B (full K, N): {dt:.1f} s of the numpy/BLAS "
+                      "restatement of the reference's tile loop"}
+
+
+INTERP_SHAPES = [(512, 512, 512), (1024, 1024, 1024), (1536, 1536, 1536), (2048, 2048, 2048)]
+
+
+def time_interpreter(shape, repeats=1, timeout=600):
+    """One launch of the matmul tile program under the Triton interpreter, in a subprocess (the
+    interpreter is selected by an environment variable read when `triton` is imported).  Returns
+    the subprocess's JSON record, or {"unavailable": reason}."""
+    import subprocess
+    env = dict(os.environ, TRITON_INTERPRET="1")
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        env[var] = str(os.cpu_count() or 1)
+    cmd = [sys.executable, "-m", "oracle.interp_matmul", *map(str, shape), str(repeats)]
+    try:
+        r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"interpreter run of {shape} exceeded {timeout} s"}
+    if r.returncode != 0:
+        return {"unavailable": "interpreter run failed: " + (r.stderr.strip().splitlines() or ["?"])[-1][:200]}
+    return json.loads(r.stdout.strip().splitlines()[-1])
+
+
+def interpreter_baseline(budget_s=60.0):
+    """The interpreter at the largest shape of INTERP_SHAPES whose run fits `budget_s` (estimated
+    from the next smaller shape: the cost grows with tiles x K-steps)."""
+    best = time_interpreter(INTERP_SHAPES[0])
+    if "unavailable" in best:
+        return {"kind": "interpreter", "value": None, "unit": "TFLOP/s", "cores": os.cpu_count(),
+                "unavailable": best["unavailable"]}
+    for shape in INTERP_SHAPES[1:]:
+        grow = (shape[0] * shape[1] * shape[2]) / (best["M"] * best["N"] * best["K"])
+        if best["seconds"] * grow > budget_s:
+            break
+        rec = time_interpreter(shape)
+        if "unavailable" in rec:
+            break
+        best = rec
+    return {"value": best["tflops"], "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "interpreter",
+            "sample": f"one launch of the 128x256x64 tile program at {best['M']}x{best['N']}x{best['K']} fp16 under "
+                      f"TRITON_INTERPRET=1 (triton {best['triton']} as executor): {best['seconds']:.1f} s; the program "
+                      "loop is single-threaded Python, numpy's BLAS may use every core inside a tile product",
+            "shape": [best["M"], best["N"], best["K"]], "seconds": best["seconds"]}
+
+
 def run_reference(args, rank, world):
     if rank != 0:
         return
-    use_all_host_threads()
-    # size the per-step sample so that the whole run stays within a few minutes
-    _, probe = time_oracle(128)
-    budget = 150.0 / max(1, args.steps + args.warmup)
-    rows = int(min(M, max(128, (budget / probe) * 128 // 128 * 128)))
-    for _ in range(args.warmup):
-        time_oracle(rows)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        time_oracle(rows)
-    dt = time.perf_counter() - t0
-    val = 2.0 * rows * N * K * args.steps / dt / 1e12
-    sample = f"{rows} of {M} rows of A against all of B per step (full K and N), numpy/BLAS tile loop"
-    cores = cpu_threads()
-    print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }))
+    # one step = one interpreter launch at the largest shape that keeps the whole run within a few minutes
+    per_step = 150.0 / max(1, args.steps + args.warmup)
+    probe = time_interpreter(INTERP_SHAPES[0])
+    line = {"impl": "reference", "metric": METRIC, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16",
+            "data": "synthetic"}
+    if "unavailable" in probe:
+        # the interpreter cannot run here: the numpy restatement of the same tile loop stands in
+        port = port_baseline()
+        line.update(value=port["value"], ms_per_step=None, config={"workload": WORKLOAD, "sample": port["sample"]},
+                    cpu_baseline=dict(port, interpreter_unavailable=probe["unavailable"]),
+                    e2e={"value": port["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+        print(json.dumps(line))
+        return
+    shape = INTERP_SHAPES[0]
+    for cand in INTERP_SHAPES[1:]:
+        grow = (cand[0] * cand[1] * cand[2]) / (probe["M"] * probe["N"] * probe["K"])
+        if probe["seconds"] * grow <= per_step:
+            shape = cand
+    rec = time_interpreter(shape, repeats=args.warmup + args.steps) if args.warmup + args.steps > 1 else probe
+    # (the subprocess repeats warm-up + timed launches back to back and reports the mean per launch)
+    val = rec["tflops"]
+    sample = (f"one launch of the reference's matmul tile program (128x256x64 tiles) at {shape[0]}x{shape[1]}x{shape[2]} "
+              f"fp16 per step under the Triton interpreter (TRITON_INTERPRET=1, triton {rec['triton']}), the largest of "
+              f"{INTERP_SHAPES} that keeps {args.steps}+{args.warmup} steps within 150 s")
+    port = port_baseline()
+    line.update(value=val, ms_per_step=rec["seconds"] * 1e3,
+                config={"workload": WORKLOAD, "sample": sample},
+                cpu_baseline={"value": val, "unit": "TFLOP/s", "cores": os.cpu_count(), "kind": "interpreter",
+                              "sample": sample, "port": port},
+                e2e={"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0})
+    print(json.dumps(line))
 
 
 def device_time(fn, steps, warmup, torch, barrier=None, mark=None):
@@ -227,13 +295,18 @@ def other_configs(torch, tb, dev):
     fl = 2 * 2.0 * 4 * 48 * 1024 * 1024 * 64 * 0.5
     o, Mst = tb.attention_forward(q, k, v, True, 0.5)
 
-    def fwd_bwd():
+    # config 5's backward runs as ONE pass (partial dQ per K/V block summed into an fp32 buffer: the
+    # reference's `sequence_parallel` layout, attention(..., sequence_parallel=True)); the two-kernel
+    # backward of the reference's current layout (bitwise repeatable, the library's default) beside it
+    def fwd_bwd(one_pass):
         o_, m_ = tb.attention_forward(q, k, v, True, 0.5)
-        tb.attention_backward(q, k, v, o_, m_, do, True, 0.5)
+        tb.attention_backward(q, k, v, o_, m_, do, True, 0.5, one_pass=one_pass)
 
-    out["c5_attn_fwd_bwd_causal_bf16_z4h48n1024d64"] = timed(fwd_bwd, fl * 3.5)
+    out["c5_attn_fwd_bwd_causal_bf16_z4h48n1024d64"] = timed(lambda: fwd_bwd(True), fl * 3.5)
     out["c5_fwd_only"] = timed(lambda: tb.attention_forward(q, k, v, True, 0.5), fl)
-    out["c5_bwd_only"] = timed(lambda: tb.attention_backward(q, k, v, o, Mst, do, True, 0.5), fl * 2.5)
+    out["c5_bwd_only"] = timed(lambda: tb.attention_backward(q, k, v, o, Mst, do, True, 0.5, one_pass=True), fl * 2.5)
+    out["c5_fwd_bwd_two_kernel_backward"] = timed(lambda: fwd_bwd(False), fl * 3.5)
+    out["c5_bwd_only_two_kernel"] = timed(lambda: tb.attention_backward(q, k, v, o, Mst, do, True, 0.5, one_pass=False), fl * 2.5)
     del q, k, v, do, o, Mst
     # rows beyond the five configs: the widened matmul / attention entry points
     ga = [torch.rand(512, 512, generator=g).half().to(dev) for _ in range(64)]
@@ -275,7 +348,13 @@ def run_profile_case(name):
 
         def fn():
             o, m = tb.attention_forward(q, k, v, True, 0.5)
-            tb.attention_backward(q, k, v, o, m, do, True, 0.5)
+            tb.attention_backward(q, k, v, o, m, do, True, 0.5, one_pass=True)
+    elif name == "c5two":  # config 5 with the two-kernel (bitwise repeatable) backward
+        q, k, v, do = (t.to(dev) for t in cases.attn_inputs(dict(Z=4, H=48, N=1024, D=64, dtype="bf16", seed=20)))
+
+        def fn():
+            o, m = tb.attention_forward(q, k, v, True, 0.5)
+            tb.attention_backward(q, k, v, o, m, do, True, 0.5, one_pass=False)
     elif name == "fp8attn":  # the 8-bit forward on config 4's shape (the reference's fp8 benchmark scale 1.3)
         q, k, v = ((torch.randn(4, 32, 4096, 128, generator=g) * 0.5).to(dev).to(torch.float8_e5m2) for _ in range(3))
         v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
@@ -296,7 +375,93 @@ def run_profile_case(name):
     print("profile case", name, "done")
 
 
+def bind_to_gpu_numa_node(index):
+    """Run this process on the CPUs of the NUMA node the GPU hangs off, so that the pinned host
+    buffers allocated afterwards are local to the GPU's PCIe root (first-touch placement) and the
+    ranks of one box do not all copy through node 0.  Best effort: returns the node or None."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(index)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:  # NVML prints an 8-digit domain, sysfs a 4-digit one
+            bus = bus[4:]
+        node = int(open(f"/sys/bus/pci/devices/{bus}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = []
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus += list(range(int(lo), int(hi or lo) + 1))
+        allowed = sorted(set(cpus) & os.sched_getaffinity(0))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
+def sustained_loop(step, torch, sampler_index, seconds=2.0):
+    """Back-to-back launches for at least `seconds`: the power-capped operating point, whatever
+    --steps was.  Returns TFLOP/s with the SM clock and the throttle reasons sampled meanwhile."""
+    sampler = ClockSampler(sampler_index)
+    sampler.start()
+    torch.cuda.synchronize()
+    sampler.mark()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.time()
+    e0.record()
+    while True:
+        for _ in range(100):
+            step()
+        n += 100
+        torch.cuda.synchronize()
+        if time.time() - t0 >= seconds:
+            break
+    e1.record()
+    torch.cuda.synchronize()
+    sampler.mark()
+    ms = e0.elapsed_time(e1) / n
+    clocks = sampler.stop()
+    return {"tflops": 2.0 * M * N * K / ms / 1e9, "ms_per_launch": ms, "launches": n,
+            "sm_mhz_median": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}
+
+
+def multi_gpu_extras(torch, tb, dev, rank, world, barrier):
+    """What else the path does on several GPUs, beside the headline: config 4's attention forward
+    sharded by (batch, head) over the ranks (total work fixed: strong scaling), and the optional
+    all-gather of the matmul's C row blocks, timed on its own.  Device times, max over ranks."""
+    import cases
+    import torch.distributed as dist
+    from triton_b200 import dist as tdist
+    out = {}
+    q, k, v, _ = cases.attn_inputs(dict(Z=4, H=32, N=4096, D=128, dtype="fp16", seed=20))
+    ql, kl, vl = (tdist.shard_heads(t, world, rank).contiguous().to(dev) for t in (q, k, v))
+    ms = device_time(lambda: tb.attention_forward(ql, kl, vl, True, 128 ** -0.5), 20, 3, torch, barrier)
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    flops = 2 * 2.0 * 4 * 32 * 4096 * 4096 * 128 * 0.5
+    out["attention_c4_fwd_sharded_by_head"] = {
+        "scaling": "strong", "heads_per_rank": ql.shape[1], "ms": float(t[0]) / 20,
+        "tflops_aggregate": flops / (float(t[0]) / 20) / 1e9}
+    del ql, kl, vl
+    # all-gather of C: every rank contributes its [8192/world, 8192] fp16 row block of one 8192^2 C
+    rows = M // world
+    c_local = torch.randn(rows, N, device=dev).half()
+    tdist.all_gather_rows(c_local)
+    ms = device_time(lambda: tdist.all_gather_rows(c_local), 10, 2, torch, barrier)
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    recv = rows * N * 2 * (world - 1)
+    out["all_gather_c_row_blocks"] = {"ms": float(t[0]) / 10, "bytes_received_per_gpu": recv,
+                                      "gbs_per_gpu": recv / (float(t[0]) / 10) / 1e6,
+                                      "note": "NCCL all_gather of an assembled 8192x8192 fp16 C, only on request"}
+    return out
+
+
 def run_ours(args, rank, local_rank, world):
+    numa = bind_to_gpu_numa_node(local_rank)  # before any pinned allocation
     import torch
     import triton_b200 as tb
     from triton_b200 import _lib
@@ -329,8 +494,9 @@ def run_ours(args, rank, local_rank, world):
     # end to end through the public API from host buffers
     e2e_steps = max(1, min(args.steps, 10))
 
-    # HostMatmul: pinned host A, B -> device (A in row blocks), matmul per block, C blocks -> pinned
-    # host, the three overlapped on two copy streams; every step moves all of A, B and C
+    # HostMatmul: pinned host A -> device in row blocks, one matmul per block, C blocks -> pinned
+    # host, the three overlapped on two copy streams.  B is the same host tensor on every step
+    # (the weights of a layer, say): it crosses the link on the first call and stays on the device
     host_mm = tb.HostMatmul(M, N, K, torch.float16, dev)
 
     def e2e_step():
@@ -345,6 +511,7 @@ def run_ours(args, rank, local_rank, world):
         t = torch.tensor([ms, ms_e2e], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, ms_e2e = float(t[0]), float(t[1])
+    extras = multi_gpu_extras(torch, tb, dev, rank, world, barrier) if world > 1 and not args.no_extra else None
 
     flops = 2.0 * M * N * K
     value = world * flops * args.steps / ms / 1e9
@@ -353,42 +520,80 @@ def run_ours(args, rank, local_rank, world):
         pk = peaks()
         per_launch_ms = ms / args.steps
         achieved = flops / per_launch_ms / 1e9
+        # The denominator follows the run: a timed region shorter than about a second in which no
+        # power-cap sample fell is a burst (cuBLAS's burst figure); anything longer, or capped, is the
+        # sustained operating point (cuBLAS's back-to-back figure).
+        capped = bool(clocks and "sw_power_cap" in (clocks.get("reasons") or []))
+        burst = (ms < 1000.0) and not capped
+        peak = pk["burst"] if burst else pk["sustained"]
+        sustained = sustained_loop(step, torch, local_rank) if world == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "per_gpu": "one 8192^3 matmul per step on the rank's own M-row block",
                        "l2": "inputs and output (384 MiB per step) exceed the 126 MB L2; no flush needed",
-                       "tile": os.environ.get("B200_GEMM_TILE", "auto")},
+                       "tile": os.environ.get("B200_GEMM_TILE", "auto"),
+                       "e2e": "A (128 MiB) host->device and C (128 MiB) device->host every step; B is unchanged "
+                              "between steps and stays on the device after the first call",
+                       "numa_node_of_pinned_buffers": numa},
             "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * M * K * 2,
-                    "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K * 2,
+                    "d2h_bytes_per_step": M * N * 2, "steps": e2e_steps,
+                    "h2d_gbs_per_rank": M * K * 2 / (ms_e2e / e2e_steps) / 1e6},
             "gpu_launches": args.steps,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": pk["sustained"], "unit": "TFLOP/s",
-                         "frac": achieved / pk["sustained"], "peak_kind": f"{pk['source']} cuBLAS bf16, sustained",
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak,
+                         "peak_kind": f"{pk['source']} cuBLAS bf16, " + ("burst (timed region %.0f ms, no power cap seen)" % ms
+                                                                         if burst else "sustained (long or power-capped timed region)"),
                          "frac_of_burst_peak": achieved / pk["burst"],
+                         "frac_of_sustained_peak": achieved / pk["sustained"],
                          "frac_of_nominal_2250": achieved / 2250.0,
+                         "sustained": sustained,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu capture of this
                          # workload, summarised in profiles/gemm_fp16_8192.md)
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH},
         }
+        if extras:
+            line["multi_gpu"] = extras
         if world == 1:
-            use_all_host_threads()
-            rows = 2048
-            v, dt = time_oracle(rows)
-            line["cpu_baseline"] = {"value": v, "unit": "TFLOP/s", "cores": cpu_threads(), "kind": "port",
-                                    "sample": f"{rows} of {M} rows of A against all of B (full K, N): {dt:.1f} s of "
-                                              "the numpy/BLAS restatement of the reference's tile loop"}
+            line["cpu_baseline"] = interpreter_baseline()
+            line["cpu_baseline"]["port"] = port_baseline()
             if not args.no_extra:
-                line["configs"] = other_configs(torch, tb, dev)
+                cfgs = other_configs(torch, tb, dev)
+                line["configs"] = cfgs
+                line["roofline"]["per_config"] = per_config_roofline(cfgs, pk)
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
         dist.destroy_process_group()
 
 
+def per_config_roofline(cfgs, pk):
+    """achieved / peak / frac of the other four configurations (short L2-flushed timings, burst
+    regime).  16-bit configs against the measured cuBLAS burst peak; the e4m3 matmul against the
+    nominal dense fp8 figure (no measured fp8 peak exists); config 1 is launch-latency bound."""
+    def entry(key, peak, kind):
+        r = cfgs.get(key)
+        if not r:
+            return None
+        return {"achieved": r["tflops"], "peak": peak, "unit": "TFLOP/s", "frac": round(r["tflops"] / peak, 4),
+                "peak_kind": kind, "ms": r["ms"], "frac_of_nominal": round(r["tflops"] / (4500.0 if "fp8" in key else 2250.0), 4)}
+    meas = f"{pk['source']} cuBLAS bf16 burst"
+    return {
+        "c1": dict(entry("c1_matmul_fp16_512", pk["burst"], meas) or {}, note="0.27 GFLOP: launch-latency bound"),
+        "c3": entry("c3_matmul_fp8_8192_scaled_bf16", 4500.0, "nominal dense fp8 (no measured fp8 peak)"),
+        "c4": entry("c4_attn_fwd_causal_fp16_z4h32n4096d128", pk["burst"], meas),
+        "c5": entry("c5_attn_fwd_bwd_causal_bf16_z4h48n1024d64", pk["burst"], meas),
+        "c5_fwd": entry("c5_fwd_only", pk["burst"], meas),
+        "c5_bwd": entry("c5_bwd_only", pk["burst"], meas),
+        "c5_two_kernel_backward": entry("c5_fwd_bwd_two_kernel_backward", pk["burst"], meas),
+    }
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemm_kernel<256,256,3> launch on this workload
-# (879.5 MB + 120.0 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md); algorithmic: 402.7 MB
+# (879.5 MB + 120.0 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md, taken at commit
+# b57e099; the kernel's main loop and rasterisation have not changed since); algorithmic: 402.7 MB
 TRAFFIC_BYTES_PER_LAUNCH = 999_518_208
 
 
@@ -399,7 +604,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the short timings of configs 1, 3, 4, 5")
-    ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5", "fp8attn", "grouped", "skinny"],
+    ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5", "c5two", "fp8attn", "grouped", "skinny"],
                     help="run three launches of one configuration and exit (for ncu captures)")
     args = ap.parse_args()
     # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm and the cpu_baseline leg are meant to

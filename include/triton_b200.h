@@ -161,7 +161,10 @@ B200_API int b200_grouped_matmul_run(b200_stream_t stream, const void* workspace
  * python/tutorials/06-fused-attention.py:98-187, 441-475 (Q, K, V, sm_scale, M, Out, the four
  * stride quadruples, Z, H, N_CTX, HEAD_DIM, STAGE -> causal).
  * q, k, v, o: [Z, H, N, D] of `dtype` (F16 or BF16) with element strides {z, h, n, d} each; the d
- * stride must be 1 and the others multiples of 8 elements; D is 64 or 128; sm_scale > 0.
+ * stride must be 1 and the others multiples of 8 elements; D is 64, 128 or 256; sm_scale > 0.
+ * (The reference's set is {16, 32, 64, 128, 256}, 06-fused-attention.py:447: 16 and 32 are served by
+ * the host wrapper, which appends zero columns up to 64 - they change neither Q K^T nor the kept
+ * columns of O.)
  * m: contiguous [Z, H, N] fp32.
  * dtype E5M2 is the reference's 8-bit forward (06-fused-attention.py:38-40, 66-69, 127, 609-615):
  * q, k, v and o are e5m2, both products run on 8-bit MMAs, P is converted to e5m2 (round to
@@ -202,6 +205,46 @@ B200_API int b200_attention_bwd(b200_stream_t stream, const void* q, const void*
                                 const int64_t stride_v[4], const int64_t stride_o[4], const int64_t stride_do[4],
                                 const int64_t stride_dq[4], const int64_t stride_dk[4], const int64_t stride_dv[4],
                                 float sm_scale, int causal, int dtype);
+
+/* The backward at head dim 64 in one pass: same results as b200_attention_bwd up to the rounding of
+ * dQ described below, about 1.6x faster.  b200_attention_bwd runs two kernels (dK/dV per K/V block,
+ * dQ per Q block, the reference's layout, 06-fused-attention.py:308-435) and each recomputes the
+ * scores, the exponentials and dS; here one kernel walks the (K/V block, Q block) pairs once,
+ * accumulates dK and dV as before and adds every 128 x 64 partial of dQ into `dq_accum` - fp32
+ * [Z, H, N, 64], b200_attention_bwd_onepass_workspace(Z, H, N, D) bytes of caller scratch, 16-byte
+ * aligned, cleared by the call - with TMA reduce-adds; a last kernel scales the sums by sm_scale and
+ * rounds them into dq.  This is the reference's older `sequence_parallel` backward
+ * (python/test/regression/test_performance.py:174, 194: partial dQ per K/V block, summed
+ * afterwards).  The partials of one Q block arrive in no fixed order, so the last bit of dQ may
+ * differ from run to run (dK, dV are deterministic); callers that need bitwise repeatability use
+ * b200_attention_bwd.  D must be 64 (B200_ERR_UNSUPPORTED otherwise, also for dK / dV / dQ layouts
+ * that TMA cannot address); all other arguments as for b200_attention_bwd. */
+B200_API size_t b200_attention_bwd_onepass_workspace(int Z, int H, int N, int D);
+B200_API int b200_attention_bwd_onepass(b200_stream_t stream, const void* q, const void* k, const void* v,
+                                        const void* o, const void* d_o, const float* m, float* delta,
+                                        float* dq_accum, void* dq, void* dk, void* dv, int Z, int H, int N, int D,
+                                        const int64_t stride_q[4], const int64_t stride_k[4],
+                                        const int64_t stride_v[4], const int64_t stride_o[4],
+                                        const int64_t stride_do[4], const int64_t stride_dq[4],
+                                        const int64_t stride_dk[4], const int64_t stride_dv[4], float sm_scale,
+                                        int causal, int dtype);
+
+/* b200_attention_bwd for every head dim of the reference's set, 256 included (06-fused-attention.py:447).
+ * The fused backward kernels hold four 128 x D operand tiles in shared memory, which fits for D = 64
+ * and 128.  At D = 256 the same arithmetic (same roundings of P and dS to the storage type) is laid
+ * out per (batch, head) as matmuls of this library - S = Q K^T and dP = dO V^T into fp32 [N, N], one
+ * element-wise pass for P and dS, then dV = P^T dO, dK = sm_scale dS^T Q, dQ = sm_scale dS K - and
+ * needs `workspace`: b200_attention_bwd_wide_workspace(N) bytes (12 N^2 + 256) of caller-owned device
+ * memory, 256-byte aligned, reused head after head.  Other head dims ignore the workspace and run the
+ * fused kernels.  All tensors 16-byte aligned, strides multiples of 8 elements. */
+B200_API size_t b200_attention_bwd_wide_workspace(int N);
+B200_API int b200_attention_bwd_wide(b200_stream_t stream, const void* q, const void* k, const void* v, const void* o,
+                                     const void* d_o, const float* m, float* delta, void* dq, void* dk, void* dv,
+                                     int Z, int H, int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
+                                     const int64_t stride_v[4], const int64_t stride_o[4],
+                                     const int64_t stride_do[4], const int64_t stride_dq[4],
+                                     const int64_t stride_dk[4], const int64_t stride_dv[4], float sm_scale,
+                                     int causal, int dtype, void* workspace);
 
 /* Same computation as b200_attention_bwd, for callers that may not allocate device memory.
  * (No counterpart in the reference, whose Python wrapper allocates `delta` with torch.empty_like.)

@@ -85,7 +85,7 @@ def test_old_style_attention_against_its_interpreter_fixture(golden, name):
 
 
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
-@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("D", [64, 128, 256])
 @pytest.mark.parametrize("N", [128, 200, 384, 1000])
 @pytest.mark.parametrize("causal", [True, False])
 def test_forward_ragged_lengths(dtype, D, N, causal):
@@ -148,6 +148,58 @@ def test_forward_scores_far_above_the_first_block(dtype, D, causal, where):
 
 
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("shape", [(1, 2, 256), (2, 3, 1024), (1, 1, 128)])
+def test_one_pass_backward(dtype, causal, shape):
+    """The head-dim-64 backward in one pass (partial dQ per K/V block added into an fp32 buffer, the
+    layout of the reference's `sequence_parallel` mode, test_performance.py:174, 194) against the
+    oracle at the backward's tolerances, and against the two-kernel path: dK and dV are the same
+    arithmetic in the same order and must be the same bits; dQ is a sum of the same partial products
+    in another order (fp32), so it may differ by a rounding of the storage type."""
+    Z, H, N = shape
+    c = dict(Z=Z, H=H, N=N, D=64, dtype=dtype, seed=6400 + N + causal)
+    q, k, v, do = cases.attn_inputs(c)
+    sm_scale = 0.5
+    qd, kd, vd, dod = (t.to(DEV) for t in (q, k, v, do))
+    o, M = triton_b200.attention_forward(qd, kd, vd, causal, sm_scale)
+    two = triton_b200.attention_backward(qd, kd, vd, o, M, dod, causal, sm_scale, one_pass=False)
+    one = triton_b200.attention_backward(qd, kd, vd, o, M, dod, causal, sm_scale, one_pass=True)
+    status_ok()
+    assert torch.equal(one[1], two[1]) and torch.equal(one[2], two[2]), "dK / dV differ from the two-kernel path"
+    tol = 1e-2 if dtype == "fp16" else 2e-2
+    np.testing.assert_allclose(f32(one[0]), f32(two[0]), rtol=1e-2, atol=tol)
+    ro, rM = R.attention_fwd(f32(q), f32(k), f32(v), causal, sm_scale, dtype)
+    if causal:
+        want = R.attention_bwd(f32(q), f32(k), f32(v), ro, f32(do), rM, sm_scale, dtype)
+    else:
+        want = R.attention_bwd_full(f32(q), f32(k), f32(v), ro, f32(do), rM, sm_scale, False, dtype)
+    for got, ref, name in zip(one, want, ("dq", "dk", "dv")):
+        np.testing.assert_allclose(f32(got), ref, rtol=1e-2, atol=tol, err_msg=name)
+    # through autograd with the reference's six-argument signature; twice, on a buffer that is not
+    # cleared by the caller: the call clears its own accumulator
+    qg, kg, vg = (t.clone().requires_grad_() for t in (qd, kd, vd))
+    triton_b200.attention(qg, kg, vg, causal, sm_scale, True).backward(dod)
+    assert torch.equal(kg.grad, two[1]) and torch.equal(vg.grad, two[2])
+    np.testing.assert_allclose(f32(qg.grad), f32(two[0]), rtol=1e-2, atol=tol)
+
+
+def test_one_pass_backward_head_dims_and_errors():
+    """Other head dims take the two-kernel path whatever the flag says; the C entry point itself refuses them."""
+    g = torch.Generator().manual_seed(9)
+    q, k, v, do = ((torch.randn(1, 2, 256, 128, generator=g) * 0.5).half().to(DEV) for _ in range(4))
+    o, M = triton_b200.attention_forward(q, k, v, True, 0.09)
+    a = triton_b200.attention_backward(q, k, v, o, M, do, True, 0.09, one_pass=True)
+    b = triton_b200.attention_backward(q, k, v, o, M, do, True, 0.09, one_pass=False)
+    assert all(torch.equal(x, y) for x, y in zip(a, b))
+    s4 = _lib.strides4
+    code = _lib.lib().b200_attention_bwd_onepass(None, *([q.data_ptr()] * 5), M.data_ptr(), M.data_ptr(), M.data_ptr(),
+                                                 *([q.data_ptr()] * 3), 1, 2, 256, 128, *([s4(q)] * 8), 0.09, 1, _lib.F16)
+    assert code == _lib.ERR_UNSUPPORTED and "head dim 64" in _lib.last_error()
+    assert _lib.lib().b200_attention_bwd_onepass_workspace(4, 48, 1024, 64) == 4 * 48 * 1024 * 64 * 4
+    status_ok()
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 @pytest.mark.parametrize("D", [64, 128])
 def test_backward_noncausal(dtype, D):
     c = dict(Z=2, H=2, N=384, D=D, dtype=dtype, seed=77 + D)
@@ -169,10 +221,36 @@ def test_strided_inputs_and_errors():
     o, M = triton_b200.attention_forward(q, k, v, True, 0.125)
     oc, Mc = triton_b200.attention_forward(q.contiguous(), k.contiguous(), v.contiguous(), True, 0.125)
     assert torch.equal(o, oc) and torch.equal(M, Mc)
-    with pytest.raises(RuntimeError, match="head dim"):
-        x = torch.zeros(1, 1, 128, 256, dtype=torch.float16, device=DEV)  # in the reference's set, no kernel here
-        triton_b200.attention_forward(x, x, x, True, 0.5)
+    with pytest.raises(RuntimeError, match="head dim 256"):  # the plain backward entry point names the one that takes scratch
+        x = torch.zeros(1, 1, 128, 256, dtype=torch.float16, device=DEV)
+        m = torch.zeros(1, 1, 128, dtype=torch.float32, device=DEV)
+        s4 = _lib.strides4
+        _lib.check(_lib.lib().b200_attention_bwd(
+            None, *([x.data_ptr()] * 5), m.data_ptr(), m.data_ptr(), *([x.data_ptr()] * 3), 1, 1, 128, 256,
+            *([s4(x)] * 8), 0.5, 1, _lib.F16), "attention_bwd")
     status_ok()
+
+
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+@pytest.mark.parametrize("causal", [True, False])
+def test_head_dim_256_forward_and_backward(dtype, causal):
+    """Head dim 256, the largest of the reference's set (06-fused-attention.py:447): the forward runs one
+    128-row tile per work item (the accumulator alone takes half of TMEM); the backward is laid out as
+    matmuls with [N, N] scratch.  Both against the oracle, same tolerances as the other head dims."""
+    c = dict(Z=2, H=2, N=384, D=256, dtype=dtype, seed=2560 + causal)
+    q, k, v, do = cases.attn_inputs(c)
+    sm_scale = 256 ** -0.5
+    got = run_gpu(q, k, v, do, causal, sm_scale, True)
+    o, M = R.attention_fwd(f32(q), f32(k), f32(v), causal, sm_scale, dtype)
+    np.testing.assert_allclose(got["o"], o, rtol=1e-2, atol=1e-2)
+    np.testing.assert_allclose(got["m"], M, rtol=1e-4, atol=1e-3)
+    if causal:
+        dq, dk, dv = R.attention_bwd(f32(q), f32(k), f32(v), o, f32(do), M, sm_scale, dtype)
+    else:
+        dq, dk, dv = R.attention_bwd_full(f32(q), f32(k), f32(v), o, f32(do), M, sm_scale, False, dtype)
+    tol = 1e-2 if dtype == "fp16" else 2e-2
+    for key, want in (("dq", dq), ("dk", dk), ("dv", dv)):
+        np.testing.assert_allclose(got[key], want, rtol=1e-2, atol=tol, err_msg=key)
 
 
 @pytest.mark.parametrize("pad", [4, 8])
@@ -258,16 +336,19 @@ def test_config5_full_size_forward_backward():
 
 @pytest.mark.skipif(not hasattr(torch, "float8_e5m2"), reason="torch without float8_e5m2")
 @pytest.mark.parametrize("causal", [True, False])
-@pytest.mark.parametrize("N,sm_scale", [(512, 0.0884), (208, 0.0884), (1024, 1.3), (2048, 1.3)])
-def test_forward_e5m2(causal, N, sm_scale):
+@pytest.mark.parametrize("N,sm_scale,D", [(512, 0.0884, 128), (208, 0.0884, 128), (1024, 1.3, 128), (2048, 1.3, 128),
+                                          (1024, 1.3, 64), (384, 0.125, 64)])
+def test_forward_e5m2(causal, N, sm_scale, D):
     """The reference's 8-bit forward (06-fused-attention.py:66-69, 609-615): e5m2 q, k, v (v with
     the key dimension contiguous), P converted to e5m2, e5m2 output.  The reference has no test for
     it; the check is the oracle's restatement run with BLOCK_N = 128 (one of the reference's
     autotune choices; the 2-bit mantissa of P makes the result depend on the block-wise running
     maximum, i.e. on BLOCK_N): relative Frobenius error <= 2e-2, in fact all but a few elements in
-    a million are bit-identical.  Both are also compared with exact fp64 attention."""
-    Z, H, D = 1, 2, 128
-    g = torch.Generator().manual_seed(N + int(causal))
+    a million are bit-identical.  Both are also compared with exact fp64 attention.  Head dim 64 is
+    the shape of the reference's own fp8 benchmark (:570); it runs on the head-dim-128 kernel with
+    zero columns appended."""
+    Z, H = 1, 2
+    g = torch.Generator().manual_seed(N + int(causal) + D)
     q, k, v = ((torch.randn(Z, H, N, D, generator=g) * 0.5).to(torch.float8_e5m2) for _ in range(3))
     vd = v.to(DEV).permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)   # the reference's fp8 V layout
     o, M = triton_b200.attention_forward(q.to(DEV), k.to(DEV), vd, causal, sm_scale)
@@ -300,9 +381,15 @@ def test_forward_e5m2(causal, N, sm_scale):
 
 @pytest.mark.skipif(not hasattr(torch, "float8_e5m2"), reason="torch without float8_e5m2")
 def test_forward_e5m2_errors():
-    x = torch.zeros(1, 1, 128, 64, device=DEV).to(torch.float8_e5m2)
+    x = torch.zeros(1, 1, 128, 256, device=DEV).to(torch.float8_e5m2)
     with pytest.raises(AssertionError, match="head dim 128"):
         triton_b200.attention_forward(x, x, x, True, 0.5)
+    s4 = _lib.strides4
+    x64 = torch.zeros(1, 1, 128, 64, device=DEV).to(torch.float8_e5m2)
+    m = torch.zeros(1, 1, 128, device=DEV)
+    code = _lib.lib().b200_attention_fwd(None, *([x64.data_ptr()] * 4), m.data_ptr(), 1, 1, 128, 64, *([s4(x64)] * 4),
+                                         0.5, 1, _lib.E5M2)
+    assert code == _lib.ERR_UNSUPPORTED and "head dim 128" in _lib.last_error()  # the C entry point itself does not pad
 
 
 def test_long_sequence_forward_sampled_rows():

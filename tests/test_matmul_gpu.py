@@ -353,6 +353,15 @@ def test_host_matmul_pipeline_matches_device_matmul():
     for (ah, bh), ch in zip(ins, outs):
         want = triton_b200.matmul(ah.to(DEV), bh.to(DEV))
         np.testing.assert_allclose(f32(ch), f32(want), rtol=1e-2, atol=1e-2)
+    # an unchanged B is not sent again; one modified in place (same storage, new version) is
+    ah, bh = ins[-1]
+    hm.run(ah, bh, outs[0])
+    torch.cuda.synchronize()
+    assert torch.equal(outs[0], outs[-1])
+    bh.mul_(-1.0)
+    hm.run(ah, bh, outs[1])
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(f32(outs[1]), -f32(outs[-1]), rtol=0, atol=0)
     status_ok()
 
 

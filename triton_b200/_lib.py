@@ -37,6 +37,10 @@ SIGNATURES = {
     "b200_attention_fwd": [_p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
     "b200_attention_fwd_stats": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _s4, _s4, _s4, _s4, _f, _i, _i],
     "b200_attention_bwd": [_p] + [_p] * 10 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
+    "b200_attention_bwd_onepass": [_p] + [_p] * 11 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
+    "b200_attention_bwd_onepass_workspace": [_i, _i, _i, _i],
+    "b200_attention_bwd_wide": [_p] + [_p] * 10 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i, _p],
+    "b200_attention_bwd_wide_workspace": [_i],
     "b200_attention_bwd_noalloc": [_p] + [_p] * 9 + [_i, _i, _i, _i] + [_s4] * 8 + [_f, _i, _i],
     "b200_attention_bwd_noalloc_capacity": [],
 }

@@ -531,6 +531,22 @@ attn_bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict
   }
 }
 
+template <int D, bool BF16>
+int launch_delta_t(DeviceCtx* ctx, cudaStream_t stream, const void* o, const void* dout, float* delta, const int64_t* so,
+                   const int64_t* sdo, int Z, int H, int N) {
+  const long long rows = (long long)Z * H * N;
+  if (rows >= (1ll << 32)) return fail(B200_ERR_UNSUPPORTED, "more than 2^32 rows");
+  const long long rows_per_block = (256 / (D / 8)) * 4;
+  long long blocks = (rows + rows_per_block - 1) / rows_per_block;
+  if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
+  attn_bwd_delta_kernel<D, BF16><<<(unsigned)blocks, 256, 0, stream>>>(
+      reinterpret_cast<const uint16_t*>(o), reinterpret_cast<const uint16_t*>(dout), delta, so[0], so[1], so[2],
+      sdo[0], sdo[1], sdo[2], (unsigned)H, (unsigned)N, (unsigned)rows);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd delta launch: %s", cudaGetErrorString(e));
+  return B200_OK;
+}
+
 template <int D, bool BF16, bool DQ>
 int launch_bwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& r1, const CUtensorMap& r2,
                  const CUtensorMap& u1, const CUtensorMap& u2, const CUtensorMap& oa, const CUtensorMap& ob,
@@ -554,16 +570,7 @@ int launch_bwd_all(DeviceCtx* ctx, cudaStream_t stream, const void* o, const voi
                    const int64_t* so, const int64_t* sdo, const CUtensorMap& tq, const CUtensorMap& tk,
                    const CUtensorMap& tv, const CUtensorMap& tdo, BwdParams p, void* dq, void* dk, void* dv,
                    const int64_t* sdq, const int64_t* sdk, const int64_t* sdv) {
-  const long long rows = (long long)p.Z * p.H * p.N;
-  if (rows >= (1ll << 32)) return fail(B200_ERR_UNSUPPORTED, "more than 2^32 rows");
-  const long long rows_per_block = (256 / (D / 8)) * 4;
-  long long blocks = (rows + rows_per_block - 1) / rows_per_block;
-  if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
-  attn_bwd_delta_kernel<D, BF16><<<(unsigned)blocks, 256, 0, stream>>>(
-      reinterpret_cast<const uint16_t*>(o), reinterpret_cast<const uint16_t*>(dout), delta, so[0], so[1], so[2],
-      sdo[0], sdo[1], sdo[2], (unsigned)p.H, (unsigned)p.N, (unsigned)rows);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd delta launch: %s", cudaGetErrorString(e));
+  if (int rc = launch_delta_t<D, BF16>(ctx, stream, o, dout, delta, so, sdo, p.Z, p.H, p.N)) return rc;
   p.delta = delta;
   // gradients through TMA stores (boxes of 32 rows x 32 columns) when all three layouts allow
   CUtensorMap mdq, mdk, mdv;
@@ -584,6 +591,21 @@ int launch_bwd_all(DeviceCtx* ctx, cudaStream_t stream, const void* o, const voi
 }
 
 }  // namespace
+
+// delta = rowsum(O * dO) for any head dim of the library (the pre-pass on its own)
+int launch_attn_bwd_delta(DeviceCtx* ctx, cudaStream_t stream, const void* o, const void* dout, float* delta, int Z,
+                          int H, int N, int D, const int64_t* so, const int64_t* sdo, int dtype) {
+  const bool bf16 = dtype == B200_BF16;
+  switch (D) {
+    case 64: return bf16 ? launch_delta_t<64, true>(ctx, stream, o, dout, delta, so, sdo, Z, H, N)
+                         : launch_delta_t<64, false>(ctx, stream, o, dout, delta, so, sdo, Z, H, N);
+    case 128: return bf16 ? launch_delta_t<128, true>(ctx, stream, o, dout, delta, so, sdo, Z, H, N)
+                          : launch_delta_t<128, false>(ctx, stream, o, dout, delta, so, sdo, Z, H, N);
+    case 256: return bf16 ? launch_delta_t<256, true>(ctx, stream, o, dout, delta, so, sdo, Z, H, N)
+                          : launch_delta_t<256, false>(ctx, stream, o, dout, delta, so, sdo, Z, H, N);
+    default: return fail(B200_ERR_UNSUPPORTED, "head dim %d", D);
+  }
+}
 
 // ---------------------------------------------------------------------------------------------
 // Built-in scratch for b200_attention_bwd_noalloc: the delta vector lives in this fixed device

@@ -7,7 +7,8 @@
 // and M = m + log2(l) per row (:183-187).  Masked scores contribute exactly 0.
 //
 // One CTA owns 256 query rows of one (batch, head): two 128-row tiles that ping-pong so that the
-// tensor pipe works on one tile while the other tile's softmax runs.
+// tensor pipe works on one tile while the other tile's softmax runs (one 128-row tile at head dim
+// 256, where a tile's accumulator alone takes half of TMEM).  Sixteen warps:
 //   warps 0-3 / 4-7   softmax of tile 0 / 1, one thread per query row (no cross-thread reduction):
 //                     tcgen05.ld S, running max and sum, exp2, P packed to 16 bit and written back over S in TMEM
 //                     (tcgen05.st) as the A operand of the second MMA.  The accumulator O is
@@ -19,12 +20,16 @@
 //                     O_i += P_i V_j (P from TMEM, V from shared memory, N-major).  MMAs of one
 //                     thread execute in issue order, which is what lets P alias S.
 //   warp 9            TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
+//   warps 10-15       lend their registers: the CTA's 64K registers are re-divided at run time
+//                     (setmaxnreg) so that a softmax thread can hold a whole 128-column score row
+//                     without spilling (208 registers; with ten warps the limit was 168 and the
+//                     row spilled to local memory, an L2 round trip per value).
 // The kernel is persistent: one CTA per SM takes work items (256 query rows of one head) from an
 // atomic counter, head-major and heavy-first, so a head's K/V stay in L2, causal work balances, and
 // the epilogue of one item overlaps the loads and first MMAs of the next.
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [384,384+D); P_i = first 64 columns of S_i
 // at head dim 128, and columns [320,384) / [448,512) at head dim 64 (16-bit), where S_i of the next
-// block is then issued before P_i V of this one.
+// block is then issued before P_i V of this one.  Head dim 256: S [0,128), O [256,512).
 #include <cmath>
 #include <cstdlib>
 
@@ -38,6 +43,9 @@ namespace {
 
 constexpr int BLK = 128;           // rows of a Q tile and of a K/V block
 constexpr int FWD_THREADS = 512;   // 8 softmax warps, MMA warp, TMA warp, 6 warps that only lend their registers
+// registers per thread after the re-division; one warp of each warpgroup shares a scheduler's 16K
+// registers: (2 * 208 + 72 + 24) * 32 lanes = 16384
+constexpr int REGS_SOFTMAX = 208, REGS_MMA_TMA = 72, REGS_IDLE = 24;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdParams {
@@ -48,7 +56,7 @@ struct FwdParams {
   int Z, H, N;
   int causal;
   float scale_log2;  // sm_scale * log2(e)
-  int num_qb;        // 256-row query blocks per head
+  int num_qb;        // query blocks (one work item each: 256 rows, 128 at head dim 256) per head
   int total_items;   // num_qb * Z * H
   int* sched_counter;  // work counter of this launch: zero at launch, put back to zero by the last CTA
   int o_tma;           // O is written through shared-memory staging and TMA stores
@@ -61,10 +69,11 @@ struct FwdParams {
 template <int D, bool FP8 = false>
 struct FwdCfg {
   static constexpr int TILE_BYTES = BLK * D * (FP8 ? 1 : 2);   // one Q tile or one K / V block
-  static constexpr int KV_STAGES = (D == 128 && !FP8) ? 4 : 8;
+  static constexpr int TILES = (D == 256) ? 1 : 2;             // 128-row query tiles per work item
+  static constexpr int KV_STAGES = (D == 256) ? 2 : ((D == 128 && !FP8) ? 4 : 8);
   // tiles + barriers + TMEM slot + scheduler slots + alignment slack
   static constexpr int STG_BYTES = 32 * 128;  // epilogue staging of one softmax warp: 32 rows x 64 columns
-  static constexpr size_t SMEM = 2 * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + 8 * STG_BYTES + (2 * KV_STAGES + 22) * 8 + 32 + 1024;
+  static constexpr size_t SMEM = (size_t)TILES * TILE_BYTES + (size_t)KV_STAGES * TILE_BYTES + 4 * TILES * STG_BYTES + (2 * KV_STAGES + 22) * 8 + 32 + 1024;
 };
 
 // one Q tile or K / V block of 128 rows: boxes of 128 bytes x 128 rows.  `along_rows`: the 8-bit V,
@@ -81,11 +90,12 @@ __device__ __forceinline__ void load_tile(uint8_t* dst, const CUtensorMap* map, 
   }
 }
 
-// One work item = 256 query rows of one (batch, head).  Items are numbered head-major, heavy
+// One work item = TILES * 128 query rows of one (batch, head).  Items are numbered head-major, heavy
 // (late, long) query blocks first inside a head, and handed out through an atomic counter.
 struct Item {
-  int qb, zh, z, h, n0, n1;
+  int qb, zh, z, h, n0, n1, nmax;  // n_i: K/V blocks tile i visits; nmax: blocks the item streams
 };
+template <int TILES>
 __device__ __forceinline__ Item decode_item(const FwdParams& p, int w) {
   Item it;
   it.zh = w / p.num_qb;
@@ -94,8 +104,9 @@ __device__ __forceinline__ Item decode_item(const FwdParams& p, int w) {
   it.h = it.zh % p.H;
   const int nkv_all = (p.N + BLK - 1) / BLK;
   // K/V blocks per tile: up to and including the block that holds the tile's diagonal when causal
-  it.n0 = p.causal ? min(2 * it.qb + 1, nkv_all) : nkv_all;
-  it.n1 = p.causal ? min(2 * it.qb + 2, nkv_all) : nkv_all;  // n0 <= n1 <= n0 + 1
+  it.n0 = p.causal ? min(TILES * it.qb + 1, nkv_all) : nkv_all;
+  it.n1 = (TILES == 2) ? (p.causal ? min(2 * it.qb + 2, nkv_all) : nkv_all) : 0;  // n0 <= n1 <= n0 + 1 with two tiles
+  it.nmax = (TILES == 2) ? it.n1 : it.n0;
   return it;
 }
 
@@ -105,16 +116,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                 const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o_map,
                 const FwdParams p) {
   using Cfg = FwdCfg<D, FP8>;
-  constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES;
+  constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES, TILES = Cfg::TILES;
+  constexpr int ITEM_ROWS = TILES * BLK;
   constexpr int MMA_WARP = 8, TMA_WARP = 9;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
-  uint8_t* sq = smem;                // Q tiles 0, 1
-  uint8_t* skv = smem + 2 * TILE;    // ring
-  uint8_t* sstage = skv + NST * TILE;  // 8 x 4 KiB, 128-byte swizzled
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sstage + 8 * Cfg::STG_BYTES);
+  uint8_t* sq = smem;                    // Q tiles
+  uint8_t* skv = smem + TILES * TILE;    // ring
+  uint8_t* sstage = skv + NST * TILE;  // one 4 KiB buffer per softmax warp, 128-byte swizzled
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sstage + 4 * TILES * Cfg::STG_BYTES);
   uint64_t* q_full = bars;             // [2]
   uint64_t* kv_full = bars + 2;        // [NST]
   uint64_t* kv_empty = kv_full + NST;  // [NST]
@@ -142,7 +154,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&s_free[i], 4);  // one arrival per softmax warp of the tile
       mbar_init(&pv_done[i], 1);
       mbar_init(&sched_full[i], 1);
-      mbar_init(&sched_empty[i], 9);  // MMA warp + one lane of each softmax warp
+      mbar_init(&sched_empty[i], 1 + 4 * TILES);  // MMA warp + one lane of each softmax warp
     }
     mbar_init(q_empty, 1);
     for (int s = 0; s < NST; ++s) {
@@ -172,10 +184,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr bool SEP_P = (D == 64) && !FP8;
   auto tm_p = [&](int i) { return SEP_P ? tmem_base + (i ? 448u : 320u) : tm_s[i]; };
 
-  // Register budget: 512 threads start with 128 registers each.  A softmax thread holds a whole
-  // 128-column score row (and its packed probabilities) and needs about 200; the MMA and TMA
-  // warps need few, warps 10-15 none: they give theirs back and the softmax warpgroups take them.
-  // Per scheduler (one warp of every warpgroup): 208 + 208 + 72 + 24 = 512 registers per lane.
   // Every role ends with its own copy of the teardown and returns: no code is shared after the
   // register budgets have diverged (values live across a join would have to sit in registers that
   // every budget has).
@@ -189,16 +197,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       tmem_dealloc(tmem_base, 512);
     }
   };
-  if (warp >= 12) {
-    reg_dec<24>();  // nothing else: these warps only take part in the barriers at both ends of the kernel
+  if (warp >= 12 || (TILES == 1 && warp >= 4 && warp < 8)) {
+    // nothing else: these warps only lend registers and take part in the barriers at both ends
+    // (at head dim 256 the second tile's softmax warpgroup has no tile)
+    reg_dec<REGS_IDLE>();
     teardown(false);
     return;
   } else if (warp >= 10) {
-    reg_dec<72>();
+    reg_dec<REGS_MMA_TMA>();
     teardown(false);
     return;
   } else if (warp == TMA_WARP) {
-    reg_dec<72>();
+    reg_dec<REGS_MMA_TMA>();
     // ------------------------------------------------------------------ scheduler + TMA producer
     if (lane == 0) {
       uint32_t s = 0, ph = 0;  // K/V ring position, runs on across items
@@ -212,13 +222,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // next launch that is handed this counter
         if (w == p.total_items + (int)gridDim.x - 1) atomicExch(p.sched_counter, 0);
         if (w >= p.total_items) break;
-        const Item it = decode_item(p, w);
+        const Item it = decode_item<TILES>(p, w);
         mbar_wait(q_empty, (n & 1u) ^ 1u, p.status, SITE_FWD_Q);  // previous item's S MMAs are done with Q
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < TILES; ++i) {
           mbar_expect_tx(&q_full[i], TILE);
-          load_tile<D, FP8>(sq + i * TILE, &tm_q, &q_full[i], it.qb * 256 + i * BLK, it.h, it.z);
+          load_tile<D, FP8>(sq + i * TILE, &tm_q, &q_full[i], it.qb * ITEM_ROWS + i * BLK, it.h, it.z);
         }
-        for (int j = 0; j < it.n1; ++j) {
+        for (int j = 0; j < it.nmax; ++j) {
           for (int kv = 0; kv < 2; ++kv) {  // K_j then V_j
             mbar_wait(&kv_empty[s], ph ^ 1u, p.status, SITE_FWD_KV_EMPTY);
             mbar_expect_tx(&kv_full[s], TILE);
@@ -232,7 +242,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     teardown(false);
     return;
   } else if (warp == MMA_WARP) {
-    reg_dec<72>();
+    reg_dec<REGS_MMA_TMA>();
     // ------------------------------------------------------------------ MMA issuer
     // The warp stays converged and an elected lane issues, for both tiles.  (Two issuing threads,
     // one per tile, were measured 20 % slower: MMAs of different threads interleave in the pipe
@@ -293,23 +303,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(&sched_empty[slot]);
         if (w >= p.total_items) break;
-        const Item it = decode_item(p, w);
-        const int n0 = it.n0, n1 = it.n1;
+        const Item it = decode_item<TILES>(p, w);
+        const int n0 = it.n0, n1 = it.n1, nmax = it.nmax;
 
         // prologue: S_0(0), S_1(0) on K_0
         mbar_wait(&kv_full[s], ph, p.status, SITE_FWD_KV_FULL);
         mbar_wait(&q_full[0], n & 1u, p.status, SITE_FWD_Q);
         issue_s(0, s);
-        mbar_wait(&q_full[1], n & 1u, p.status, SITE_FWD_Q);
-        issue_s(1, s);
+        if constexpr (TILES == 2) {
+          mbar_wait(&q_full[1], n & 1u, p.status, SITE_FWD_Q);
+          issue_s(1, s);
+        }
         tc_commit_elect(&kv_empty[s]);
-        if (n1 == 1) tc_commit_elect(q_empty);
+        if (nmax == 1) tc_commit_elect(q_empty);
         advance();
-        for (int j = 0; j < n1; ++j) {
+        for (int j = 0; j < nmax; ++j) {
           const uint32_t vs = s, vph = ph;  // V_j
           advance();
           const uint32_t ks = s, kph = ph;  // K_{j+1} (if any)
-          const bool more1 = (j + 1 < n1), more0 = (j + 1 < n0);
+          const bool more1 = (TILES == 2) && (j + 1 < n1), more0 = (j + 1 < n0);
           if constexpr (SEP_P) {
             // the next scores first: S_i(j+1) only needs the S buffer, which is free once the
             // softmax warps have loaded S_i(j)
@@ -345,27 +357,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (j == n1 - 1) tc_commit_elect(&o_full[1]);
             if (more1) advance();
           } else {
-          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
-          mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
-          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x60);
-          if (j < n0) {
-            issue_pv(0, vs, j > 0, pcnt[0]++ & 1u);
-            if (j == n0 - 1) tc_commit_elect(&o_full[0]);
-            if (more0) {
-              mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
-              issue_s(0, ks);
+            if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
+            mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
+            if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x60);
+            if (j < n0) {
+              issue_pv(0, vs, j > 0, pcnt[0]++ & 1u);
+              if (TILES == 1) tc_commit_elect(&kv_empty[vs]);
+              if (j == n0 - 1) tc_commit_elect(&o_full[0]);
+              if (more0) {
+                mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+                issue_s(0, ks);
+                if (TILES == 1) {
+                  tc_commit_elect(&kv_empty[ks]);
+                  if (j + 2 == n0) tc_commit_elect(q_empty);
+                  advance();
+                }
+              }
             }
-          }
-          issue_pv(1, vs, j > 0, pcnt[1]++ & 1u);
-          tc_commit_elect(&kv_empty[vs]);
-          if (j == n1 - 1) tc_commit_elect(&o_full[1]);
-          if (more1) {
-            mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
-            issue_s(1, ks);
-            tc_commit_elect(&kv_empty[ks]);
-            if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
-            advance();
-          }
+            if constexpr (TILES == 2) {
+              issue_pv(1, vs, j > 0, pcnt[1]++ & 1u);
+              tc_commit_elect(&kv_empty[vs]);
+              if (j == n1 - 1) tc_commit_elect(&o_full[1]);
+              if (more1) {
+                mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+                issue_s(1, ks);
+                tc_commit_elect(&kv_empty[ks]);
+                if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
+                advance();
+              }
+            }
           }
         }
       }
@@ -374,7 +394,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     teardown(true);
     return;
   } else {
-    reg_inc<208>();
+    reg_inc<REGS_SOFTMAX>();
     // ------------------------------------------------------------------ softmax + epilogue
     // 4 warps per tile, one thread per query row.
     const int i = warp >> 2;                 // tile
@@ -396,9 +416,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       w = __shfl_sync(0xffffffffu, w, 0);
       if (w >= p.total_items) break;
-      const Item it = decode_item(p, w);
+      const Item it = decode_item<TILES>(p, w);
       const int qb = it.qb;
-      const int row = qb * 256 + i * BLK + row_in_tile;  // query index
+      const int row = qb * ITEM_ROWS + i * BLK + row_in_tile;  // query index
       const int nb = i ? it.n1 : it.n0;
       float m_ref = -INFINITY, l = 0.f;
       float m_true = -INFINITY;  // the exact running maximum (m_ref lags it by up to the rescale threshold)
@@ -410,7 +430,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (traced) B200_TRACE_EVENT(p.status, i, 1);
         tc_fence_after();
         const int col0 = j * BLK;
-        const bool need_mask = (p.causal && col0 + BLK - 1 > qb * 256 + i * BLK) || (col0 + BLK > p.N);
+        const bool need_mask = (p.causal && col0 + BLK - 1 > qb * ITEM_ROWS + i * BLK) || (col0 + BLK > p.N);
         // load 32 columns at a time; the row maximum of a chunk is taken while the next chunk loads
         uint32_t r[BLK];
         float mx4[16];
@@ -550,7 +570,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // store of one row per lane touches 32 lines per instruction and made this epilogue cost
         // 5200 clk per item at D = 128.
         uint8_t* stg = sstage + warp * Cfg::STG_BYTES;
-        const int warp_row0 = qb * 256 + i * BLK + quarter * 32;
+        const int warp_row0 = qb * ITEM_ROWS + i * BLK + quarter * 32;
         if constexpr (FP8) {
           // 8-bit O: the 128 columns of a row are one 128-byte line of the staging buffer
           if (lane == 0) tma_store_wait_read<0>();
@@ -716,15 +736,17 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
   p.o_sz = so[0]; p.o_sh = so[1]; p.o_sn = so[2];
   p.Z = Z; p.H = H; p.N = N; p.causal = causal;
   p.scale_log2 = sm_scale * 1.44269504f;  // the reference's constant (06-fused-attention.py:161)
-  p.num_qb = (N + 255) / 256;
+  const int item_rows = (D == 256) ? BLK : 2 * BLK;  // one 128-row tile per work item at head dim 256, two otherwise
+  p.num_qb = (N + item_rows - 1) / item_rows;
   p.total_items = p.num_qb * Z * H;
   p.status = ctx->status;
   p.sched_counter = next_sched_counter(ctx, stream);
   if (!p.sched_counter) return B200_ERR_CUDA;
   const bool bf16 = dtype == B200_BF16;
+  if (D == 256) return bf16 ? launch_fwd_t<256, true>(ctx, stream, tq, tk, tv, to, p) : launch_fwd_t<256, false>(ctx, stream, tq, tk, tv, to, p);
   if (D == 128) return bf16 ? launch_fwd_t<128, true>(ctx, stream, tq, tk, tv, to, p) : launch_fwd_t<128, false>(ctx, stream, tq, tk, tv, to, p);
   if (D == 64) return bf16 ? launch_fwd_t<64, true>(ctx, stream, tq, tk, tv, to, p) : launch_fwd_t<64, false>(ctx, stream, tq, tk, tv, to, p);
-  return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
+  return fail(B200_ERR_UNSUPPORTED, "head dim %d: the forward has kernels for 64, 128 and 256", D);
 }
 
 }  // namespace tb

@@ -462,7 +462,9 @@ int b200_attention_fwd_stats(b200_stream_t stream, const void* q, const void* k,
   if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
   if (dtype != B200_F16 && dtype != B200_BF16 && dtype != B200_E5M2)
     return fail(B200_ERR_ARG, "forward attention dtype must be F16, BF16 or E5M2");
-  if (D != 64 && D != 128) return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
+  if (D != 64 && D != 128 && D != 256)
+    return fail(B200_ERR_UNSUPPORTED, "head dim %d: the forward has kernels for 64, 128 and 256", D);
+  if (D == 256 && dtype == B200_E5M2) return fail(B200_ERR_UNSUPPORTED, "the 8-bit forward has a kernel for head dim 128 only");
   if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
   if (!stride_q || !stride_k || !stride_v || !stride_o) return fail(B200_ERR_ARG, "null stride array");
   if (dtype != B200_E5M2 && (stride_q[3] != 1 || stride_k[3] != 1 || stride_v[3] != 1 || stride_o[3] != 1))
@@ -490,7 +492,11 @@ int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const
                        const int64_t stride_dk[4], const int64_t stride_dv[4], float sm_scale, int causal, int dtype) {
   if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
   if (dtype != B200_F16 && dtype != B200_BF16) return fail(B200_ERR_ARG, "attention dtype must be F16 or BF16");
-  if (D != 64 && D != 128) return fail(B200_ERR_UNSUPPORTED, "head dim %d: this library has kernels for 64 and 128", D);
+  if (D == 256)
+    return fail(B200_ERR_UNSUPPORTED,
+                "head dim 256: the backward needs [N, N] scratch at this head dim; call b200_attention_bwd_wide with a "
+                "workspace of b200_attention_bwd_wide_workspace(N) bytes");
+  if (D != 64 && D != 128) return fail(B200_ERR_UNSUPPORTED, "head dim %d: the backward has kernels for 64, 128 and (b200_attention_bwd_wide) 256", D);
   if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
   if (N % 128 != 0) return fail(B200_ERR_ARG, "backward needs N to be a multiple of 128 (N = %d)", N);
   const int64_t* all[8] = {stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk, stride_dv};
@@ -508,6 +514,79 @@ int b200_attention_bwd(b200_stream_t stream, const void* q, const void* k, const
   return launch_attn_bwd(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, d_o, m, delta, dq, dk, dv, Z, H, N, D,
                          stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk, stride_dv, sm_scale,
                          causal, dtype);
+}
+
+size_t b200_attention_bwd_onepass_workspace(int Z, int H, int N, int D) {
+  return (Z > 0 && H > 0 && N > 0 && D > 0) ? attn_bwd_fused_workspace_bytes(Z, H, N, D) : 0;
+}
+
+int b200_attention_bwd_onepass(b200_stream_t stream, const void* q, const void* k, const void* v, const void* o,
+                               const void* d_o, const float* m, float* delta, float* dq_accum, void* dq, void* dk,
+                               void* dv, int Z, int H, int N, int D, const int64_t stride_q[4],
+                               const int64_t stride_k[4], const int64_t stride_v[4], const int64_t stride_o[4],
+                               const int64_t stride_do[4], const int64_t stride_dq[4], const int64_t stride_dk[4],
+                               const int64_t stride_dv[4], float sm_scale, int causal, int dtype) {
+  if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
+  if (dtype != B200_F16 && dtype != B200_BF16) return fail(B200_ERR_ARG, "attention dtype must be F16 or BF16");
+  if (D != 64) return fail(B200_ERR_UNSUPPORTED, "the one-pass backward has a kernel for head dim 64 only (head dim %d)", D);
+  if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
+  if (N % 128 != 0) return fail(B200_ERR_ARG, "backward needs N to be a multiple of 128 (N = %d)", N);
+  const int64_t* all[8] = {stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk, stride_dv};
+  for (const int64_t* st : all) {
+    if (!st) return fail(B200_ERR_ARG, "null stride array");
+    if (st[3] != 1) return fail(B200_ERR_UNSUPPORTED, "the head dimension must be contiguous");
+  }
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
+  if (Z == 0 || H == 0 || N == 0) return B200_OK;
+  if (!q || !k || !v || !o || !d_o || !m || !delta || !dq_accum || !dq || !dk || !dv) return fail(B200_ERR_ARG, "null pointer");
+  if ((long long)Z * H * (N / 128) > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "too many work items");
+  for (const int64_t* s : {stride_o, stride_do})
+    if ((s[0] & 7) || (s[1] & 7) || (s[2] & 7)) return fail(B200_ERR_UNSUPPORTED, "O / dO strides must be multiples of 8 elements");
+  if ((reinterpret_cast<uintptr_t>(o) & 15) || (reinterpret_cast<uintptr_t>(d_o) & 15))
+    return fail(B200_ERR_UNSUPPORTED, "O / dO must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(delta) & 15) ||
+      (reinterpret_cast<uintptr_t>(dq_accum) & 15))
+    return fail(B200_ERR_UNSUPPORTED, "m, delta and dq_accum must be 16-byte aligned");
+  return launch_attn_bwd_fused(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, d_o, m, delta, dq_accum, dq, dk, dv,
+                               Z, H, N, D, stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk,
+                               stride_dv, sm_scale, causal, dtype);
+}
+
+size_t b200_attention_bwd_wide_workspace(int N) { return N > 0 ? attn_bwd_wide_workspace_bytes(N) : 0; }
+
+int b200_attention_bwd_wide(b200_stream_t stream, const void* q, const void* k, const void* v, const void* o,
+                            const void* d_o, const float* m, float* delta, void* dq, void* dk, void* dv, int Z, int H,
+                            int N, int D, const int64_t stride_q[4], const int64_t stride_k[4],
+                            const int64_t stride_v[4], const int64_t stride_o[4], const int64_t stride_do[4],
+                            const int64_t stride_dq[4], const int64_t stride_dk[4], const int64_t stride_dv[4],
+                            float sm_scale, int causal, int dtype, void* workspace) {
+  if (D != 256)  // the fused kernels serve the other head dims; same arguments minus the workspace
+    return b200_attention_bwd(stream, q, k, v, o, d_o, m, delta, dq, dk, dv, Z, H, N, D, stride_q, stride_k, stride_v,
+                              stride_o, stride_do, stride_dq, stride_dk, stride_dv, sm_scale, causal, dtype);
+  if (Z < 0 || H < 0 || N < 0) return fail(B200_ERR_ARG, "negative dimension");
+  if (dtype != B200_F16 && dtype != B200_BF16) return fail(B200_ERR_ARG, "attention dtype must be F16 or BF16");
+  if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
+  if (N % 128 != 0) return fail(B200_ERR_ARG, "backward needs N to be a multiple of 128 (N = %d)", N);
+  const int64_t* all[8] = {stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk, stride_dv};
+  for (const int64_t* st : all) {
+    if (!st) return fail(B200_ERR_ARG, "null stride array");
+    if (st[3] != 1) return fail(B200_ERR_UNSUPPORTED, "the head dimension must be contiguous");
+    if ((st[0] & 7) || (st[1] & 7) || (st[2] & 7)) return fail(B200_ERR_UNSUPPORTED, "strides must be multiples of 8 elements");
+  }
+  DeviceCtx* ctx = ready_ctx();
+  if (!ctx) return g_err_code;
+  if (Z == 0 || H == 0 || N == 0) return B200_OK;
+  if (!q || !k || !v || !o || !d_o || !m || !delta || !dq || !dk || !dv) return fail(B200_ERR_ARG, "null pointer");
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return fail(B200_ERR_ARG, "head dim 256 needs a 256-byte aligned workspace of b200_attention_bwd_wide_workspace(N) bytes");
+  for (const void* ptr : {q, k, v, o, d_o, (const void*)dq, (const void*)dk, (const void*)dv})
+    if (reinterpret_cast<uintptr_t>(ptr) & 15) return fail(B200_ERR_UNSUPPORTED, "tensors must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(m) & 15) || (reinterpret_cast<uintptr_t>(delta) & 15))
+    return fail(B200_ERR_UNSUPPORTED, "m and delta must be 16-byte aligned");
+  return launch_attn_bwd_wide(ctx, reinterpret_cast<cudaStream_t>(stream), q, k, v, o, d_o, m, delta, dq, dk, dv, Z, H, N,
+                              D, stride_q, stride_k, stride_v, stride_o, stride_do, stride_dq, stride_dk, stride_dv,
+                              sm_scale, causal, dtype, workspace);
 }
 
 long long b200_attention_bwd_noalloc_capacity(void) { return attn_bwd_scratch_capacity(); }

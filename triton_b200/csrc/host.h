@@ -91,6 +91,26 @@ int launch_attn_bwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
                     const int64_t* sdo, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv, float sm_scale,
                     int causal, int dtype);
 
+// the backward's pre-pass on its own: delta[z, h, n] = sum_d O * dO (head dims 64, 128, 256)
+int launch_attn_bwd_delta(DeviceCtx* ctx, cudaStream_t stream, const void* o, const void* dout, float* delta, int Z,
+                          int H, int N, int D, const int64_t* so, const int64_t* sdo, int dtype);
+
+// head dim 256 backward, composed of matmul launches per head (attn_bwd_wide.cu)
+size_t attn_bwd_wide_workspace_bytes(int N);
+int launch_attn_bwd_wide(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v,
+                         const void* o, const void* dout, const float* m, float* delta, void* dq, void* dk, void* dv,
+                         int Z, int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv,
+                         const int64_t* so, const int64_t* sdo, const int64_t* sdq, const int64_t* sdk,
+                         const int64_t* sdv, float sm_scale, int causal, int dtype, void* workspace);
+
+// head dim 64 backward in one pass (attn_bwd_fused.cu); dq_acc: Z*H*N*64 floats of caller scratch
+size_t attn_bwd_fused_workspace_bytes(int Z, int H, int N, int D);
+int launch_attn_bwd_fused(DeviceCtx* ctx, cudaStream_t stream, const void* q, const void* k, const void* v, const void* o,
+                          const void* dout, const float* m, float* delta, float* dq_acc, void* dq, void* dk, void* dv, int Z,
+                          int H, int N, int D, const int64_t* sq, const int64_t* sk, const int64_t* sv, const int64_t* so,
+                          const int64_t* sdo, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv, float sm_scale,
+                          int causal, int dtype);
+
 // built-in scratch of the no-allocation backward entry point (attn_bwd.cu)
 long long attn_bwd_scratch_capacity();
 float* attn_bwd_scratch(DeviceCtx* ctx);

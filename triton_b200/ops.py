@@ -250,9 +250,11 @@ def group_gemm_fn(group_A, group_B, out_dtype=None):
 
 class HostMatmul:
     """C = A @ B for operands that live in (pinned) host memory: the call a host-side user of the
-    matmul makes.  B goes to the device once per call; A is sent in row blocks and every block's
-    product is copied back while the next block is on its way, so the two directions of the link
-    and the tensor cores overlap (the product of a block takes a fraction of its transfer time).
+    matmul makes.  A is sent in row blocks and every block's product is copied back while the next
+    block is on its way, so the two directions of the link and the tensor cores overlap (the product
+    of a block takes a fraction of its transfer time).  B goes to the device when it is new: a call
+    that passes the same host tensor, unmodified since the previous call (same storage, same torch
+    version counter - the weights of a layer, say), reuses the copy already on the device.
     Device buffers and the two copy streams are kept by the object; `run` returns after enqueueing,
     the caller's current stream waits for the last copy-out."""
 
@@ -265,14 +267,18 @@ class HostMatmul:
             self.b = torch.empty(K, N, dtype=dtype, device=self.dev)
             self.c = torch.empty(M, N, dtype=dtype, device=self.dev)
             self.s_in, self.s_out = torch.cuda.Stream(self.dev), torch.cuda.Stream(self.dev)
+        self._b_key = None  # (data_ptr, version, strides) of the host B whose copy self.b holds
 
     def run(self, a_h, b_h, c_h, activation=""):
         assert a_h.shape == (self.M, self.K) and b_h.shape == (self.K, self.N) and c_h.shape == (self.M, self.N)
         cur = torch.cuda.current_stream(self.dev)
         self.s_in.wait_stream(cur)   # earlier work that still reads the device buffers
         self.s_out.wait_stream(cur)
-        with torch.cuda.stream(self.s_in):
-            self.b.copy_(b_h, non_blocking=True)
+        b_key = (b_h.data_ptr(), b_h._version, b_h.stride())
+        if b_key != self._b_key:
+            with torch.cuda.stream(self.s_in):
+                self.b.copy_(b_h, non_blocking=True)
+            self._b_key = b_key
         for r0 in range(0, self.M, self.rows):
             r1 = min(self.M, r0 + self.rows)
             with torch.cuda.stream(self.s_in):
@@ -316,11 +322,18 @@ def attention_forward(q, k, v, causal, sm_scale, return_row_max=False):
         qp, kp, vp = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v))
         o, *stats = attention_forward(qp, kp, vp, causal, sm_scale, return_row_max)
         return (o[..., :D].contiguous(), *stats)
+    if fp8 and D in (16, 32, 64):
+        # the 8-bit kernel is built for head dim 128 (rows of 128 bytes); smaller head dims - 64 is the
+        # reference's own fp8 benchmark shape, 06-fused-attention.py:570 - get zero columns appended,
+        # which leave q k^T, P and the kept columns of O bit for bit what they are without them
+        pad8 = lambda t: torch.nn.functional.pad(t.view(torch.uint8), (0, 128 - D)).view(torch.float8_e5m2)
+        o, *stats = attention_forward(pad8(q), pad8(k), pad8(v), causal, sm_scale, return_row_max)
+        return (o[..., :D].contiguous(), *stats)
     with _on_device(dev):
         if fp8:
             # the reference's fp8 forward (06-fused-attention.py:609-615) is given V with the key
             # dimension contiguous; any other V is brought into that layout first
-            assert D == 128, "the 8-bit forward has a kernel for head dim 128"
+            assert D == 128, "the 8-bit forward has a kernel for head dim 128 (smaller ones are padded above)"
             if v.stride(2) != 1:
                 v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
             o = torch.empty((Z, H, N, D), device=dev, dtype=q.dtype)
@@ -337,26 +350,50 @@ def attention_forward(q, k, v, causal, sm_scale, return_row_max=False):
     return (o, M, row_max) if return_row_max else (o, M)
 
 
-def attention_backward(q, k, v, o, M, do, causal, sm_scale):
-    """dq, dk, dv.  Same checks as the reference's backward (06-fused-attention.py:478-494)."""
+def _one_pass_default():
+    """B200_ATTN_BWD_ONEPASS=1 makes the one-pass backward the default wherever it applies."""
+    return os.environ.get("B200_ATTN_BWD_ONEPASS", "0") not in ("", "0")
+
+
+def attention_backward(q, k, v, o, M, do, causal, sm_scale, one_pass=None):
+    """dq, dk, dv.  Same checks as the reference's backward (06-fused-attention.py:478-494).
+
+    `one_pass` (head dim 64 only): a single kernel that computes the scores, exponentials and dS
+    once per (K/V block, Q block) pair and adds the partial dQ of every K/V block into an fp32
+    buffer - the layout of the reference's older `sequence_parallel` backward
+    (python/test/regression/test_performance.py:174, 194) - instead of the two kernels of the
+    reference's current layout, which each recompute them.  About 1.6x faster; dK and dV are the
+    same bits, the last bit of dQ can vary from run to run because the partials are summed in no
+    fixed order.  Default: off (bitwise repeatable), or what B200_ATTN_BWD_ONEPASS says."""
     assert do.is_contiguous()
     assert q.stride() == k.stride() == v.stride() == o.stride() == do.stride()
     Z, H, N, D = q.shape
     assert N % 128 == 0
     dev = _require_cuda(q, k, v, o, do, M)
+    if one_pass is None:
+        one_pass = _one_pass_default()
     if D in (16, 32):  # as in attention_forward: zero-padded to the kernels' head dim 64
         qp, kp, vp, op, dop = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v, o, do))
-        return tuple(g[..., :D].contiguous() for g in attention_backward(qp, kp, vp, op, M, dop, causal, sm_scale))
+        return tuple(g[..., :D].contiguous() for g in attention_backward(qp, kp, vp, op, M, dop, causal, sm_scale, one_pass))
     with _on_device(dev):
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)
         delta = torch.empty_like(M)
-        code = _lib.lib().b200_attention_bwd(
-            _stream(q), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(),
-            delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), Z, H, N, D,
-            _lib.strides4(q), _lib.strides4(k), _lib.strides4(v), _lib.strides4(o), _lib.strides4(do),
-            _lib.strides4(dq), _lib.strides4(dk), _lib.strides4(dv), float(sm_scale), 1 if causal else 0, _DT[q.dtype])
+        ptrs = (q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), M.data_ptr(), delta.data_ptr())
+        tail = (dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), Z, H, N, D,
+                _lib.strides4(q), _lib.strides4(k), _lib.strides4(v), _lib.strides4(o), _lib.strides4(do),
+                _lib.strides4(dq), _lib.strides4(dk), _lib.strides4(dv), float(sm_scale), 1 if causal else 0, _DT[q.dtype])
+        L = _lib.lib()
+        if D == 256:
+            # head dim 256: per-head matmuls with [N, N] intermediates in scratch (see the header)
+            ws = torch.empty(L.b200_attention_bwd_wide_workspace(N) + 256, dtype=torch.uint8, device=dev)
+            code = L.b200_attention_bwd_wide(_stream(q), *ptrs, *tail, (ws.data_ptr() + 255) & ~255)
+        elif one_pass and D == 64:
+            acc = torch.empty(L.b200_attention_bwd_onepass_workspace(Z, H, N, D) // 4, dtype=torch.float32, device=dev)
+            code = L.b200_attention_bwd_onepass(_stream(q), *ptrs, acc.data_ptr(), *tail)
+        else:
+            code = L.b200_attention_bwd(_stream(q), *ptrs, *tail)
         _lib.check(code, "attention_bwd")
     return dq, dk, dv
 
@@ -365,28 +402,31 @@ class _attention(torch.autograd.Function):
     """Mirror of the reference's autograd wrapper (06-fused-attention.py:438-520)."""
 
     @staticmethod
-    def forward(ctx, q, k, v, causal, sm_scale):
+    def forward(ctx, q, k, v, causal, sm_scale, sequence_parallel=False):
         o, M = attention_forward(q, k, v, causal, sm_scale)
         ctx.save_for_backward(q, k, v, o, M)
         ctx.sm_scale = sm_scale
         ctx.causal = causal
+        ctx.sequence_parallel = sequence_parallel
         return o
 
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, M = ctx.saved_tensors
+        one_pass = True if (ctx.sequence_parallel and q.shape[-1] == 64) else None
         dq, dk, dv = attention_backward(q, k, v, o, M, do.contiguous() if not do.is_contiguous() else do,
-                                        ctx.causal, ctx.sm_scale)
-        return dq, dk, dv, None, None
+                                        ctx.causal, ctx.sm_scale, one_pass)
+        return dq, dk, dv, None, None, None
 
 
 def attention(q, k, v, causal, sm_scale, sequence_parallel=False):
     """O = softmax(Q K^T * sm_scale [causal]) V, differentiable: the reference's
     `attention = _attention.apply` (06-fused-attention.py:520).  The sixth argument is the older
     `triton.ops.attention(q, k, v, causal, sm_scale, sequence_parallel)` signature
-    (python/test/regression/test_performance.py:194); it changes nothing here: both backward
-    kernels are parallel over 128-row blocks of the sequence in either case."""
-    return _attention.apply(q, k, v, causal, sm_scale)
+    (python/test/regression/test_performance.py:194): with it the backward forms partial dQ per
+    K/V block and sums them, which here is the one-pass backward kernel (head dim 64; other head
+    dims run the two-kernel backward either way)."""
+    return _attention.apply(q, k, v, causal, sm_scale, sequence_parallel)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -18,9 +18,9 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 REGIONS, EVENTS = 4, 4096  # kTraceRegions, kTraceEvents of csrc/trace.h
 
 FWD_TAGS = {1: "wait for S (MMA of this tile + hand-over)", 2: "TMEM load + row maximum", 3: "rescale decision (+ O rescale)",
-            4: "exp2, pack, P store, arrive", 8: "wait for the last P V (o_full)", 9: "epilogue: store issue, M",
-            0xA: "epilogue: TMEM load of 64 columns", 0xB: "epilogue: wait for the staging buffer",
-            0xC: "epilogue: scale, pack, staging write, fence"}
+            4: "exp2, pack, P store, arrive", 9: "row statistics handed to the correction warps"}
+FWD_CORR = {7: "wait for a tile's row statistics", 8: "wait for the tile's last P V (o_full)",
+            9: "epilogue: O / l through staging and TMA stores, M"}
 FWD_MMA = {0x10: "P V issued / before the wait for P", 0x20: "P arrived", 0x40: "S issued",
            0x50: "tile 1's S issued; before the wait for V", 0x60: "V arrived"}
 BWD_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3: "wait for T2 (dP)",
@@ -91,6 +91,9 @@ def main():
                 print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
         print("  MMA warp")
         for key, n, mean in _summarise(t[2].tolist(), FWD_MMA):
+            print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
+        print("  correction warp 0")
+        for key, n, mean in _summarise(t[3].tolist(), FWD_CORR):
             print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
     else:
         for region, label in ((0, "dK/dV kernel, compute warp 0"), (1, "dQ kernel, compute warp 0")):
