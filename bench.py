@@ -266,15 +266,29 @@ def other_configs(torch, tb, dev):
     g = torch.Generator().manual_seed(0)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-    def timed(fn, flops, reps=10):
+    def timed(fn, flops, reps=10, graph=False):
+        """median of `reps` L2-flushed launches; graph=True replays a CUDA graph of fn (the reference
+        times attention with do_bench_cudagraph, python/triton/testing.py:19-81: for launches of a few
+        tens of microseconds the host side of an eager launch is part of what CUDA events see)"""
         for _ in range(3):
             fn()
+        run = fn
+        if graph:
+            torch.cuda.synchronize()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg, stream=side):
+                fn()
+            torch.cuda.current_stream().wait_stream(side)
+            run = cg.replay
+            run()
         ts = []
         for _ in range(reps):
             flush.zero_()  # inputs of these configs can fit in L2: flush between repetitions
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            fn()
+            run()
             e1.record()
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
@@ -284,6 +298,7 @@ def other_configs(torch, tb, dev):
     a = torch.randn(512, 512, generator=g).half().to(dev)
     b = torch.randn(512, 512, generator=g).half().to(dev)
     out["c1_matmul_fp16_512"] = timed(lambda: tb.matmul(a, b), 2.0 * 512 ** 3)
+    out["c1_matmul_fp16_512_cudagraph"] = timed(lambda: tb.matmul(a, b), 2.0 * 512 ** 3, graph=True)
     a8, sa = tb.quantize_e4m3(torch.randn(M, K, generator=g).to(dev))
     b8, sb = tb.quantize_e4m3(torch.randn(K, N, generator=g).to(dev))
     out["c3_matmul_fp8_8192_scaled_bf16"] = timed(lambda: tb.matmul(a8, b8, scale_a=sa, scale_b=sb), 2.0 * M * N * K)
@@ -306,6 +321,8 @@ def other_configs(torch, tb, dev):
     out["c5_fwd_only"] = timed(lambda: tb.attention_forward(q, k, v, True, 0.5), fl)
     out["c5_bwd_only"] = timed(lambda: tb.attention_backward(q, k, v, o, Mst, do, True, 0.5, one_pass=True), fl * 2.5)
     out["c5_fwd_bwd_two_kernel_backward"] = timed(lambda: fwd_bwd(False), fl * 3.5)
+    out["c5_attn_fwd_bwd_cudagraph"] = timed(lambda: fwd_bwd(True), fl * 3.5, graph=True)
+    out["c5_fwd_bwd_two_kernel_backward_cudagraph"] = timed(lambda: fwd_bwd(False), fl * 3.5, graph=True)
     out["c5_bwd_only_two_kernel"] = timed(lambda: tb.attention_backward(q, k, v, o, Mst, do, True, 0.5, one_pass=False), fl * 2.5)
     del q, k, v, do, o, Mst
     # rows beyond the five configs: the widened matmul / attention entry points
@@ -588,6 +605,7 @@ def per_config_roofline(cfgs, pk):
         "c5_fwd": entry("c5_fwd_only", pk["burst"], meas),
         "c5_bwd": entry("c5_bwd_only", pk["burst"], meas),
         "c5_two_kernel_backward": entry("c5_fwd_bwd_two_kernel_backward", pk["burst"], meas),
+        "c5_cudagraph": entry("c5_attn_fwd_bwd_cudagraph", pk["burst"], meas),
     }
 
 

@@ -3,6 +3,7 @@ Triton interpreter (tests/golden/make_golden.py), and against the reference test
 own torch formulations (python/tutorials/06-fused-attention.py:533-559,
 python/tutorials/03-matrix-multiplication.py:357-371)."""
 import hashlib
+import os
 
 import numpy as np
 import pytest
@@ -10,6 +11,8 @@ import torch
 
 import cases
 from oracle import ref_ops as R
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def sha(t):
@@ -30,6 +33,32 @@ def test_matmul_matches_interpreter(golden, name):
     # same tile order and fp32 accumulation: differences are BLAS summation order only
     np.testing.assert_allclose(got, want, rtol=1e-3, atol=1e-3)
     assert (got != want).mean() < 0.02
+
+
+def test_interpreter_tile_program_matches_reference_fixture(golden, tmp_path):
+    """oracle/interp_matmul.py restates the reference's matmul tile program in its own kernel language
+    so that the Triton interpreter can be timed where no checkout of the reference exists.  Run under
+    the same interpreter on the fixtures' inputs it must reproduce, bit for bit, what the reference's
+    own kernel text produced (config 1 and the ragged case, whose edge tiles wrap and mask)."""
+    import subprocess
+    import sys
+    script = tmp_path / "run.py"
+    script.write_text(
+        "import sys, numpy as np\n"
+        f"sys.path[:0] = [{ROOT!r}, {ROOT + '/tests/golden'!r}]\n"
+        "from oracle import interp_matmul as im\n"
+        "import cases\n"
+        "out = {}\n"
+        "for name in ('c1_512', 'ragged'):\n"
+        "    a, b = cases.matmul_inputs(cases.MATMUL_CASES[name])\n"
+        "    out[name] = im.matmul(a, b).numpy()\n"
+        f"np.savez({str(tmp_path / 'out.npz')!r}, **out)\n")
+    env = dict(os.environ, TRITON_INTERPRET="1")
+    r = subprocess.run([sys.executable, str(script)], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    with np.load(tmp_path / "out.npz") as z:
+        for name in ("c1_512", "ragged"):
+            assert np.array_equal(z[name], golden[f"matmul.{name}.c"]), name
 
 
 def test_matmul_c1_reference_test_tolerance():

@@ -487,7 +487,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(256)
 attn_bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ dout, float* __restrict__ delta,
                       long long o_sz, long long o_sh, long long o_sn, long long d_sz, long long d_sh, long long d_sn,
-                      unsigned H, unsigned N, unsigned rows_total) {
+                      unsigned H, unsigned N, unsigned rows_total, float* __restrict__ zero_rows) {
   constexpr int TPR = D / 8;           // threads per row
   constexpr unsigned RPB = 256 / TPR;  // rows per block and step
   constexpr int U = 4;                 // rows per thread in flight (independent 16-byte loads)
@@ -505,6 +505,11 @@ attn_bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict
         const unsigned n = row % N, zh = row / N, hh = zh % H, zz = zh / H;
         ov[u] = *reinterpret_cast<const uint4*>(o + zz * o_sz + hh * o_sh + (long long)n * o_sn + part * 8);
         dv[u] = *reinterpret_cast<const uint4*>(dout + zz * d_sz + hh * d_sh + (long long)n * d_sn + part * 8);
+        if (zero_rows) {  // the one-pass backward's fp32 dQ accumulator, [rows][D]: cleared on the way
+          float4* z = reinterpret_cast<float4*>(zero_rows + (long long)row * D + part * 8);
+          z[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+          z[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
     }
 #pragma unroll
@@ -533,7 +538,7 @@ attn_bwd_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict
 
 template <int D, bool BF16>
 int launch_delta_t(DeviceCtx* ctx, cudaStream_t stream, const void* o, const void* dout, float* delta, const int64_t* so,
-                   const int64_t* sdo, int Z, int H, int N) {
+                   const int64_t* sdo, int Z, int H, int N, float* zero_rows = nullptr) {
   const long long rows = (long long)Z * H * N;
   if (rows >= (1ll << 32)) return fail(B200_ERR_UNSUPPORTED, "more than 2^32 rows");
   const long long rows_per_block = (256 / (D / 8)) * 4;
@@ -541,7 +546,7 @@ int launch_delta_t(DeviceCtx* ctx, cudaStream_t stream, const void* o, const voi
   if (blocks > (long long)ctx->sm_count * 16) blocks = (long long)ctx->sm_count * 16;
   attn_bwd_delta_kernel<D, BF16><<<(unsigned)blocks, 256, 0, stream>>>(
       reinterpret_cast<const uint16_t*>(o), reinterpret_cast<const uint16_t*>(dout), delta, so[0], so[1], so[2],
-      sdo[0], sdo[1], sdo[2], (unsigned)H, (unsigned)N, (unsigned)rows);
+      sdo[0], sdo[1], sdo[2], (unsigned)H, (unsigned)N, (unsigned)rows, zero_rows);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return fail(B200_ERR_CUDA, "attn bwd delta launch: %s", cudaGetErrorString(e));
   return B200_OK;
@@ -592,13 +597,15 @@ int launch_bwd_all(DeviceCtx* ctx, cudaStream_t stream, const void* o, const voi
 
 }  // namespace
 
-// delta = rowsum(O * dO) for any head dim of the library (the pre-pass on its own)
+// delta = rowsum(O * dO) for any head dim of the library (the pre-pass on its own); zero_rows: optional
+// contiguous fp32 [Z*H*N][D] buffer that the same pass clears (head dim 64 only)
 int launch_attn_bwd_delta(DeviceCtx* ctx, cudaStream_t stream, const void* o, const void* dout, float* delta, int Z,
-                          int H, int N, int D, const int64_t* so, const int64_t* sdo, int dtype) {
+                          int H, int N, int D, const int64_t* so, const int64_t* sdo, int dtype, float* zero_rows) {
   const bool bf16 = dtype == B200_BF16;
+  if (zero_rows && D != 64) return fail(B200_ERR_ARG, "the pre-pass clears an accumulator at head dim 64 only");
   switch (D) {
-    case 64: return bf16 ? launch_delta_t<64, true>(ctx, stream, o, dout, delta, so, sdo, Z, H, N)
-                         : launch_delta_t<64, false>(ctx, stream, o, dout, delta, so, sdo, Z, H, N);
+    case 64: return bf16 ? launch_delta_t<64, true>(ctx, stream, o, dout, delta, so, sdo, Z, H, N, zero_rows)
+                         : launch_delta_t<64, false>(ctx, stream, o, dout, delta, so, sdo, Z, H, N, zero_rows);
     case 128: return bf16 ? launch_delta_t<128, true>(ctx, stream, o, dout, delta, so, sdo, Z, H, N)
                           : launch_delta_t<128, false>(ctx, stream, o, dout, delta, so, sdo, Z, H, N);
     case 256: return bf16 ? launch_delta_t<256, true>(ctx, stream, o, dout, delta, so, sdo, Z, H, N)

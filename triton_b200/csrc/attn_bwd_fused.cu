@@ -17,8 +17,10 @@
 // (deterministic) and serves head dim 128.
 //
 // Sixteen warps: 0-7 compute (two threads per K/V row, splitting the Q columns), 8-11 drain the dQ
-// partial from TMEM into staging buffers and issue the reduce-adds, 12 issues MMAs, 13 runs TMA,
-// 14-15 lend registers (setmaxnreg).
+// partial from TMEM into staging buffers and issue the reduce-adds and, at the end of an item, write
+// dK and dV (so that the compute warps go straight on to the next item), 12 issues MMAs, 13 runs
+// TMA, 14-15 lend registers (setmaxnreg).  K and V are double-buffered: the next item's pair is
+// loaded while this item runs.
 // TMEM columns: T1 [0,128) T2 [128,256) dK [256,320) dV [320,384) dQ partial [384,448).
 #include <cmath>
 
@@ -33,8 +35,8 @@ namespace {
 constexpr int BLK = 128, D = 64;
 constexpr int FB_THREADS = 512;
 // registers per thread after the re-division; one warp of each warpgroup shares a scheduler's 16K
-// registers: (2 * 168 + 88 + 88) * 32 lanes = 16384
-constexpr int REGS_COMPUTE = 168, REGS_DRAIN = 88, REGS_OTHER = 88;
+// registers: (2 * 176 + 88 + 72) * 32 lanes = 16384
+constexpr int REGS_COMPUTE = 176, REGS_DRAIN = 88, REGS_OTHER = 72;
 
 struct FusedParams {
   const float* m;      // [Z*H, N] base-2 LSE from the forward
@@ -49,12 +51,11 @@ struct FusedParams {
 };
 
 constexpr int TILE = BLK * D * 2;            // one 128 x 64 tile of 16-bit values
-constexpr int NST = 3;                       // stages of the (Q, dO) ring
+constexpr int NST = 2;                       // stages of the (Q, dO) ring
 constexpr int STAGE = 2 * TILE + 1024;       // Q_t, dO_t, M and delta of the streamed rows
 constexpr int DS_BYTES = BLK * BLK * 2;      // dS as an M-major operand: two blocks of 64 q x 128 kv rows
-constexpr int DQ_STG = 2 * 32 * 128;         // dQ staging of one drain warp: two boxes of 32 rows x 32 fp32 columns
-constexpr int OUT_STG = 32 * 64;             // dK / dV staging of one compute warp: 32 rows x 32 columns
-constexpr size_t FUSED_SMEM = 2 * TILE + (size_t)NST * STAGE + DS_BYTES + 4 * DQ_STG + 8 * OUT_STG + (2 * NST + 20) * 8 + 32 + 1024;
+constexpr int DQ_STG = 2 * 32 * 128;         // staging of one drain warp: two boxes of 32 rows x 128 bytes (dQ: 32 fp32 columns each; dK, dV: 64 16-bit columns)
+constexpr size_t FUSED_SMEM = 4 * TILE + (size_t)NST * STAGE + DS_BYTES + 4 * DQ_STG + (2 * NST + 22) * 8 + 32 + 1024;
 
 __device__ __forceinline__ void load_tile_f(uint8_t* dst, const CUtensorMap* map, uint64_t* bar, int row0, int h, int z) {
   tma_load_4d(dst, map, bar, 0, row0, h, z);  // head dim 64: one box of 64 columns x 128 rows
@@ -100,15 +101,14 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;
-  uint8_t* sres = smem;                   // K, V
-  uint8_t* sring = smem + 2 * TILE;       // stages
+  uint8_t* sres = smem;                   // (K, V) of even items, (K, V) of odd items
+  uint8_t* sring = smem + 4 * TILE;       // stages
   uint8_t* sds = sring + NST * STAGE;     // dS, M-major
-  uint8_t* sdq = sds + DS_BYTES;          // 4 x 8 KiB
-  uint8_t* sout = sdq + 4 * DQ_STG;       // 8 x 2 KiB, rows of 64 bytes, not swizzled
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sout + 8 * OUT_STG);
-  uint64_t* r_full = bars;              // K, V of the item loaded
-  uint64_t* r_empty = bars + 1;         // every MMA of the item has read them
-  uint64_t* full = bars + 2;            // [NST]
+  uint8_t* sdq = sds + DS_BYTES;          // 4 x 8 KiB, 128-byte swizzled
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdq + 4 * DQ_STG);
+  uint64_t* r_full = bars;              // [2] K, V of an item loaded (buffer = item parity)
+  uint64_t* r_empty = bars + 2;         // [2] every MMA of the item has read them
+  uint64_t* full = bars + 4;            // [NST]
   uint64_t* empty = full + NST;         // [NST]
   uint64_t* t1_full = empty + NST;      // T1(t) in TMEM
   uint64_t* t2_full = t1_full + 1;      // T2(t) in TMEM
@@ -118,16 +118,20 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   uint64_t* dq_full = ds_free + 1;      // the dQ partial of step t is in TMEM
   uint64_t* dq_free = dq_full + 1;      // the drain warps have read it
   uint64_t* acc_full = dq_free + 1;     // dK, dV of the item final
-  uint64_t* sched_full = acc_full + 1;  // [2] an item id was published
+  uint64_t* acc_free = acc_full + 1;    // the drain warps have read them: the next item may overwrite
+  uint64_t* sched_full = acc_free + 1;  // [2] an item id was published
   uint64_t* sched_empty = sched_full + 2;  // [2] all 13 readers have taken it
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sched_empty + 2);
   volatile int* sched_item = reinterpret_cast<volatile int*>(tmem_slot + 2);  // [2]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  B200_TRACE_DECL;  // trace builds: region 0 = first compute warp, 2 = MMA warp, 3 = first drain warp
 
   if (threadIdx.x == 0) {
-    mbar_init(r_full, 1);
-    mbar_init(r_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&r_full[i], 1);
+      mbar_init(&r_empty[i], 1);
+    }
     for (int s = 0; s < NST; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
@@ -140,6 +144,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     mbar_init(dq_full, 1);
     mbar_init(dq_free, 4);  // one arrival per drain warp
     mbar_init(acc_full, 1);
+    mbar_init(acc_free, 4);  // one arrival per drain warp
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sched_full[i], 1);
       mbar_init(&sched_empty[i], 13);  // MMA warp + one lane of each compute and drain warp
@@ -185,19 +190,27 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     // ------------------------------------------------------------------ scheduler + TMA producer
     if (lane == 0) {
       uint32_t s = 0, ph = 0;  // ring position, runs on across items
-      for (uint32_t n = 0;; ++n) {
+      // draws the n-th ticket, publishes it and, if it is an item, starts the load of its K and V
+      // into buffer n & 1 (free once the item two back has finished)
+      auto next_item = [&](uint32_t n) {
         const int w = atomicAdd(p.sched_counter, 1);
         const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
         mbar_wait(&sched_empty[slot], sph ^ 1u, p.status, SITE_BWD_SCHED);
         sched_item[slot] = w;
         mbar_arrive(&sched_full[slot]);
         if (w == p.total_items + (int)gridDim.x - 1) atomicExch(p.sched_counter, 0);  // the last ticket of the launch
-        if (w >= p.total_items) break;
+        if (w < p.total_items) {
+          const FusedItem it(p, w);
+          mbar_wait(&r_empty[slot], sph ^ 1u, p.status, SITE_BWD_KV);
+          mbar_expect_tx(&r_full[slot], 2 * TILE);
+          load_tile_f(sres + slot * 2 * TILE, &tm_k, &r_full[slot], it.blk * BLK, it.h, it.z);
+          load_tile_f(sres + slot * 2 * TILE + TILE, &tm_v, &r_full[slot], it.blk * BLK, it.h, it.z);
+        }
+        return w;
+      };
+      int w = next_item(0);
+      for (uint32_t n = 0; w < p.total_items; ++n) {
         const FusedItem it(p, w);
-        mbar_wait(r_empty, (n & 1u) ^ 1u, p.status, SITE_BWD_KV);  // the previous item no longer reads K, V
-        mbar_expect_tx(r_full, 2 * TILE);
-        load_tile_f(sres, &tm_k, r_full, it.blk * BLK, it.h, it.z);
-        load_tile_f(sres + TILE, &tm_v, r_full, it.blk * BLK, it.h, it.z);
         for (int t = it.t_lo; t < it.t_hi; ++t) {
           mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_BWD_LOAD_EMPTY);
           uint8_t* st = sring + s * STAGE;
@@ -209,6 +222,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
           bulk_load_f(st + 2 * TILE + 512, p.delta + (long long)it.zh * p.N + t * BLK, 512, &full[s]);
           if (++s == NST) { s = 0; ph ^= 1u; }
         }
+        w = next_item(n + 1);  // the next item's K and V travel while this item's last steps run
       }
     }
     __syncwarp();
@@ -222,10 +236,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       constexpr uint32_t IDESC_T = make_idesc(FMT, FMT, 0, 0, 128, BLK);   // K or V (K-major) x Q or dO (K-major)
       constexpr uint32_t IDESC_ACC = make_idesc(FMT, FMT, 0, 1, 128, D);   // P / dS (TMEM) x dO / Q (N-major)
       constexpr uint32_t IDESC_DQ = make_idesc(FMT, FMT, 1, 1, 128, D);    // dS (shared memory, M-major) x K (N-major)
-      const uint64_t dr0 = smem_desc_sw128(smem_u32(sres), 0, 1024);
+      const uint64_t dres = smem_desc_sw128(smem_u32(sres), 0, 1024);
       const uint64_t du0 = smem_desc_sw128(smem_u32(sring), 0, 1024);
       const uint64_t dun0 = smem_desc_sw128(smem_u32(sring), BLK * 128, 1024);  // N-major view of a streamed tile
-      const uint64_t dkn = smem_desc_sw128(smem_u32(sres), BLK * 128, 1024);    // N-major view of K
+      const uint64_t dkn0 = smem_desc_sw128(smem_u32(sres), BLK * 128, 1024);   // N-major view of K
       const uint64_t dds = smem_desc_sw128(smem_u32(sds), BLK * 128, 1024);     // dS: 64-row M blocks 16 KiB apart
 
       auto issue_t = [&](uint32_t tm, uint64_t dr, uint64_t du) {  // T = R U^T, D/16 MMAs
@@ -251,7 +265,8 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         const FusedItem item(p, w);
         const int steps = item.t_hi - item.t_lo;  // >= 1
 
-        mbar_wait(r_full, n & 1u, p.status, SITE_BWD_KV);
+        const uint64_t dr0 = dres + slot * ((2 * TILE) >> 4), dkn = dkn0 + slot * ((2 * TILE) >> 4);  // this item's K, V
+        mbar_wait(&r_full[slot], sph, p.status, SITE_BWD_KV);
         mbar_wait(&full[s], ph, p.status, SITE_BWD_LOAD_FULL);
         issue_t(tm_t1, dr0, du0 + s * (STAGE >> 4));
         tc_commit_elect(t1_full);
@@ -263,7 +278,10 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
           if (ns == NST) { ns = 0; nph ^= 1u; }
           const uint64_t dun_q = dun0 + cs * (STAGE >> 4), dun_do = dun_q + (TILE >> 4);
           const bool more = it + 1 < steps;
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x10);
           mbar_wait(p_full, cnt & 1u, p.status, SITE_BWD_P_FULL);
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x20);
+          if (it == 0) mbar_wait(acc_free, (n & 1u) ^ 1u, p.status, SITE_BWD_FREE);  // the previous item's dK, dV have left TMEM
           tc_fence_after();
           issue_acc(tm_dv, tm_t1, dun_do, it > 0);  // dV += P dO
           if (more) {  // the next scores: T1 is free once the dV MMAs have consumed P (in-order pipe)
@@ -271,18 +289,21 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             issue_t(tm_t1, dr0, du0 + ns * (STAGE >> 4));
             tc_commit_elect(t1_full);
           }
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x30);
           mbar_wait(ds_full, cnt & 1u, p.status, SITE_BWD_DS_FULL);
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x40);
           tc_fence_after();
           issue_acc(tm_dk, tm_t2, dun_q, it > 0);  // dK += dS Q
+          tc_commit_elect(&empty[cs]);  // that was the last read of Q_t and dO_t: the stage refills while dQ runs
           // dQ partial = dS^T K: the previous partial must have left TMEM
           mbar_wait(dq_free, (cnt & 1u) ^ 1u, p.status, SITE_BWD_FREE);
+          if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < BLK / 16; ++kk)
             umma_ss_elect<false>(tm_dq, dds + kk * ((16 * 128) >> 4), dkn + kk * ((16 * 128) >> 4), IDESC_DQ, kk != 0);
           tc_commit_elect(dq_full);
           tc_commit_elect(ds_free);
-          tc_commit_elect(&empty[cs]);
           if (more) {  // the next dP: T2 is free once the dK MMAs have consumed dS
             issue_t(tm_t2, dr0 + (TILE >> 4), du0 + ns * (STAGE >> 4) + (TILE >> 4));
             tc_commit_elect(t2_full);
@@ -290,7 +311,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
           s = ns; ph = nph;
         }
         tc_commit_elect(acc_full);
-        tc_commit_elect(r_empty);  // the item's last MMAs (dQ reads K) are behind this
+        tc_commit_elect(&r_empty[slot]);  // the item's last MMAs (dQ reads K) are behind this
       }
     }
     __syncwarp();
@@ -316,6 +337,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       const FusedItem item(p, w);
       for (int t = item.t_lo; t < item.t_hi; ++t, ++cnt) {
         mbar_wait(dq_full, cnt & 1u, p.status, SITE_BWD_ACC_FULL);
+        if (quarter == 0 && lane == 0) B200_TRACE_EVENT(p.status, 3, 7);
         tc_fence_after();
         uint32_t r[D];
         tmem_ld32(tm_dq + lane_addr, r);
@@ -342,9 +364,45 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
           tma_reduce_add_4d(&map_dqacc, stg + 4096, 32, row0, item.h, item.z);
           tma_store_commit();
         }
+        if (quarter == 0 && lane == 0) B200_TRACE_EVENT(p.status, 3, 8);
+      }
+      // the item's dK and dV: this warp's 32 rows, 64 columns each = one box of 128-byte lines per
+      // gradient, through the same two staging boxes
+      mbar_wait(acc_full, n & 1u, p.status, SITE_BWD_ACC_FULL);
+      tc_fence_after();
+      if (lane == 0) tma_store_wait_read<0>();  // the last reduce-adds have read the staging boxes
+      __syncwarp();
+#pragma unroll 1
+      for (int g = 0; g < 2; ++g) {  // 0: dK (carries sm_scale), 1: dV
+        const float mul = g ? 1.0f : p.sm_scale;
+        uint8_t* box = stg + g * 4096;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld32((g ? tm_dv : tm_dk) + lane_addr + c, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t wv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              wv[k] = pack2<BF16>(__uint_as_float(o[8 * ch + 2 * k]) * mul, __uint_as_float(o[8 * ch + 2 * k + 1]) * mul);
+            *reinterpret_cast<uint4*>(box + sw128_offset(lane, (c >> 3) + ch)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+          }
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(acc_free);
+        const int row0 = item.blk * BLK + quarter * 32;
+        tma_store_4d(&map_dk, stg, 0, row0, item.h, item.z);
+        tma_store_4d(&map_dv, stg + 4096, 0, row0, item.h, item.z);
+        tma_store_commit();
       }
     }
-    if (lane == 0) tma_store_wait_all<0>();  // this warp's reduce-adds are complete before the CTA exits
+    if (lane == 0) tma_store_wait_all<0>();  // this warp's stores and reduce-adds are complete before the CTA exits
     __syncwarp();
     teardown(false);
     return;
@@ -352,12 +410,12 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
     reg_inc<REGS_COMPUTE>();
     // ------------------------------------------------------------------ compute
     // Two threads per K/V row: warps w and w+4 own the same TMEM lanes and split the 128 Q columns
-    // of T1 / T2 (and, in the epilogue, the accumulator columns) in halves.  Each thread packs its
+    // of T1 / T2 in halves.  Each thread packs its
     // P and dS over the first 32 of its OWN 64 columns, so the halves never touch each other's
     // columns and need no barrier between them.
     const uint32_t quarter = warp & 3u;
     const int half = warp >> 2;
-    constexpr int HC = BLK / 2, HD = D / 2;
+    constexpr int HC = BLK / 2;
     const int r = quarter * 32 + lane;       // K/V row inside the block
     const uint32_t lane_addr = (quarter * 32u) << 16;
     const float scale = p.scale_log2;
@@ -377,14 +435,17 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       const FusedItem item(p, w);
       const int blk = item.blk;
       const int steps = item.t_hi - item.t_lo;
-      for (int it = 0; it < steps; ++it, ++cnt) {
+      const bool traced = warp == 0 && lane == 0;  // used by trace builds only
+      if (traced) B200_TRACE_EVENT(p.status, 0, 0x100 | steps);
+      uint32_t pr[HC];  // P of the step in hand, fp32 bits (phase A writes it, phase B reads it)
+      // phase A of step `it`: scores -> P (exp2), packed over T1 as the dV product's operand
+      auto phase_a = [&](int it, uint32_t c_, uint32_t s_) {
         const int t = item.t_lo + it;
-        const float* sm = reinterpret_cast<const float*>(sring + s * STAGE + 2 * TILE) + half * HC;  // column M
-        const float* sd = sm + 128;                                                                  // column delta
+        const float* sm = reinterpret_cast<const float*>(sring + s_ * STAGE + 2 * TILE) + half * HC;  // column M
         const bool diag = p.causal && (t == blk);  // the only block that needs the causal mask
-        mbar_wait(t1_full, cnt & 1u, p.status, SITE_BWD_S_FULL);
+        mbar_wait(t1_full, c_ & 1u, p.status, SITE_BWD_S_FULL);
+        if (traced) B200_TRACE_EVENT(p.status, 0, 1);
         tc_fence_after();
-        uint32_t pr[HC];  // P as fp32 bits
 #pragma unroll
         for (int c = 0; c < HC; c += 32) tmem_ld32(tm_t1 + lane_addr + half * HC + c, pr + c);
         tmem_ld_wait();
@@ -411,8 +472,13 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(p_full);
-
-        mbar_wait(t2_full, cnt & 1u, p.status, SITE_BWD_DP_FULL);
+        if (traced) B200_TRACE_EVENT(p.status, 0, 2);
+      };
+      // phase B of step `it`: dS = P (dP - delta), packed over T2 (dK product) and to shared memory (dQ product)
+      auto phase_b = [&](uint32_t c_, uint32_t s_) {
+        const float* sd = reinterpret_cast<const float*>(sring + s_ * STAGE + 2 * TILE) + 128 + half * HC;  // column delta
+        mbar_wait(t2_full, c_ & 1u, p.status, SITE_BWD_DP_FULL);
+        if (traced) B200_TRACE_EVENT(p.status, 0, 3);
         tc_fence_after();
         uint32_t dsw[HC / 2];  // dS packed to 16 bit
 #pragma unroll
@@ -436,7 +502,9 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         for (int c = 0; c < HC / 2; c += 16) tmem_st16(tm_t2 + lane_addr + half * HC + c, dsw + c);  // own columns
         // the same dS as the A operand of the dQ product: row r (kv) of the M-major tile, this
         // thread's 64 q columns = one 128-byte line of block `half`, 16-byte chunks swizzled
-        mbar_wait(ds_free, (cnt & 1u) ^ 1u, p.status, SITE_BWD_FREE);  // the previous step's dQ MMAs have read the tile
+        if (traced) B200_TRACE_EVENT(p.status, 0, 5);
+        mbar_wait(ds_free, (c_ & 1u) ^ 1u, p.status, SITE_BWD_FREE);  // the previous step's dQ MMAs have read the tile
+        if (traced) B200_TRACE_EVENT(p.status, 0, 6);
         {
           uint8_t* line = sds + half * (BLK * 128);
 #pragma unroll
@@ -447,42 +515,18 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(ds_full);
+        if (traced) B200_TRACE_EVENT(p.status, 0, 4);
+      };
+      // Both warps of a scheduler (the halves of a row) run A(t) B(t) in step.  (Skewing them - half 1
+      // doing B(t-1) A(t), so that one half's exponentials overlap the other's dS arithmetic - was
+      // measured 25 % slower: T1 of the next step needs both halves' P, so the early half only waits.)
+      for (int it = 0; it < steps; ++it, ++cnt) {
+        phase_a(it, cnt, s);
+        phase_b(cnt, s);
         if (++s == NST) s = 0;
       }
-
-      // epilogue: each thread stores its half of the accumulator columns through its warp's staging
-      // buffer and TMA stores.  It overlaps the next item's loads and first T MMAs; the next item's
-      // first accumulate MMA needs this warp's next P / dS, i.e. comes after these reads.
-      mbar_wait(acc_full, n & 1u, p.status, SITE_BWD_ACC_FULL);
-      tc_fence_after();
-      auto store_rows = [&](uint32_t tm_acc, const CUtensorMap* map, float mul) {
-        uint8_t* stg = sout + warp * OUT_STG;
-        const int warp_row0 = blk * BLK + quarter * 32;
-        uint32_t o[32];
-        tmem_ld32(tm_acc + lane_addr + half * HD, o);
-        tmem_ld_wait();
-        if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging buffer
-        __syncwarp();
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t wv[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            wv[k] = pack2<BF16>(__uint_as_float(o[8 * ch + 2 * k]) * mul, __uint_as_float(o[8 * ch + 2 * k + 1]) * mul);
-          *reinterpret_cast<uint4*>(stg + lane * 64 + ch * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_4d(map, stg, half * HD, warp_row0, item.h, item.z);
-          tma_store_commit();
-        }
-      };
-      store_rows(tm_dk, &map_dk, p.sm_scale);  // dK carries sm_scale
-      store_rows(tm_dv, &map_dv, 1.0f);
+      // dK and dV of the item are written by the drain warps: straight on to the next item
     }
-    if (lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
-    __syncwarp();
     teardown(false);
   }
 }
@@ -547,16 +591,16 @@ int launch_attn_bwd_fused(DeviceCtx* ctx, cudaStream_t stream, const void* q, co
   if (!encode_qkv_map(&tk, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], BLK)) return B200_ERR_UNSUPPORTED;
   if (!encode_qkv_map(&tv, dtype, v, Z, H, N, D, sv[0], sv[1], sv[2], BLK)) return B200_ERR_UNSUPPORTED;
   if (!encode_qkv_map(&tdo, dtype, dout, Z, H, N, D, sdo[0], sdo[1], sdo[2], BLK)) return B200_ERR_UNSUPPORTED;
-  if (!encode_rows_map(&mdk, dtype, dk, Z, H, N, D, sdk[0], sdk[1], sdk[2], 32, 32, false)) return B200_ERR_UNSUPPORTED;
-  if (!encode_rows_map(&mdv, dtype, dv, Z, H, N, D, sdv[0], sdv[1], sdv[2], 32, 32, false)) return B200_ERR_UNSUPPORTED;
+  // dK, dV leave through boxes of 32 rows x 64 columns (128-byte lines, swizzled)
+  if (!encode_qkv_map(&mdk, dtype, dk, Z, H, N, D, sdk[0], sdk[1], sdk[2], 32)) return B200_ERR_UNSUPPORTED;
+  if (!encode_qkv_map(&mdv, dtype, dv, Z, H, N, D, sdv[0], sdv[1], sdv[2], 32)) return B200_ERR_UNSUPPORTED;
   // the fp32 accumulator of dQ: contiguous [Z, H, N, 64], boxes of 32 columns (128 bytes, swizzled) x 32 rows
   if (!encode_rows_map(&macc, B200_F32, dq_acc, Z, H, N, D, (int64_t)H * N * D, (int64_t)N * D, D, 32, 32, true))
     return B200_ERR_UNSUPPORTED;
   if ((sdq[0] & 7) || (sdq[1] & 7) || (sdq[2] & 7) || (reinterpret_cast<uintptr_t>(dq) & 15))
     return fail(B200_ERR_UNSUPPORTED, "dQ must be 16-byte aligned with strides that are multiples of 8 elements");
-  if (int rc = launch_attn_bwd_delta(ctx, stream, o, dout, delta, Z, H, N, D, so, sdo, dtype)) return rc;
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)rows * D * sizeof(float), stream);
-  if (e != cudaSuccess) return fail(B200_ERR_CUDA, "dQ accumulator clear: %s", cudaGetErrorString(e));
+  // the pre-pass also clears the dQ accumulator (one launch, one pass over the rows)
+  if (int rc = launch_attn_bwd_delta(ctx, stream, o, dout, delta, Z, H, N, D, so, sdo, dtype, dq_acc)) return rc;
   FusedParams p{};
   p.m = m; p.delta = delta;
   p.Z = Z; p.H = H; p.N = N; p.causal = causal;

@@ -93,7 +93,8 @@ int launch_attn_bwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
 
 // the backward's pre-pass on its own: delta[z, h, n] = sum_d O * dO (head dims 64, 128, 256)
 int launch_attn_bwd_delta(DeviceCtx* ctx, cudaStream_t stream, const void* o, const void* dout, float* delta, int Z,
-                          int H, int N, int D, const int64_t* so, const int64_t* sdo, int dtype);
+                          int H, int N, int D, const int64_t* so, const int64_t* sdo, int dtype,
+                          float* zero_rows = nullptr);
 
 // head dim 256 backward, composed of matmul launches per head (attn_bwd_wide.cu)
 size_t attn_bwd_wide_workspace_bytes(int N);

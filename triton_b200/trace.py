@@ -1,7 +1,8 @@
 """Device-side clock trace of the attention kernels.
 
     python -m triton_b200.trace fwd [--case c4|c5|noncausal|e5m2]
-    python -m triton_b200.trace bwd [--case c5|long]
+    python -m triton_b200.trace bwd [--case c5|long]        (the two-kernel backward)
+    python -m triton_b200.trace bwd1 [--case c5|long]       (the one-pass backward, head dim 64)
 
 Builds the instrumented variant of the library (`-DB200_TRACE`, libtriton_b200_trace.so beside the
 production one), runs a few launches of one configuration through the normal Python wrappers and
@@ -23,6 +24,12 @@ FWD_CORR = {7: "wait for a tile's row statistics", 8: "wait for the tile's last 
             9: "epilogue: O / l through staging and TMA stores, M"}
 FWD_MMA = {0x10: "P V issued / before the wait for P", 0x20: "P arrived", 0x40: "S issued",
            0x50: "tile 1's S issued; before the wait for V", 0x60: "V arrived"}
+ONE_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3: "wait for T2 (dP)",
+            5: "dS, TMEM store", 6: "wait for the shared-memory dS tile (previous dQ MMAs)",
+            4: "shared-memory dS write, proxy fence, arrive"}
+ONE_MMA = {0x10: "dQ / T2 issued; before the wait for P", 0x20: "P arrived", 0x30: "dV, next T1 issued; before the wait for dS",
+           0x40: "dS arrived", 0x50: "dK issued, previous dQ partial drained"}
+ONE_DRAIN = {7: "wait for a dQ partial", 8: "TMEM load, staging write, reduce-add issue"}
 BWD_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3: "wait for T2 (dP)",
             4: "dS, store, arrive", 8: "wait for the last accumulate (acc_full)", 9: "epilogue (gradient stores)"}
 
@@ -45,7 +52,7 @@ def _summarise(ev, names, item_tag=0x100):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["fwd", "bwd"])
+    ap.add_argument("kernel", choices=["fwd", "bwd", "bwd1"])
     ap.add_argument("--case", default=None)
     args = ap.parse_args()
     from . import build
@@ -57,6 +64,8 @@ def main():
     from triton_b200 import _lib
     assert _lib._lib is None, "the library was loaded before the trace build was selected"
     case = args.case or ("c4" if args.kernel == "fwd" else "c5")
+    if case == "c4" and args.kernel != "fwd":
+        raise SystemExit("the backward traces take --case c5 or long")
     Z, H, N, D, dt, causal, sm = {"c4": (4, 32, 4096, 128, torch.float16, True, 128 ** -0.5),
                                   "noncausal": (4, 32, 4096, 128, torch.float16, False, 128 ** -0.5),
                                   "c5": (4, 48, 1024, 64, torch.bfloat16, True, 0.5),
@@ -75,13 +84,14 @@ def main():
         return buf.copy()
 
     o, M = tb.attention_forward(q, k, v, causal, sm)
-    if args.kernel == "bwd":
-        tb.attention_backward(q, k, v, o, M, do, causal, sm)
+    one = args.kernel == "bwd1"
+    if args.kernel != "fwd":
+        tb.attention_backward(q, k, v, o, M, do, causal, sm, one_pass=one)
     read()  # discard the first (cold) launch
     if args.kernel == "fwd":
         tb.attention_forward(q, k, v, causal, sm)
     else:
-        tb.attention_backward(q, k, v, o, M, do, causal, sm)
+        tb.attention_backward(q, k, v, o, M, do, causal, sm, one_pass=one)
     t = read()
     print(f"{args.kernel} Z{Z} H{H} N{N} D{D} causal={causal}: CTA 0, mean SM clocks since the previous trace point")
     if args.kernel == "fwd":
@@ -95,6 +105,11 @@ def main():
         print("  correction warp 0")
         for key, n, mean in _summarise(t[3].tolist(), FWD_CORR):
             print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
+    elif one:
+        for region, label, names in ((0, "compute warp 0", ONE_TAGS), (2, "MMA warp", ONE_MMA), (3, "drain warp 0", ONE_DRAIN)):
+            print(f"  {label}")
+            for key, n, mean in _summarise(t[region].tolist(), names):
+                print(f"    {key:56s} n={n:5d}  {mean:8.0f} clk")
     else:
         for region, label in ((0, "dK/dV kernel, compute warp 0"), (1, "dQ kernel, compute warp 0")):
             print(f"  {label}")
