@@ -466,8 +466,8 @@ def multi_gpu_extras(torch, tb, dev, rank, world, barrier):
     # all-gather of C: every rank contributes its [8192/world, 8192] fp16 row block of one 8192^2 C
     rows = M // world
     c_local = torch.randn(rows, N, device=dev).half()
-    tdist.all_gather_rows(c_local)
-    ms = device_time(lambda: tdist.all_gather_rows(c_local), 10, 2, torch, barrier)
+    tdist.all_gather_rows(c_local, equal_rows=True)
+    ms = device_time(lambda: tdist.all_gather_rows(c_local, equal_rows=True), 10, 2, torch, barrier)
     t = torch.tensor([ms], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     recv = rows * N * 2 * (world - 1)

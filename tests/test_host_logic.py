@@ -94,6 +94,9 @@ def _worker(rank, world, port, q):
         local = tdist.shard_heads(t, world, rank)[0] * 2.0
         gathered = tdist.all_gather_rows(local)
         ok = ok and torch.equal(gathered, t.reshape(6, 8, 4) * 2.0)
+        same = torch.full((3, 5), float(rank))
+        both = tdist.all_gather_rows(same, equal_rows=True)
+        ok = ok and torch.equal(both, torch.cat([torch.full((3, 5), float(r)) for r in range(world)]))
         q.put((rank, bool(ok), tuple(c.shape)))
     finally:
         dist.destroy_process_group()

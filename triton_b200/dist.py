@@ -43,11 +43,17 @@ def sharded_matmul(a_local, b, compute, gather=False, group=None):
     return all_gather_rows(c_local, group)
 
 
-def all_gather_rows(x, group=None):
-    """Concatenate `x` (leading dimension may differ per rank) over the ranks of `group`."""
+def all_gather_rows(x, group=None, equal_rows=False):
+    """Concatenate `x` (leading dimension may differ per rank) over the ranks of `group`.
+    equal_rows=True: the caller knows that every rank holds the same number of rows; one collective
+    into the assembled tensor, no size exchange and no host synchronisation."""
     world = dist.get_world_size(group)
     if world == 1:
         return x
+    if equal_rows:
+        out = torch.empty((world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
     n_local = torch.tensor([x.shape[0]], dtype=torch.int64, device=x.device)
     sizes = [torch.zeros_like(n_local) for _ in range(world)]
     dist.all_gather(sizes, n_local, group=group)
