@@ -358,6 +358,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  B200_TRACE_DECL;  // trace builds: region 0 = TMA warp, 1 / 2 = the issuing warps, 3 = first epilogue warp
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -392,7 +393,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         const int m0 = pid_m * BM, n0 = pid_n * BN;
         const int kb_end = min(p.num_k, (split + 1) * p.kb_per_split);
         for (int kb = split * p.kb_per_split; kb < kb_end; ++kb) {
+          B200_TRACE_EVENT(p.status, 0, 1);
           mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
+          B200_TRACE_EVENT(p.status, 0, 2);
           mbar_expect_tx(&full[s], STAGE_BYTES);
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           load_operand<false>(p.ga, &tma_a, a_dst, &full[s], kb * p.bk_elems, m0);
@@ -422,12 +425,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         const int split = work / p.num_tiles;
         const int kb_cnt = min(p.num_k, (split + 1) * p.kb_per_split) - split * p.kb_per_split;
         const uint32_t acc = ti % NACC;
+        if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 0x10);
         mbar_wait(&tmem_empty[acc], ((ti / NACC) & 1u) ^ 1u, p.status, SITE_GEMM_TMEM_EMPTY);
+        if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 0x20);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         uint32_t accum = 0;
         for (int kb = 0; kb < kb_cnt; ++kb) {
+          if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 1);
           mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);  // TMA bytes landed
+          if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 2);
           const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < KBYTES / 32; ++k) {
@@ -459,7 +466,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       int pid_m, pid_n;
       tile_coords(p, tile, pid_m, pid_n);
       const uint32_t acc = ti % NACC;
+      if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 1);
       mbar_wait(&tmem_full[acc], (ti / NACC) & 1u, p.status, SITE_GEMM_TMEM_FULL);
+      if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 2);
       tc_fence_after();
       if (p.splits > 1) {
         // split-K: the raw fp32 partial sums go to this split's slice of the workspace
@@ -475,6 +484,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                         pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
+      if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 3);
     }
     if (p.c_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
   }

@@ -3,6 +3,7 @@
     python -m triton_b200.trace fwd [--case c4|c5|noncausal|e5m2]
     python -m triton_b200.trace bwd [--case c5|long]        (the two-kernel backward)
     python -m triton_b200.trace bwd1 [--case c5|long]       (the one-pass backward, head dim 64)
+    python -m triton_b200.trace gemm [--case c2|c3]         (the 256 x 256 matmul tile, 8192^3)
 
 Builds the instrumented variant of the library (`-DB200_TRACE`, libtriton_b200_trace.so beside the
 production one), runs a few launches of one configuration through the normal Python wrappers and
@@ -19,9 +20,9 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 REGIONS, EVENTS = 4, 4096  # kTraceRegions, kTraceEvents of csrc/trace.h
 
 FWD_TAGS = {1: "wait for S (MMA of this tile + hand-over)", 2: "TMEM load + row maximum", 3: "rescale decision (+ O rescale)",
-            4: "exp2, pack, P store, arrive", 9: "row statistics handed to the correction warps"}
-FWD_CORR = {7: "wait for a tile's row statistics", 8: "wait for the tile's last P V (o_full)",
-            9: "epilogue: O / l through staging and TMA stores, M"}
+            4: "exp2, pack, P store, arrive", 8: "epilogue: wait for the tile's last P V (o_full)",
+            0xA: "epilogue: TMEM load of 64 columns of O", 0xB: "epilogue: previous store has read the staging buffer",
+            0xC: "epilogue: scale, pack, staging write, fence", 9: "epilogue: last store issued, M written"}
 FWD_MMA = {0x10: "P V issued / before the wait for P", 0x20: "P arrived", 0x40: "S issued",
            0x50: "tile 1's S issued; before the wait for V", 0x60: "V arrived"}
 ONE_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3: "wait for T2 (dP)",
@@ -30,6 +31,10 @@ ONE_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3:
 ONE_MMA = {0x10: "dQ / T2 issued; before the wait for P", 0x20: "P arrived", 0x30: "dV, next T1 issued; before the wait for dS",
            0x40: "dS arrived", 0x50: "dK issued, previous dQ partial drained"}
 ONE_DRAIN = {7: "wait for a dQ partial", 8: "TMEM load, staging write, reduce-add issue"}
+GEMM_TMA = {1: "stage filled (loads issued); before the wait for a free stage", 2: "a stage is free"}
+GEMM_MMA = {1: "4 MMAs + commit issued; before the wait for the next K block", 2: "K block landed (full)",
+            0x10: "tile done; before the wait for the accumulator to drain", 0x20: "accumulator free (tmem_empty)"}
+GEMM_EPI = {1: "tile stored; before the wait for the next accumulator", 2: "accumulator complete (tmem_full)", 3: "accumulator drained, stores issued"}
 BWD_TAGS = {1: "wait for T1 (scores)", 2: "TMEM load, exp2, P store, arrive", 3: "wait for T2 (dP)",
             4: "dS, store, arrive", 8: "wait for the last accumulate (acc_full)", 9: "epilogue (gradient stores)"}
 
@@ -50,9 +55,42 @@ def _summarise(ev, names, item_tag=0x100):
     return [(k, cnt[k], tot[k] / cnt[k]) for k in tot]
 
 
+def trace_gemm(case, lib):
+    import numpy as np
+    import torch
+    import triton_b200 as tb
+    from triton_b200 import _lib
+    L = _lib.lib()
+    L.b200_trace_read.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
+    buf = np.zeros((REGIONS, EVENTS, 2), dtype=np.uint32)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    n = 8192
+    a = (torch.randn(n, n, generator=g, device="cuda") / n ** 0.5).half()
+    b = (torch.randn(n, n, generator=g, device="cuda") / n ** 0.5).half()
+    if case == "c3":
+        a, sa = tb.quantize_e4m3(a.float() * n ** 0.5)
+        b, sb = tb.quantize_e4m3(b.float() * n ** 0.5)
+        fn = lambda: tb.matmul(a, b, scale_a=sa, scale_b=sb)
+    else:
+        fn = lambda: tb.matmul(a, b)
+    for _ in range(2):
+        fn()
+        _lib.check(L.b200_trace_read(ctypes.c_void_p(buf.ctypes.data), buf.nbytes), "trace_read")
+    t = buf.copy()
+    print(f"gemm {case} 8192^3: CTA 0, mean SM clocks since the previous trace point")
+    for region, label, names in ((0, "TMA warp", GEMM_TMA), (1, "issuing warp, rows 0-127", GEMM_MMA),
+                                 (2, "issuing warp, rows 128-255", GEMM_MMA), (3, "epilogue warp 0", GEMM_EPI)):
+        print(f"  {label}")
+        for key, cnt, mean in _summarise(t[region].tolist(), names, item_tag=1 << 30):
+            print(f"    {key:72s} n={cnt:5d}  {mean:8.0f} clk")
+    st = _lib.status()
+    print("status word", hex(st))
+    return 0 if st == 0 else 1
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["fwd", "bwd", "bwd1"])
+    ap.add_argument("kernel", choices=["fwd", "bwd", "bwd1", "gemm"])
     ap.add_argument("--case", default=None)
     args = ap.parse_args()
     from . import build
@@ -63,6 +101,8 @@ def main():
     import triton_b200 as tb
     from triton_b200 import _lib
     assert _lib._lib is None, "the library was loaded before the trace build was selected"
+    if args.kernel == "gemm":
+        return trace_gemm(args.case or "c2", lib)
     case = args.case or ("c4" if args.kernel == "fwd" else "c5")
     if case == "c4" and args.kernel != "fwd":
         raise SystemExit("the backward traces take --case c5 or long")
@@ -98,12 +138,9 @@ def main():
         for region, label in ((0, "softmax warp 0 of tile 0"), (1, "softmax warp 0 of tile 1")):
             print(f"  {label}")
             for key, n, mean in _summarise(t[region].tolist(), FWD_TAGS):
-                print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
+                print(f"    {key:56s} n={n:5d}  {mean:8.0f} clk")
         print("  MMA warp")
         for key, n, mean in _summarise(t[2].tolist(), FWD_MMA):
-            print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
-        print("  correction warp 0")
-        for key, n, mean in _summarise(t[3].tolist(), FWD_CORR):
             print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
     elif one:
         for region, label, names in ((0, "compute warp 0", ONE_TAGS), (2, "MMA warp", ONE_MMA), (3, "drain warp 0", ONE_DRAIN)):
