@@ -48,6 +48,13 @@ constexpr int FWD_THREADS = 512;   // 8 softmax warps, MMA warp, TMA warp, 6 war
 constexpr int REGS_SOFTMAX = 208, REGS_MMA_TMA = 72, REGS_IDLE = 24;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
+// Column pairs out of every 8 whose exp2 is computed by a cubic on the FMA pipe (0: all on the
+// special-function unit).
+#ifndef B200_FWD_POLY
+#define B200_FWD_POLY 2
+#endif
+constexpr int kPolyStride = 3;  // spreads the chosen pairs over a group of 8 (3 is coprime to 8)
+
 struct FwdParams {
   void* o;
   float* m;  // [Z*H, N] base-2 log-sum-exp of the scaled scores
@@ -515,6 +522,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               p0 = ex2(x0);
               p1 = ex2(x1);
               sum2[k & 1] = add2(sum2[k & 1], pk2(p0, p1));
+            } else if (!FP8 && ((k * kPolyStride) & 7) < B200_FWD_POLY) {
+              // some of the exponentials on the FMA pipe: the special-function unit is the
+              // busiest unit of this loop
+              float x0, x1;
+              upk2(fma2(pk2(__uint_as_float(r[c + 2 * k]), __uint_as_float(r[c + 2 * k + 1])), scale2, neg_m2), x0, x1);
+              ex2_cubic2(x0, x1, p0, p1);
+              sum4[k & 3] += p0 + p1;
             } else {
               p0 = ex2(fmaf(__uint_as_float(r[c + 2 * k]), scale, neg_m));
               p1 = ex2(fmaf(__uint_as_float(r[c + 2 * k + 1]), scale, neg_m));

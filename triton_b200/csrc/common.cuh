@@ -507,6 +507,24 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+// 2^x for a pair of values in (-inf, 9] without the special-function unit: x = n + f with n = floor(x)
+// (the low mantissa bits of x + 1.5 * 2^23 rounded down), 2^f by a cubic with 8.6e-5 relative error
+// (below the rounding of the 16-bit P it feeds), n added to the exponent field.
+__device__ __forceinline__ void ex2_cubic2(float x0, float x1, float& p0, float& p1) {
+  const uint64_t x = pk2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const uint64_t magic = pk2(12582912.f, 12582912.f);
+  uint64_t t;
+  asm("add.rm.f32x2 %0, %1, %2;" : "=l"(t) : "l"(x), "l"(magic));
+  const uint64_t f = sub2(x, sub2(t, magic));
+  uint64_t q = fma2(pk2(0x1.3baaa6p-4f, 0x1.3baaa6p-4f), f, pk2(0x1.d2378ap-3f, 0x1.d2378ap-3f));
+  q = fma2(q, f, pk2(0x1.63e658p-1f, 0x1.63e658p-1f));
+  q = fma2(q, f, pk2(1.f, 1.f));
+  float t0, t1, q0, q1;
+  upk2(t, t0, t1);
+  upk2(q, q0, q1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
 // byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a 128-byte-swizzled tile whose
 // rows are 128 B and whose base is 1024-byte aligned (the pattern TMA SWIZZLE_128B writes)
 __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {

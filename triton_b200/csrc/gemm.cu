@@ -34,6 +34,7 @@
 #include <cuda_fp8.h>
 
 #include <cstdlib>
+#include <type_traits>
 #include <vector>
 
 #include "common.cuh"
@@ -195,36 +196,111 @@ constexpr int pair_staging_warps(int stages, int nb) {
 // a warp-wide store of one row each would touch 32 separate lines per instruction and made the
 // epilogue cost 9 % of a 256 x 256 tile.  Other outputs (fp32, or a C that TMA cannot address) take
 // direct stores.
-template <bool BIAS, bool EXT>
+template <bool BIAS, bool EXT, class Release>
 __device__ __forceinline__ void drain_accumulator_t(const GemmParams& p, const CUtensorMap* tma_c, uint8_t* stg,
                                                     uint32_t taddr, int ncols, int row0, int col0, int lane,
-                                                    float scale, bool vec_ok) {
+                                                    float scale, bool vec_ok, Release&& release_accumulator) {
   if (p.c_tma) {
-#pragma unroll 1
-    for (int c0 = 0; c0 < ncols; c0 += 64) {
-      uint32_t r[64];
-      tmem_ld32(taddr + c0, r);
-      tmem_ld32(taddr + c0 + 32, r + 32);
-      tmem_ld_wait();
+    // The conversions dominate this path (256 values per thread and tile, two epilogue warps per
+    // scheduler), so the activation and the output type are compile-time constants inside it: scale,
+    // (activation,) convert, nothing else per value.
+    auto tma_path = [&](auto leaky_tag, auto bf16_tag) {
+    constexpr bool LEAKY = decltype(leaky_tag)::value, OUT_BF16 = decltype(bf16_tag)::value;
+    // one TMA store of 32 rows x 64 columns through the warp's staging buffer; `word(j)` gives packed
+    // word j (columns 2j, 2j+1) of this lane's row
+    auto emit = [&](auto&& word, int c0) {
       if (lane == 0) tma_store_wait_read<0>();  // the previous store has read the staging buffer
       __syncwarp();
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float v0 = finish<BIAS>(p, __uint_as_float(r[8 * c + 2 * j]), scale, row0 + lane, col0 + c0 + 8 * c + 2 * j);
-          const float v1 = finish<BIAS>(p, __uint_as_float(r[8 * c + 2 * j + 1]), scale, row0 + lane, col0 + c0 + 8 * c + 2 * j + 1);
-          w[j] = (p.out_dtype == B200_BF16) ? pack2<true>(v0, v1) : pack2<false>(v0, v1);
-        }
-        *reinterpret_cast<uint4*>(stg + sw128_offset(lane, c)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
+      for (int c = 0; c < 8; ++c)
+        *reinterpret_cast<uint4*>(stg + sw128_offset(lane, c)) = make_uint4(word(4 * c), word(4 * c + 1), word(4 * c + 2), word(4 * c + 3));
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && row0 < p.M && col0 + c0 < p.N) {
         tma_store_2d(tma_c, stg, col0 + c0, row0);
         tma_store_commit();
       }
+    };
+    // packed word j of the 64 fp32 columns in r that start at column c0 of the tile
+    auto pack_word = [&](const uint32_t* r, int c0, int j) {
+      float v0 = __uint_as_float(r[2 * j]) * scale, v1 = __uint_as_float(r[2 * j + 1]) * scale;
+      if constexpr (LEAKY) {
+        v0 = v0 >= 0.f ? v0 : 0.01f * v0;
+        v1 = v1 >= 0.f ? v1 : 0.01f * v1;
+      }
+      if constexpr (BIAS) {
+        v0 = add_bias(p, v0, row0 + lane, col0 + c0 + 2 * j);
+        v1 = add_bias(p, v1, row0 + lane, col0 + c0 + 2 * j + 1);
+      }
+      return pack2<OUT_BF16>(v0, v1);
+    };
+    if (ncols == 256) {
+      // A 256-column accumulator has no second buffer, so the MMA warps wait for this drain, and a
+      // store cannot reuse the staging buffer before the previous one has read it.  So the
+      // accumulator is emptied into registers first: three of the four 64-column groups are packed
+      // to the output type and kept (96 registers, 32 columns in flight at a time), the fourth goes
+      // to the staging buffer, and the accumulator is released after its last TMEM load; the
+      // stores run under the next tile's MMAs.
+      uint32_t k1[32], k2[32], k3[32];
+      auto load_pack = [&](int c0, uint32_t* k) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c0 + 32 * h, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) k[16 * h + j] = pack_word(r, c0 + 32 * h, j);
+        }
+      };
+      load_pack(64, k1);
+      load_pack(128, k2);
+      load_pack(192, k3);
+      {
+        uint32_t r[32];
+        tmem_ld32(taddr, r);
+        tmem_ld_wait();
+        if (lane == 0) tma_store_wait_read<0>();  // the previous tile's last store has read the staging buffer
+        __syncwarp();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(stg + sw128_offset(lane, c)) =
+              make_uint4(pack_word(r, 0, 4 * c), pack_word(r, 0, 4 * c + 1), pack_word(r, 0, 4 * c + 2), pack_word(r, 0, 4 * c + 3));
+        tmem_ld32(taddr + 32, r);
+        tmem_ld_wait();
+        release_accumulator();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(stg + sw128_offset(lane, 4 + c)) =
+              make_uint4(pack_word(r, 32, 4 * c), pack_word(r, 32, 4 * c + 1), pack_word(r, 32, 4 * c + 2), pack_word(r, 32, 4 * c + 3));
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 < p.M && col0 < p.N) {
+          tma_store_2d(tma_c, stg, col0, row0);
+          tma_store_commit();
+        }
+      }
+      emit([&](int j) { return k1[j]; }, 64);
+      emit([&](int j) { return k2[j]; }, 128);
+      emit([&](int j) { return k3[j]; }, 192);
+      return;
+    }
+#pragma unroll 1
+    for (int c0 = 0; c0 < ncols; c0 += 64) {
+      uint32_t r[64];
+      tmem_ld32(taddr + c0, r);
+      tmem_ld32(taddr + c0 + 32, r + 32);
+      tmem_ld_wait();
+      if (c0 + 64 >= ncols) release_accumulator();
+      emit([&](int j) { return pack_word(r, c0, j); }, c0);
+    }
+    };
+    const bool leaky = p.activation == B200_ACT_LEAKY_RELU, bf = p.out_dtype == B200_BF16;
+    if (leaky) {
+      if (bf) tma_path(std::true_type{}, std::true_type{});
+      else tma_path(std::true_type{}, std::false_type{});
+    } else {
+      if (bf) tma_path(std::false_type{}, std::true_type{});
+      else tma_path(std::false_type{}, std::false_type{});
     }
   } else {
     const int row = row0 + lane;
@@ -235,18 +311,22 @@ __device__ __forceinline__ void drain_accumulator_t(const GemmParams& p, const C
       tmem_ld_wait();
       if (row < p.M) store_chunk32<BIAS, EXT>(p, row, col0 + c0, r, scale, vec_ok);
     }
+    release_accumulator();
   }
 }
 
-template <bool EXT>
+// Drains one warp's part of an accumulator and calls `release` (every thread, once) as soon as the
+// last TMEM load has completed, which on the TMA-store path is before the last stores: the caller
+// passes what tells the MMA warp that the accumulator may be overwritten.
+template <bool EXT, class Release>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUtensorMap* tma_c, uint8_t* stg,
                                                   uint32_t taddr, int ncols, int row0, int col0, int lane,
-                                                  float scale, bool vec_ok) {
+                                                  float scale, bool vec_ok, Release&& release) {
   if constexpr (EXT) {
-    if (p.bias_mode) drain_accumulator_t<true, true>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok);
-    else drain_accumulator_t<false, true>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok);
+    if (p.bias_mode) drain_accumulator_t<true, true>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok, release);
+    else drain_accumulator_t<false, true>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok, release);
   } else {
-    drain_accumulator_t<false, false>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok);
+    drain_accumulator_t<false, false>(p, tma_c, stg, taddr, ncols, row0, col0, lane, scale, vec_ok, release);
   }
 }
 
@@ -479,9 +559,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         drain_softmax(p, tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN,
                       pid_m * BM + half * 128 + quarter * 32, lane, scale);
       } else
-      drain_accumulator<EXT>(p, &tma_c, staging + (warp - 2) * STG_BYTES,
-                        tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
-                        pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
+      {
+        drain_accumulator<EXT>(p, &tma_c, staging + (warp - 2) * STG_BYTES,
+                          tmem_base + ((quarter * 32u) << 16) + (acc + half) * BN, BN,
+                          pid_m * BM + half * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok, [&]() {
+                            tc_fence_before();
+                            mbar_arrive(&tmem_empty[acc]);
+                            if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 3);
+                          });
+        continue;
+      }
       tc_fence_before();
       mbar_arrive(&tmem_empty[acc]);
       if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 3);
@@ -626,7 +713,7 @@ gemm_chain_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     mbar_wait(acc2_full, 0, p.status, SITE_GEMM_TMEM_FULL);
     tc_fence_after();
     drain_accumulator<false>(p, &tma_c, staging + (warp - 2) * STG_BYTES, tmem_base + TM_ACC2 + lane_addr, BN,
-                             m0 + quarter * 32, 0, lane, 1.f, vec_ok);
+                             m0 + quarter * 32, 0, lane, 1.f, vec_ok, []() {});
     if (p.c_tma && lane == 0) tma_store_wait_all<0>();
   }
 
@@ -766,10 +853,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       tc_fence_after();
       drain_accumulator<EXT>(p, &tma_c, staging + (warp - 2) * STG_BYTES,
                         tmem_base + ((quarter * 32u) << 16) + acc * 256, BN,
-                        pid_m * 256 + rank * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(&tmem_empty[acc], 0);  // the leader's barrier
+                        pid_m * 256 + rank * 128 + quarter * 32, pid_n * BN, lane, scale, vec_ok, [&]() {
+                          tc_fence_before();
+                          __syncwarp();
+                          if (lane == 0) mbar_arrive_cluster(&tmem_empty[acc], 0);  // the leader's barrier
+                        });
     }
     if (p.c_tma && lane == 0) tma_store_wait_all<0>();
   }
@@ -1030,9 +1118,10 @@ gemm_grouped_kernel(const GroupDesc* __restrict__ groups, int total_tiles, const
       tc_fence_after();
       drain_accumulator<false>(q, &gd->tc, staging + (warp - 2) * STG_BYTES,
                                tmem_base + ((quarter * 32u) << 16) + acc * BN, BN,
-                               (t / gd->num_pid_n) * BM + quarter * 32, (t % gd->num_pid_n) * BN, lane, 1.f, vec_ok);
-      tc_fence_before();
-      mbar_arrive(&tmem_empty[acc]);
+                               (t / gd->num_pid_n) * BM + quarter * 32, (t % gd->num_pid_n) * BN, lane, 1.f, vec_ok, [&]() {
+                                 tc_fence_before();
+                                 mbar_arrive(&tmem_empty[acc]);
+                               });
     }
     if (any_tma && lane == 0) tma_store_wait_all<0>();
   }
