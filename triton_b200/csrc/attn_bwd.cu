@@ -145,6 +145,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       mbar_init(&sched_empty[i], 9);  // MMA thread + one lane of each compute warp
     }
     fence_barrier_init();
+    cta_wait_flag_clear();
     tma_prefetch_desc(&tm_r1);
     tma_prefetch_desc(&tm_r2);
     tma_prefetch_desc(&tm_u1);
@@ -468,10 +469,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_r1, const __grid_constant
       if (!DQ) store_rows(tm_b, &tm_ob, p.out_b, p.ob_sz, p.ob_sh, p.ob_sn, 1.0f);
       if (warp == 0 && lane == 0) B200_TRACE_EVENT(p.status, DQ ? 1 : 0, 9);
     }
-    if (p.out_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
+    if (p.out_tma && lane == 0) tma_store_wait_read<0>();  // the staging buffer has been read: the CTA may exit, the writes land on their own
   }
 
-  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  cta_linger_after_failure();
   tc_fence_before();
   __syncthreads();
   if (warp == MMA_WARP) {

@@ -150,6 +150,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       mbar_init(&sched_empty[i], 13);  // MMA warp + one lane of each compute and drain warp
     }
     fence_barrier_init();
+    cta_wait_flag_clear();
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
     tma_prefetch_desc(&tm_q);
@@ -172,7 +173,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
   // Every role ends with its own copy of the teardown and returns: nothing is shared after the
   // register budgets have diverged.
   auto teardown = [&](bool owner) {
-    if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+    cta_linger_after_failure();
     tc_fence_before();
     __syncthreads();
     if (owner) {
@@ -402,7 +403,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         tma_store_commit();
       }
     }
-    if (lane == 0) tma_store_wait_all<0>();  // this warp's stores and reduce-adds are complete before the CTA exits
+    if (lane == 0) tma_store_wait_read<0>();  // the staging buffers have been read: the CTA may exit, the writes land on their own
     __syncwarp();
     teardown(false);
     return;

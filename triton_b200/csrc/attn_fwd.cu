@@ -126,6 +126,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr int TILE = Cfg::TILE_BYTES, NST = Cfg::KV_STAGES, TILES = Cfg::TILES;
   constexpr int ITEM_ROWS = TILES * BLK;
   constexpr int MMA_WARP = 8, TMA_WARP = 9;
+  constexpr bool WAIT_PAUSE = (D != 64);  // see mbar_wait_slow
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
@@ -169,6 +170,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(&kv_empty[s], 1);
     }
     fence_barrier_init();
+    cta_wait_flag_clear();
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
@@ -196,7 +198,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // every budget has).
   auto teardown = [&](bool owner) {
     // after a recorded failure give copies in flight time to land before the CTA exits
-    if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+    cta_linger_after_failure();
     tc_fence_before();
     __syncthreads();
     if (owner) {
@@ -222,7 +224,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       for (uint32_t n = 0;; ++n) {
         const int w = atomicAdd(p.sched_counter, 1);
         const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
-        mbar_wait(&sched_empty[slot], sph ^ 1u, p.status, SITE_FWD_SCHED);
+        mbar_wait<WAIT_PAUSE>(&sched_empty[slot], sph ^ 1u, p.status, SITE_FWD_SCHED);
         sched_item[slot] = w;
         mbar_arrive(&sched_full[slot]);
         // every CTA draws exactly one ticket past the end: the last of them puts the zero back for the
@@ -230,14 +232,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         if (w == p.total_items + (int)gridDim.x - 1) atomicExch(p.sched_counter, 0);
         if (w >= p.total_items) break;
         const Item it = decode_item<TILES>(p, w);
-        mbar_wait(q_empty, (n & 1u) ^ 1u, p.status, SITE_FWD_Q);  // previous item's S MMAs are done with Q
+        mbar_wait<WAIT_PAUSE>(q_empty, (n & 1u) ^ 1u, p.status, SITE_FWD_Q);  // previous item's S MMAs are done with Q
         for (int i = 0; i < TILES; ++i) {
           mbar_expect_tx(&q_full[i], TILE);
           load_tile<D, FP8>(sq + i * TILE, &tm_q, &q_full[i], it.qb * ITEM_ROWS + i * BLK, it.h, it.z);
         }
         for (int j = 0; j < it.nmax; ++j) {
           for (int kv = 0; kv < 2; ++kv) {  // K_j then V_j
-            mbar_wait(&kv_empty[s], ph ^ 1u, p.status, SITE_FWD_KV_EMPTY);
+            mbar_wait<WAIT_PAUSE>(&kv_empty[s], ph ^ 1u, p.status, SITE_FWD_KV_EMPTY);
             mbar_expect_tx(&kv_full[s], TILE);
             load_tile<D, FP8>(skv + s * TILE, kv == 0 ? &tm_k : &tm_v, &kv_full[s], j * BLK, it.h, it.z, kv == 1);
             if (++s == NST) { s = 0; ph ^= 1u; }
@@ -287,7 +289,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x10 | (i << 1) | h);
-          mbar_wait(&p_full[2 * i + h], parity, p.status, SITE_FWD_P_FULL);
+          mbar_wait<WAIT_PAUSE>(&p_full[2 * i + h], parity, p.status, SITE_FWD_P_FULL);
           if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x20 | (i << 1) | h);
           tc_fence_after();
           if constexpr (FP8) {
@@ -305,7 +307,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
       for (uint32_t n = 0;; ++n) {
         const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
-        mbar_wait(&sched_full[slot], sph, p.status, SITE_FWD_SCHED);
+        mbar_wait<WAIT_PAUSE>(&sched_full[slot], sph, p.status, SITE_FWD_SCHED);
         const int w = sched_item[slot];
         __syncwarp();
         if (lane == 0) mbar_arrive(&sched_empty[slot]);
@@ -314,11 +316,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const int n0 = it.n0, n1 = it.n1, nmax = it.nmax;
 
         // prologue: S_0(0), S_1(0) on K_0
-        mbar_wait(&kv_full[s], ph, p.status, SITE_FWD_KV_FULL);
-        mbar_wait(&q_full[0], n & 1u, p.status, SITE_FWD_Q);
+        mbar_wait<WAIT_PAUSE>(&kv_full[s], ph, p.status, SITE_FWD_KV_FULL);
+        mbar_wait<WAIT_PAUSE>(&q_full[0], n & 1u, p.status, SITE_FWD_Q);
         issue_s(0, s);
         if constexpr (TILES == 2) {
-          mbar_wait(&q_full[1], n & 1u, p.status, SITE_FWD_Q);
+          mbar_wait<WAIT_PAUSE>(&q_full[1], n & 1u, p.status, SITE_FWD_Q);
           issue_s(1, s);
         }
         tc_commit_elect(&kv_empty[s]);
@@ -333,17 +335,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             // the next scores first: S_i(j+1) only needs the S buffer, which is free once the
             // softmax warps have loaded S_i(j)
             if (more0) {
-              mbar_wait(&s_free[0], fcnt[0]++ & 1u, p.status, SITE_FWD_S_EMPTY);
+              mbar_wait<WAIT_PAUSE>(&s_free[0], fcnt[0]++ & 1u, p.status, SITE_FWD_S_EMPTY);
               tc_fence_after();
-              mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+              mbar_wait<WAIT_PAUSE>(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
               issue_s(0, ks);
             } else if (j < n0) {
               ++fcnt[0];  // the tile's last block: its arrival is not waited for, the count goes on
             }
             if (more1) {
-              mbar_wait(&s_free[1], fcnt[1]++ & 1u, p.status, SITE_FWD_S_EMPTY);
+              mbar_wait<WAIT_PAUSE>(&s_free[1], fcnt[1]++ & 1u, p.status, SITE_FWD_S_EMPTY);
               tc_fence_after();
-              mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+              mbar_wait<WAIT_PAUSE>(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
               issue_s(1, ks);
               tc_commit_elect(&kv_empty[ks]);
               if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
@@ -351,7 +353,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               ++fcnt[1];
             }
             if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
-            mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
+            mbar_wait<WAIT_PAUSE>(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
             if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x60);
             if (j < n0) {
               issue_pv(0, vs, j > 0, pcnt[0]++ & 1u);
@@ -365,14 +367,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (more1) advance();
           } else {
             if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
-            mbar_wait(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
+            mbar_wait<WAIT_PAUSE>(&kv_full[vs], vph, p.status, SITE_FWD_KV_FULL);
             if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x60);
             if (j < n0) {
               issue_pv(0, vs, j > 0, pcnt[0]++ & 1u);
               if (TILES == 1) tc_commit_elect(&kv_empty[vs]);
               if (j == n0 - 1) tc_commit_elect(&o_full[0]);
               if (more0) {
-                mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+                mbar_wait<WAIT_PAUSE>(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
                 issue_s(0, ks);
                 if (TILES == 1) {
                   tc_commit_elect(&kv_empty[ks]);
@@ -386,7 +388,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               tc_commit_elect(&kv_empty[vs]);
               if (j == n1 - 1) tc_commit_elect(&o_full[1]);
               if (more1) {
-                mbar_wait(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
+                mbar_wait<WAIT_PAUSE>(&kv_full[ks], kph, p.status, SITE_FWD_KV_FULL);
                 issue_s(1, ks);
                 tc_commit_elect(&kv_empty[ks]);
                 if (j + 2 == n1) tc_commit_elect(q_empty);  // that was the item's last S: the Q tiles may be replaced
@@ -417,7 +419,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t slot = n & 1u, sph = (n >> 1) & 1u;
       int w = 0;
       if (lane == 0) {
-        mbar_wait(&sched_full[slot], sph, p.status, SITE_FWD_SCHED);
+        mbar_wait<WAIT_PAUSE>(&sched_full[slot], sph, p.status, SITE_FWD_SCHED);
         w = sched_item[slot];
         mbar_arrive(&sched_empty[slot]);
       }
@@ -433,7 +435,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (traced) B200_TRACE_EVENT(p.status, i, 0x100 | nb);
 
       for (int j = 0; j < nb; ++j, ++scnt) {
-        mbar_wait(&s_full[i], scnt & 1u, p.status, SITE_FWD_S_FULL);
+        mbar_wait<WAIT_PAUSE>(&s_full[i], scnt & 1u, p.status, SITE_FWD_S_FULL);
         if (traced) B200_TRACE_EVENT(p.status, i, 1);
         tc_fence_after();
         const int col0 = j * BLK;
@@ -474,7 +476,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // item's first block the epilogue's wait for the last P V of the previous item has seen to that
         auto wait_pv = [&]() {
           if (SEP_P && j > 0) {
-            mbar_wait(&pv_done[i], (scnt - 1u) & 1u, p.status, SITE_FWD_O_READY);
+            mbar_wait<WAIT_PAUSE>(&pv_done[i], (scnt - 1u) & 1u, p.status, SITE_FWD_O_READY);
             tc_fence_after();
           }
         };
@@ -571,7 +573,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // epilogue: O / l and M.  It overlaps the next item's Q / K loads and first S MMAs; the next
       // item's first P V (which overwrites O) needs this tile's next P, i.e. comes after these
       // reads in program order.
-      mbar_wait(&o_full[i], n & 1u, p.status, SITE_FWD_O_FULL);
+      mbar_wait<WAIT_PAUSE>(&o_full[i], n & 1u, p.status, SITE_FWD_O_FULL);
       if (traced) B200_TRACE_EVENT(p.status, i, 8);
       tc_fence_after();
       const float inv_l = 1.f / l;
@@ -675,7 +677,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       if (valid && p.row_max) p.row_max[(long long)it.zh * p.N + row] = m_true;
       if (traced) B200_TRACE_EVENT(p.status, i, 9);
     }
-    if (p.o_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
+    if (p.o_tma && lane == 0) tma_store_wait_read<0>();  // the staging buffer has been read: the CTA may exit, the writes land on their own
     teardown(false);
   }
 }

@@ -232,6 +232,7 @@ __global__ void __launch_bounds__(64, 1) wait_timeout_selftest_kernel(unsigned* 
   if (threadIdx.x == 0) {
     mbar_init(&never, 1);
     fence_barrier_init();
+    cta_wait_flag_clear();
   }
   if (warp == 0) {
     tmem_alloc(&tmem_slot, 32);
@@ -245,7 +246,7 @@ __global__ void __launch_bounds__(64, 1) wait_timeout_selftest_kernel(unsigned* 
     if (!mbar_try_wait(&never, 0)) mbar_wait_slow(&never, 0, status, SITE_SELFTEST, limit_ns);
   }
   __syncwarp();
-  if (*(volatile unsigned*)status != 0) __nanosleep(100000);
+  cta_linger_after_failure();
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {

@@ -73,6 +73,19 @@ __device__ __forceinline__ void record_wait_failure(unsigned* status, unsigned c
     }
   }
 }
+// One word of shared memory per CTA, set when one of the CTA's waits gave up (its own limit, or a
+// failure that some thread of the grid had recorded): the teardown of a kernel looks at it, not at
+// the status word in device memory, whose load would put a memory round trip at the end of every
+// CTA.  Cleared by the thread that initialises the barriers.
+__device__ __forceinline__ unsigned* cta_wait_flag() {
+  __shared__ unsigned flag;
+  return &flag;
+}
+__device__ __forceinline__ void cta_wait_flag_clear() { *reinterpret_cast<volatile unsigned*>(cta_wait_flag()) = 0u; }
+// after a wait of this CTA gave up: give copies in flight time to land before the CTA exits
+__device__ __forceinline__ void cta_linger_after_failure() {
+  if (*reinterpret_cast<volatile unsigned*>(cta_wait_flag()) != 0u) __nanosleep(100000);
+}
 // Bounded wait.  Returns false (and records `site`) when the limit is reached or another
 // thread already recorded a failure.  Out of line by default, so that the spin loop stays out of
 // the callers' hot paths; kernels that re-divide registers between warpgroups (setmaxnreg) define
@@ -83,15 +96,34 @@ __device__ __forceinline__ void record_wait_failure(unsigned* status, unsigned c
 #else
 #define B200_WAIT_SLOW_ATTR __noinline__
 #endif
+// STATUS_FIRST: the slow path begins with a look at the status word, i.e. with one memory round
+// trip (~700 clk) before the second poll.  Off by default: most waits end within a few hundred
+// clocks and that load would set a floor under every hand-over (forward attention at head dim 64:
+// 480 -> 540 TFLOP/s without it).  The forward attention kernel at head dims 128 and 256 turns it
+// on: there the pause measured +3 % (C4 1010 -> 1045 TFLOP/s, non-causal 1225 -> 1285), and no
+// pause at a single wait site, timed sleep or suspend hint reproduced it.
+template <bool STATUS_FIRST = false>
 static __device__ B200_WAIT_SLOW_ATTR bool mbar_wait_slow(uint64_t* bar, uint32_t parity, unsigned* status, unsigned site,
                                                    unsigned long long limit_ns = kWaitLimitNs) {
-  if (*(volatile unsigned*)status != 0) return false;
-  const unsigned long long t0 = gtimer_ns();
+  if constexpr (STATUS_FIRST) {
+    if (*(volatile unsigned*)status != 0) {
+      *reinterpret_cast<volatile unsigned*>(cta_wait_flag()) = 1u;
+      return false;
+    }
+  }
+  // the status word and the timer are looked at every 64 polls
+  unsigned long long t0 = 0;
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63u) == 0) {
-      if (*(volatile unsigned*)status != 0) return false;
-      if (gtimer_ns() - t0 > limit_ns) {
+      if (*(volatile unsigned*)status != 0) {
+        *reinterpret_cast<volatile unsigned*>(cta_wait_flag()) = 1u;
+        return false;
+      }
+      const unsigned long long now = gtimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > limit_ns) {
+        *reinterpret_cast<volatile unsigned*>(cta_wait_flag()) = 1u;
         record_wait_failure(status, site | ((parity & 1u) << 8) | ((blockIdx.x & 0xFFFFu) << 16));
         return false;
       }
@@ -99,9 +131,10 @@ static __device__ B200_WAIT_SLOW_ATTR bool mbar_wait_slow(uint64_t* bar, uint32_
   }
   return true;
 }
+template <bool STATUS_FIRST = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned* status, unsigned site) {
   if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, status, site);
+  return mbar_wait_slow<STATUS_FIRST>(bar, parity, status, site);
 }
 
 // generic-proxy writes to shared memory -> visible to the async proxy (TMA store, tcgen05.mma)

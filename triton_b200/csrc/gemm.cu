@@ -451,6 +451,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     }
     if (p.c_tma) tma_prefetch_desc(&tma_c);
     fence_barrier_init();
+    cta_wait_flag_clear();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
   }
@@ -464,24 +465,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t s = 0, ph = 0;
-      for (int work = blockIdx.x; work < p.num_tiles * p.splits; work += gridDim.x) {
-        const int tile = work % p.num_tiles, split = work / p.num_tiles;
-        int pid_m, pid_n;
-        tile_coords(p, tile, pid_m, pid_n);
-        const int m0 = pid_m * BM, n0 = pid_n * BN;
-        const int kb_end = min(p.num_k, (split + 1) * p.kb_per_split);
-        for (int kb = split * p.kb_per_split; kb < kb_end; ++kb) {
-          B200_TRACE_EVENT(p.status, 0, 1);
-          mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
-          B200_TRACE_EVENT(p.status, 0, 2);
-          mbar_expect_tx(&full[s], STAGE_BYTES);
-          uint8_t* a_dst = smem + s * STAGE_BYTES;
-          load_operand<false>(p.ga, &tma_a, a_dst, &full[s], kb * p.bk_elems, m0);
-          load_operand<false>(p.gb, &tma_b, a_dst + A_BYTES, &full[s], kb * p.bk_elems, n0);
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
+    // TMA producer.  The warp stays converged and every box of a stage has a lane of its own (K-major
+    // operand: one box; MN-major: one per 128 bytes of M / N), so the loads of a stage go out as one
+    // instruction instead of one after the other from a lone lane: the issue loop of this warp, not
+    // the data, was what a short K loop waited for (one-wave problems: 0.33 us per K block).
+    const uint32_t n_a = p.ga.mn_major ? p.ga.nbox : 1u, n_b = p.gb.mn_major ? p.gb.nbox : 1u;
+    const bool has_box = (uint32_t)lane < n_a + n_b, is_b = (uint32_t)lane >= n_a;
+    const uint32_t box = is_b ? lane - n_a : lane;
+    const uint32_t mn_major = is_b ? p.gb.mn_major : p.ga.mn_major;
+    const uint32_t dst_off = (is_b ? A_BYTES : 0u) + (mn_major ? box * (is_b ? p.gb.box_bytes : p.ga.box_bytes) : 0u);
+    const int mn_off = mn_major ? (int)(box * (is_b ? p.gb.box_mn : p.ga.box_mn)) : 0;
+    const CUtensorMap* map = is_b ? &tma_b : &tma_a;
+    uint32_t s = 0, ph = 0;
+    for (int work = blockIdx.x; work < p.num_tiles * p.splits; work += gridDim.x) {
+      const int tile = work % p.num_tiles, split = work / p.num_tiles;
+      int pid_m, pid_n;
+      tile_coords(p, tile, pid_m, pid_n);
+      const int mn0 = (is_b ? pid_n * BN : pid_m * BM) + mn_off;
+      const int kb_end = min(p.num_k, (split + 1) * p.kb_per_split);
+      for (int kb = split * p.kb_per_split; kb < kb_end; ++kb) {
+        if (lane == 0) B200_TRACE_EVENT(p.status, 0, 1);
+        mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
+        if (lane == 0) B200_TRACE_EVENT(p.status, 0, 2);
+        if (lane == 0) mbar_expect_tx(&full[s], STAGE_BYTES);
+        if (has_box) {
+          const int k0 = kb * p.bk_elems;
+          tma_load_2d(smem + s * STAGE_BYTES + dst_off, map, &full[s], mn_major ? mn0 : k0, mn_major ? k0 : mn0);
         }
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
     }
     __syncwarp();
@@ -500,6 +511,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const uint32_t ka = p.ga.kstep_bytes >> 4, kb16 = p.gb.kstep_bytes >> 4;
       const uint32_t idesc = p.idesc;
       const bool fp8 = p.fp8 != 0;
+      uint32_t a_off[KBYTES / 32], b_off[KBYTES / 32];  // descriptor advance of the four K steps of a stage
+#pragma unroll
+      for (int k = 0; k < KBYTES / 32; ++k) {
+        a_off[k] = h * ((128 * KBYTES) >> 4) + k * ka;
+        b_off[k] = k * kb16;
+      }
       uint32_t s = 0, ph = 0, ti = 0;
       for (int work = blockIdx.x; work < p.num_tiles * p.splits; work += gridDim.x, ++ti) {
         const int split = work / p.num_tiles;
@@ -509,25 +526,26 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         mbar_wait(&tmem_empty[acc], ((ti / NACC) & 1u) ^ 1u, p.status, SITE_GEMM_TMEM_EMPTY);
         if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 0x20);
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        uint32_t accum = 0;
-        for (int kb = 0; kb < kb_cnt; ++kb) {
-          if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 1);
-          mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);  // TMA bytes landed
-          if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 2);
-          const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
+        const uint32_t d_tmem = tmem_base + acc * BN + h * BN;
+        // the operand type is fixed outside the K loop: nothing between two MMAs but the descriptor sums
+        auto k_loop = [&](auto fp8_tag) {
+          constexpr bool F8 = decltype(fp8_tag)::value;
+          uint32_t accum = 0;
+          for (int kb = 0; kb < kb_cnt; ++kb) {
+            if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 1);
+            mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);  // TMA bytes landed
+            if (lane == 0) B200_TRACE_EVENT(p.status, 1 + h, 2);
+            const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
-          for (int k = 0; k < KBYTES / 32; ++k) {
-            const uint64_t da = das + (h * ((128 * KBYTES) >> 4) + k * ka);  // rows [128h, 128h+128): 16 KiB apart
-            if (fp8)
-              umma_ss_elect<true>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
-            else
-              umma_ss_elect<false>(d_tmem + h * BN, da, dbs + k * kb16, idesc, accum);
+            for (int k = 0; k < KBYTES / 32; ++k)  // rows [128h, 128h+128) of A: 16 KiB apart
+              umma_ss_elect<F8>(d_tmem, das + a_off[k], dbs + b_off[k], idesc, k == 0 ? accum : 1u);
             accum = 1;
+            tc_commit_elect(&empty[s]);
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
           }
-          tc_commit_elect(&empty[s]);
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
-        }
+        };
+        if (fp8) k_loop(std::true_type{});
+        else k_loop(std::false_type{});
         tc_commit_elect(&tmem_full[acc]);
       }
     }
@@ -573,11 +591,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       mbar_arrive(&tmem_empty[acc]);
       if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 3);
     }
-    if (p.c_tma && lane == 0) tma_store_wait_all<0>();  // this warp's stores are complete before the CTA exits
+    if (p.c_tma && lane == 0) tma_store_wait_read<0>();  // the staging buffer has been read: the CTA may exit, the writes land on their own
   }
 
   // teardown: after a recorded failure give copies in flight time to land before the CTA exits
-  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  cta_linger_after_failure();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -628,6 +646,7 @@ gemm_chain_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     mbar_init(z_full, 4);  // one arrival per conversion warp
     mbar_init(acc2_full, 1);
     fence_barrier_init();
+    cta_wait_flag_clear();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     tma_prefetch_desc(&tma_w);
@@ -714,10 +733,10 @@ gemm_chain_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_consta
     tc_fence_after();
     drain_accumulator<false>(p, &tma_c, staging + (warp - 2) * STG_BYTES, tmem_base + TM_ACC2 + lane_addr, BN,
                              m0 + quarter * 32, 0, lane, 1.f, vec_ok, []() {});
-    if (p.c_tma && lane == 0) tma_store_wait_all<0>();
+    if (p.c_tma && lane == 0) tma_store_wait_read<0>();
   }
 
-  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  cta_linger_after_failure();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -756,6 +775,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();  // 0 = leader
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  B200_TRACE_DECL;  // trace builds (leader of pair 0): region 0 = TMA warp, 1 = issuing warp, 3 = first epilogue warp
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -767,6 +787,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       mbar_init(&tmem_empty[i], 8);  // one arrival per epilogue warp of both CTAs
     }
     fence_barrier_init();
+    cta_wait_flag_clear();
     tma_prefetch_desc(&tma_a);
     tma_prefetch_desc(&tma_b);
     if (p.c_tma) tma_prefetch_desc(&tma_c);
@@ -788,7 +809,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tile_coords(p, tile, pid_m, pid_n);
         const int m0 = pid_m * 256 + rank * 128, n0 = pid_n * BN + rank * HALF_N;
         for (int kb = 0; kb < p.num_k; ++kb) {
+          B200_TRACE_EVENT(p.status, 0, 1);
           mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
+          B200_TRACE_EVENT(p.status, 0, 2);
           if (rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
           uint8_t* a_dst = smem + s * STAGE_BYTES;
           load_operand<true>(p.ga, &tma_a, a_dst, &full[s], kb * p.bk_elems, m0);
@@ -811,12 +834,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       uint32_t s = 0, ph = 0, ti = 0;
       for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++ti) {
         const uint32_t acc = ti % NACC;
+        if (lane == 0) B200_TRACE_EVENT(p.status, 1, 0x10);
         mbar_wait(&tmem_empty[acc], ((ti / NACC) & 1u) ^ 1u, p.status, SITE_GEMM_TMEM_EMPTY);
+        if (lane == 0) B200_TRACE_EVENT(p.status, 1, 0x20);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * 256;
         uint32_t accum = 0;
         for (int kb = 0; kb < p.num_k; ++kb) {
+          if (lane == 0) B200_TRACE_EVENT(p.status, 1, 1);
           mbar_wait(&full[s], ph, p.status, SITE_GEMM_FULL);
+          if (lane == 0) B200_TRACE_EVENT(p.status, 1, 2);
           const uint64_t das = da0 + s * (STAGE_BYTES >> 4), dbs = db0 + s * (STAGE_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < KBYTES / 32; ++k) {
@@ -849,7 +876,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       int pid_m, pid_n;
       tile_coords(p, tile, pid_m, pid_n);
       const uint32_t acc = ti % NACC;
+      if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 1);
       mbar_wait(&tmem_full[acc], (ti / NACC) & 1u, p.status, SITE_GEMM_TMEM_FULL);
+      if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 2);
       tc_fence_after();
       drain_accumulator<EXT>(p, &tma_c, staging + (warp - 2) * STG_BYTES,
                         tmem_base + ((quarter * 32u) << 16) + acc * 256, BN,
@@ -857,12 +886,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                           tc_fence_before();
                           __syncwarp();
                           if (lane == 0) mbar_arrive_cluster(&tmem_empty[acc], 0);  // the leader's barrier
+                          if (warp == 2 && lane == 0) B200_TRACE_EVENT(p.status, 3, 3);
                         });
     }
-    if (p.c_tma && lane == 0) tma_store_wait_all<0>();
+    if (p.c_tma && lane == 0) tma_store_wait_read<0>();
   }
 
-  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  cta_linger_after_failure();
   tc_fence_before();
   cluster_sync();  // neither CTA may exit (or free TMEM) while its peer can still reach it
   if (warp == 1) {
@@ -1039,6 +1069,7 @@ gemm_grouped_kernel(const GroupDesc* __restrict__ groups, int total_tiles, const
       mbar_init(&tmem_empty[i], BM);
     }
     fence_barrier_init();
+    cta_wait_flag_clear();
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, TMEM_COLS);
@@ -1050,23 +1081,30 @@ gemm_grouped_kernel(const GroupDesc* __restrict__ groups, int total_tiles, const
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t s = 0, ph = 0;
-      int g = 0;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-        g = find_group(groups, g, tile);
-        const GroupDesc* gd = groups + g;
-        const int t = tile - gd->tile_start;
-        const int m0 = (t / gd->num_pid_n) * BM, n0 = (t % gd->num_pid_n) * BN;
-        const int num_k = gd->num_k;
-        for (int kb = 0; kb < num_k; ++kb) {
-          mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
-          mbar_expect_tx(&full[s], STAGE_BYTES);
-          uint8_t* a_dst = smem + s * STAGE_BYTES;
-          load_operand<false>(p.ga, &gd->ta, a_dst, &full[s], kb * p.bk_elems, m0);
-          load_operand<false>(p.gb, &gd->tb, a_dst + A_BYTES, &full[s], kb * p.bk_elems, n0);
-          if (++s == STAGES) { s = 0; ph ^= 1u; }
+    // converged warp, one lane per TMA box of a stage (see gemm_kernel)
+    const uint32_t n_a = p.ga.mn_major ? p.ga.nbox : 1u, n_b = p.gb.mn_major ? p.gb.nbox : 1u;
+    const bool has_box = (uint32_t)lane < n_a + n_b, is_b = (uint32_t)lane >= n_a;
+    const uint32_t box = is_b ? lane - n_a : lane;
+    const uint32_t mn_major = is_b ? p.gb.mn_major : p.ga.mn_major;
+    const uint32_t dst_off = (is_b ? A_BYTES : 0u) + (mn_major ? box * (is_b ? p.gb.box_bytes : p.ga.box_bytes) : 0u);
+    const int mn_off = mn_major ? (int)(box * (is_b ? p.gb.box_mn : p.ga.box_mn)) : 0;
+    uint32_t s = 0, ph = 0;
+    int g = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      g = find_group(groups, g, tile);
+      const GroupDesc* gd = groups + g;
+      const int t = tile - gd->tile_start;
+      const int mn0 = (is_b ? (t % gd->num_pid_n) * BN : (t / gd->num_pid_n) * BM) + mn_off;
+      const CUtensorMap* map = is_b ? &gd->tb : &gd->ta;
+      const int num_k = gd->num_k;
+      for (int kb = 0; kb < num_k; ++kb) {
+        mbar_wait(&empty[s], ph ^ 1u, p.status, SITE_GEMM_EMPTY);
+        if (lane == 0) mbar_expect_tx(&full[s], STAGE_BYTES);
+        if (has_box) {
+          const int k0 = kb * p.bk_elems;
+          tma_load_2d(smem + s * STAGE_BYTES + dst_off, map, &full[s], mn_major ? mn0 : k0, mn_major ? k0 : mn0);
         }
+        if (++s == STAGES) { s = 0; ph ^= 1u; }
       }
     }
     __syncwarp();
@@ -1123,10 +1161,10 @@ gemm_grouped_kernel(const GroupDesc* __restrict__ groups, int total_tiles, const
                                  mbar_arrive(&tmem_empty[acc]);
                                });
     }
-    if (any_tma && lane == 0) tma_store_wait_all<0>();
+    if (any_tma && lane == 0) tma_store_wait_read<0>();
   }
 
-  if (*(volatile unsigned*)p.status != 0) __nanosleep(100000);
+  cta_linger_after_failure();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -1289,19 +1327,24 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     bm = force / 1000;
     bn = force % 1000;
   } else {
-    // Pick the shape with the smallest estimated time: waves x (tile time + fixed cost).  Per-SM
-    // rates relative to the 256 x 256 tile (measured on multi-wave problems: 1.17, 1.02, 0.70,
-    // 0.37 PFLOP/s at 4096^3) and about 4 us of prologue / epilogue per tile.  On large problems
-    // the single-CTA 256 x 256 shape also beat the pair shapes for every dtype (fp16 1.41 vs 1.27
-    // PFLOP/s, e4m3 2.85 vs 2.66 on the same GPU); those stay selectable through B200_GEMM_TILE.
-    struct Cand { int bm, bn; double rate; };
-    const Cand cands[4] = {{256, 256, 1.0}, {128, 256, 0.88}, {128, 128, 0.60}, {128, 64, 0.32}};
+    // Pick the shape with the smallest estimated time: waves x (K blocks x time per K block + time
+    // per tile).  The per-K-block times (us, one 128-byte K block, any operand type) are measured on
+    // square fp16 problems from 1024 to 8192: the 128-row shapes are bound by the issue loops and,
+    // with every SM busy, by the L2 -> shared-memory fill (a 128 x 256 tile draws 96 B/clk/SM), the
+    // 256 x 256 shape by the tensor pipe; the per-tile time is the part of the epilogue and tile
+    // turn-around that the next tile's main loop does not cover.  The model reproduces the measured
+    // order of the shapes at every size of that sweep (e.g. 2304: 128 x 128 in three waves before
+    // 256 x 256 in a 55 % wave; 3584: 128 x 256).  The pair shapes (`cta_group::2`) never won a size:
+    // 256 x 256 on a pair has the fill traffic per flop of a 128 x 256 tile, 256 x 512 has no second
+    // accumulator; they stay selectable through B200_GEMM_TILE.
+    struct Cand { int bm, bn; double kb_us, tile_us; };
+    const Cand cands[4] = {{256, 256, 0.68, 1.0}, {128, 256, 0.36, 0.3}, {128, 128, 0.21, 0.3}, {128, 64, 0.20, 0.3}};
+    const int num_k_est = (int)(((long long)K * elt + KBYTES - 1) / KBYTES);
     double best = 1e300;
     for (const Cand& cd : cands) {
       const long long t = tiles(cd.bm, cd.bn);
       const long long waves = (t + ctx->sm_count - 1) / ctx->sm_count;
-      const double tile_us = 2.0 * cd.bm * cd.bn * (double)K / (7.9e6 * cd.rate) + 4.0;
-      const double est = (double)waves * tile_us;
+      const double est = (double)waves * (num_k_est * cd.kb_us + cd.tile_us);
       if (est < best) { best = est; bm = cd.bm; bn = cd.bn; }
     }
   }

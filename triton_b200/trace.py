@@ -64,7 +64,7 @@ def trace_gemm(case, lib):
     L.b200_trace_read.argtypes = [ctypes.c_void_p, ctypes.c_size_t]
     buf = np.zeros((REGIONS, EVENTS, 2), dtype=np.uint32)
     g = torch.Generator(device="cuda").manual_seed(0)
-    n = 8192
+    n = {"c1": 512, "n1024": 1024, "n2048": 2048}.get(case, 8192)
     a = (torch.randn(n, n, generator=g, device="cuda") / n ** 0.5).half()
     b = (torch.randn(n, n, generator=g, device="cuda") / n ** 0.5).half()
     if case == "c3":
@@ -77,7 +77,13 @@ def trace_gemm(case, lib):
         fn()
         _lib.check(L.b200_trace_read(ctypes.c_void_p(buf.ctypes.data), buf.nbytes), "trace_read")
     t = buf.copy()
-    print(f"gemm {case} 8192^3: CTA 0, mean SM clocks since the previous trace point")
+    if os.environ.get("B200_TRACE_RAW"):  # the timeline itself (small cases): clocks since the CTA's first event
+        firsts = [int(t[r][0][1]) for r in range(REGIONS) if t[r][0][0] or t[r][0][1]]
+        t_min = min(firsts) if firsts else 0
+        for region in range(REGIONS):
+            ev = [(int(tag), (int(clk) - t_min) & 0xFFFFFFFF) for tag, clk in t[region].tolist() if tag or clk][:48]
+            print(f"  region {region}: " + " ".join(f"{tag:x}@{clk}" for tag, clk in ev))
+    print(f"gemm {case} {n}^3: CTA 0, mean SM clocks since the previous trace point")
     for region, label, names in ((0, "TMA warp", GEMM_TMA), (1, "issuing warp, rows 0-127", GEMM_MMA),
                                  (2, "issuing warp, rows 128-255", GEMM_MMA), (3, "epilogue warp 0", GEMM_EPI)):
         print(f"  {label}")
