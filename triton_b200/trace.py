@@ -149,6 +149,12 @@ def main():
         for key, n, mean in _summarise(t[2].tolist(), FWD_MMA):
             print(f"    {key:48s} n={n:5d}  {mean:8.0f} clk")
     elif one:
+        if os.environ.get("B200_TRACE_RAW"):  # the timeline itself: clocks since the CTA's first event
+            firsts = [int(t[r][0][1]) for r in range(REGIONS) if t[r][0][0] or t[r][0][1]]
+            t_min = min(firsts) if firsts else 0
+            for region in (0, 2, 3):
+                ev = [(int(tag), (int(clk) - t_min) & 0xFFFFFFFF) for tag, clk in t[region].tolist() if tag or clk][:int(os.environ["B200_TRACE_RAW"])]
+                print(f"  region {region}: " + " ".join(f"{tag:x}@{clk}" for tag, clk in ev))
         for region, label, names in ((0, "compute warp 0", ONE_TAGS), (2, "MMA warp", ONE_MMA), (3, "drain warp 0", ONE_DRAIN)):
             print(f"  {label}")
             for key, n, mean in _summarise(t[region].tolist(), names):
