@@ -296,6 +296,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
           tc_fence_after();
           issue_acc(tm_dk, tm_t2, dun_q, it > 0);  // dK += dS Q
           tc_commit_elect(&empty[cs]);  // that was the last read of Q_t and dO_t: the stage refills while dQ runs
+          if (!more) tc_commit_elect(acc_full);  // dK and dV of the item are final: they leave TMEM while the last dQ product runs
           // dQ partial = dS^T K: the previous partial must have left TMEM
           mbar_wait(dq_free, (cnt & 1u) ^ 1u, p.status, SITE_BWD_FREE);
           if (lane == 0) B200_TRACE_EVENT(p.status, 2, 0x50);
@@ -311,7 +312,6 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
           }
           s = ns; ph = nph;
         }
-        tc_commit_elect(acc_full);
         tc_commit_elect(&r_empty[slot]);  // the item's last MMAs (dQ reads K) are behind this
       }
     }
@@ -336,7 +336,48 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
       w = __shfl_sync(0xffffffffu, w, 0);
       if (w >= p.total_items) break;
       const FusedItem item(p, w);
+      // the item's dK and dV: this warp's 32 rows, 64 columns each = one box of 128-byte lines per
+      // gradient, through the same two staging boxes as the dQ partials
+      auto write_dk_dv = [&]() {
+        mbar_wait(acc_full, n & 1u, p.status, SITE_BWD_ACC_FULL);
+        tc_fence_after();
+        if (lane == 0) tma_store_wait_read<0>();  // the last reduce-adds have read the staging boxes
+        __syncwarp();
+#pragma unroll 1
+        for (int g = 0; g < 2; ++g) {  // 0: dK (carries sm_scale), 1: dV
+          const float mul = g ? 1.0f : p.sm_scale;
+          uint8_t* box = stg + g * 4096;
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld32((g ? tm_dv : tm_dk) + lane_addr + c, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              uint32_t wv[4];
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                wv[k] = pack2<BF16>(__uint_as_float(o[8 * ch + 2 * k]) * mul, __uint_as_float(o[8 * ch + 2 * k + 1]) * mul);
+              *reinterpret_cast<uint4*>(box + sw128_offset(lane, (c >> 3) + ch)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+            }
+          }
+        }
+        tc_fence_before();
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(acc_free);
+          const int row0 = item.blk * BLK + quarter * 32;
+          tma_store_4d(&map_dk, stg, 0, row0, item.h, item.z);
+          tma_store_4d(&map_dv, stg + 4096, 0, row0, item.h, item.z);
+          tma_store_commit();
+        }
+      };
       for (int t = item.t_lo; t < item.t_hi; ++t, ++cnt) {
+        // dK and dV are final once the last step's dK product is done, before its dQ product: they
+        // go first, so that the next item's first dV product (issued as soon as its P is there) does
+        // not wait for the accumulators
+        if (t == item.t_hi - 1) write_dk_dv();
         mbar_wait(dq_full, cnt & 1u, p.status, SITE_BWD_ACC_FULL);
         if (quarter == 0 && lane == 0) B200_TRACE_EVENT(p.status, 3, 7);
         tc_fence_after();
@@ -348,7 +389,7 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         __syncwarp();
         if (lane == 0) {
           mbar_arrive(dq_free);
-          tma_store_wait_read<0>();  // the previous reduce-adds have read the staging buffer
+          tma_store_wait_read<0>();  // the previous reduce-adds (or the dK / dV stores) have read the staging buffer
         }
         __syncwarp();
 #pragma unroll
@@ -366,41 +407,6 @@ attn_bwd_fused_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
           tma_store_commit();
         }
         if (quarter == 0 && lane == 0) B200_TRACE_EVENT(p.status, 3, 8);
-      }
-      // the item's dK and dV: this warp's 32 rows, 64 columns each = one box of 128-byte lines per
-      // gradient, through the same two staging boxes
-      mbar_wait(acc_full, n & 1u, p.status, SITE_BWD_ACC_FULL);
-      tc_fence_after();
-      if (lane == 0) tma_store_wait_read<0>();  // the last reduce-adds have read the staging boxes
-      __syncwarp();
-#pragma unroll 1
-      for (int g = 0; g < 2; ++g) {  // 0: dK (carries sm_scale), 1: dV
-        const float mul = g ? 1.0f : p.sm_scale;
-        uint8_t* box = stg + g * 4096;
-#pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
-          uint32_t o[32];
-          tmem_ld32((g ? tm_dv : tm_dk) + lane_addr + c, o);
-          tmem_ld_wait();
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t wv[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              wv[k] = pack2<BF16>(__uint_as_float(o[8 * ch + 2 * k]) * mul, __uint_as_float(o[8 * ch + 2 * k + 1]) * mul);
-            *reinterpret_cast<uint4*>(box + sw128_offset(lane, (c >> 3) + ch)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-          }
-        }
-      }
-      tc_fence_before();
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(acc_free);
-        const int row0 = item.blk * BLK + quarter * 32;
-        tma_store_4d(&map_dk, stg, 0, row0, item.h, item.z);
-        tma_store_4d(&map_dv, stg + 4096, 0, row0, item.h, item.z);
-        tma_store_commit();
       }
     }
     if (lane == 0) tma_store_wait_read<0>();  // the staging buffers have been read: the CTA may exit, the writes land on their own
