@@ -610,9 +610,9 @@ def per_config_roofline(cfgs, pk):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemm_kernel<256,256,3> launch on this workload
-# (879.5 MB + 120.0 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md, taken at commit
-# b57e099; the kernel's main loop and rasterisation have not changed since); algorithmic: 402.7 MB
-TRAFFIC_BYTES_PER_LAUNCH = 999_518_208
+# (882.2 MB + 131.6 MB, ncu --set full capture summarised in profiles/gemm_fp16_8192.md, taken at commit
+# bdaa51d); algorithmic: 402.7 MB
+TRAFFIC_BYTES_PER_LAUNCH = 1_013_782_784
 
 
 def main():
