@@ -295,10 +295,44 @@ def other_configs(torch, tb, dev):
         ms = statistics.median(ts)
         return {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1)}
 
+    def timed_unrolled(fn, flops, rep_ms=20.0, max_repeat=200):
+        """the reference's do_bench_cudagraph recipe (python/triton/testing.py:19-81): one CUDA graph of
+        n_repeat = rep_ms / estimate unrolled calls (capped at max_repeat here), no cache flush between
+        them, mean of 10 replays; what its attention benchmark and autotuner time with"""
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+
+        def capture(n):
+            side.wait_stream(torch.cuda.current_stream())
+            cg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(cg, stream=side):
+                for _ in range(n):
+                    fn()
+            torch.cuda.current_stream().wait_stream(side)
+            return cg
+
+        def replay_ms(cg):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            cg.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1)
+
+        one = capture(1)
+        replay_ms(one)
+        n = max(1, min(max_repeat, int(rep_ms / max(replay_ms(one), 1e-4))))
+        cg = capture(n)
+        ms = statistics.mean(replay_ms(cg) / n for _ in range(10))
+        return {"ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "n_repeat": n}
+
     a = torch.randn(512, 512, generator=g).half().to(dev)
     b = torch.randn(512, 512, generator=g).half().to(dev)
     out["c1_matmul_fp16_512"] = timed(lambda: tb.matmul(a, b), 2.0 * 512 ** 3)
     out["c1_matmul_fp16_512_cudagraph"] = timed(lambda: tb.matmul(a, b), 2.0 * 512 ** 3, graph=True)
+    out["c1_matmul_fp16_512_do_bench_cudagraph"] = timed_unrolled(lambda: tb.matmul(a, b), 2.0 * 512 ** 3)
     a8, sa = tb.quantize_e4m3(torch.randn(M, K, generator=g).to(dev))
     b8, sb = tb.quantize_e4m3(torch.randn(K, N, generator=g).to(dev))
     out["c3_matmul_fp8_8192_scaled_bf16"] = timed(lambda: tb.matmul(a8, b8, scale_a=sa, scale_b=sb), 2.0 * M * N * K)
@@ -323,6 +357,7 @@ def other_configs(torch, tb, dev):
     out["c5_fwd_bwd_two_kernel_backward"] = timed(lambda: fwd_bwd(False), fl * 3.5)
     out["c5_attn_fwd_bwd_cudagraph"] = timed(lambda: fwd_bwd(True), fl * 3.5, graph=True)
     out["c5_fwd_bwd_two_kernel_backward_cudagraph"] = timed(lambda: fwd_bwd(False), fl * 3.5, graph=True)
+    out["c5_attn_fwd_bwd_do_bench_cudagraph"] = timed_unrolled(lambda: fwd_bwd(True), fl * 3.5, max_repeat=100)
     out["c5_bwd_only_two_kernel"] = timed(lambda: tb.attention_backward(q, k, v, o, Mst, do, True, 0.5, one_pass=False), fl * 2.5)
     del q, k, v, do, o, Mst
     # rows beyond the five configs: the widened matmul / attention entry points
@@ -606,6 +641,9 @@ def per_config_roofline(cfgs, pk):
         "c5_bwd": entry("c5_bwd_only", pk["burst"], meas),
         "c5_two_kernel_backward": entry("c5_fwd_bwd_two_kernel_backward", pk["burst"], meas),
         "c5_cudagraph": entry("c5_attn_fwd_bwd_cudagraph", pk["burst"], meas),
+        # the reference's own timing recipe for these two (do_bench_cudagraph: unrolled graph, warm L2)
+        "c1_do_bench_cudagraph": entry("c1_matmul_fp16_512_do_bench_cudagraph", pk["burst"], meas),
+        "c5_do_bench_cudagraph": entry("c5_attn_fwd_bwd_do_bench_cudagraph", pk["burst"], meas),
     }
 
 

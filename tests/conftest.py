@@ -9,6 +9,13 @@ for p in (ROOT, os.path.join(ROOT, "tests", "golden")):
         sys.path.insert(0, p)
 
 
+# The suite asserts the library's defaults, among them that the default backward is bitwise
+# repeatable: settings of the caller's shell that change a default (the opt-in one-pass backward, a
+# forced tile shape) are not carried into the tests.
+for _var in ("B200_ATTN_BWD_ONEPASS", "B200_GEMM_TILE", "B200_GEMM_PAIR_STAGES", "B200_GEMM_PLAIN"):
+    os.environ.pop(_var, None)
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
 
