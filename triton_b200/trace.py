@@ -140,6 +140,12 @@ def main():
         tb.attention_backward(q, k, v, o, M, do, causal, sm, one_pass=one)
     t = read()
     print(f"{args.kernel} Z{Z} H{H} N{N} D{D} causal={causal}: CTA 0, mean SM clocks since the previous trace point")
+    if args.kernel == "fwd" and os.environ.get("B200_TRACE_RAW"):  # the timeline itself: clocks since the CTA's first event
+        firsts = [int(t[r][0][1]) for r in range(REGIONS) if t[r][0][0] or t[r][0][1]]
+        t_min = min(firsts) if firsts else 0
+        for region in (0, 1, 2):
+            ev = [(int(tag), (int(clk) - t_min) & 0xFFFFFFFF) for tag, clk in t[region].tolist() if tag or clk][:int(os.environ["B200_TRACE_RAW"])]
+            print(f"  region {region}: " + " ".join(f"{tag:x}@{clk}" for tag, clk in ev))
     if args.kernel == "fwd":
         for region, label in ((0, "softmax warp 0 of tile 0"), (1, "softmax warp 0 of tile 1")):
             print(f"  {label}")
