@@ -451,16 +451,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int c = 0; c < BLK; c += 32) {
           if (c + 32 < BLK) tmem_ld32(tm_s[i] + lane_addr + c + 32, r + c + 32);
           if (need_mask) {
+            // columns of this chunk that the row may see: below N and, when causal, up to the row itself
+            const int lim = min(p.N, p.causal ? row + 1 : p.N) - (col0 + c);
 #pragma unroll
-            for (int k = 0; k < 32; ++k) {
-              const int col = col0 + c + k;
-              const bool ok = (col < p.N) && (!p.causal || col <= row);
-              if (!ok) r[c + k] = __float_as_uint(-INFINITY);
-            }
+            for (int k = 0; k < 32; ++k)
+              if (k >= lim) r[c + k] = __float_as_uint(-INFINITY);
           }
 #pragma unroll
-          for (int u = 0; u < 16; ++u)
-            mx4[u] = fmaxf(mx4[u], fmaxf(__uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1])));
+          for (int u = 0; u < 16; ++u)  // three-input maximum: one instruction per column pair
+            mx4[u] = max3(mx4[u], __uint_as_float(r[c + 2 * u]), __uint_as_float(r[c + 2 * u + 1]));
           if (c + 32 < BLK) tmem_ld_wait32(r + c + 32);
         }
 #pragma unroll
