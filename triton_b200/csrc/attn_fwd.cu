@@ -22,7 +22,7 @@
 //   warp 9            TMA producer: Q tiles once, then K_0, V_0, K_1, V_1 ... through a ring.
 //   warps 10-15       lend their registers: the CTA's 64K registers are re-divided at run time
 //                     (setmaxnreg) so that a softmax thread can hold a whole 128-column score row
-//                     without spilling (208 registers; with ten warps the limit was 168 and the
+//                     without spilling (216 registers; with ten warps the limit was 168 and the
 //                     row spilled to local memory, an L2 round trip per value).
 // The kernel is persistent: one CTA per SM takes work items (256 query rows of one head) from an
 // atomic counter, head-major and heavy-first, so a head's K/V stay in L2, causal work balances, and
@@ -44,8 +44,8 @@ namespace {
 constexpr int BLK = 128;           // rows of a Q tile and of a K/V block
 constexpr int FWD_THREADS = 512;   // 8 softmax warps, MMA warp, TMA warp, 6 warps that only lend their registers
 // registers per thread after the re-division; one warp of each warpgroup shares a scheduler's 16K
-// registers: (2 * 208 + 72 + 24) * 32 lanes = 16384
-constexpr int REGS_SOFTMAX = 208, REGS_MMA_TMA = 72, REGS_IDLE = 24;
+// registers: (2 * 216 + 56 + 24) * 32 lanes = 16384
+constexpr int REGS_SOFTMAX = 216, REGS_MMA_TMA = 56, REGS_IDLE = 24;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 // Column pairs out of every 8 whose exp2 is computed by a cubic on the FMA pipe (0: all on the
