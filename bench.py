@@ -653,6 +653,67 @@ def per_config_roofline(cfgs, pk):
 TRAFFIC_BYTES_PER_LAUNCH = 1_013_782_784
 
 
+def run_sweep(name):
+    """The ranges of the reference's own benchmark plots, one JSON line per point (not part of the
+    driver's contract; BASELINE.md quotes these).  "matmul": square fp16 problems M = N = K = 128 i,
+    i = 2 .. 32, against cuBLAS (python/tutorials/03-matrix-multiplication.py:399-420).
+    "attention": BATCH 4, N_HEADS 32, N_CTX 2^10 .. 2^14, HEAD_DIM 64 and 128, causal and not, forward
+    and backward, fp16 (python/tutorials/06-fused-attention.py:566-620; FLOP count as there: 4 B H N^2 D,
+    halved when causal, x 2.5 for the backward).  Timing as the reference's do_bench does it: an L2
+    flush before every repetition, CUDA events, median."""
+    import torch
+    import triton_b200 as tb
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def med_ms(fn, reps):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    if name == "matmul":
+        for i in range(2, 33):
+            n = 128 * i
+            a = (torch.randn(n, n, generator=g, device=dev) / n ** 0.5).half()
+            b = (torch.randn(n, n, generator=g, device=dev) / n ** 0.5).half()
+            c = torch.empty(n, n, dtype=torch.float16, device=dev)
+            ours = med_ms(lambda: tb.matmul(a, b, out=c, out_dtype=torch.float16), 20)
+            cub = med_ms(lambda: torch.matmul(a, b, out=c), 20)
+            print(json.dumps({"sweep": "matmul", "M=N=K": n, "ms": round(ours, 4), "tflops": round(2.0 * n ** 3 / ours / 1e9, 1),
+                              "cublas_ms": round(cub, 4), "cublas_tflops": round(2.0 * n ** 3 / cub / 1e9, 1)}), flush=True)
+        return
+    Z, H = 4, 32
+    for D in (64, 128):
+        for causal in (True, False):
+            for n_ctx in (1024, 2048, 4096, 8192, 16384):
+                # the reference benchmark's data: unit-variance q, k, v and sm_scale = 1.3 (sharply peaked rows)
+                q, k, v, do = (torch.randn(Z, H, n_ctx, D, generator=g, device=dev).half() for _ in range(4))
+                sm = 1.3
+                fl = 4.0 * Z * H * n_ctx * n_ctx * D * (0.5 if causal else 1.0)
+                reps = 10 if n_ctx <= 4096 else 4
+                fwd = med_ms(lambda: tb.attention_forward(q, k, v, causal, sm), reps)
+                o, m = tb.attention_forward(q, k, v, causal, sm)
+                bwd = med_ms(lambda: tb.attention_backward(q, k, v, o, m, do, causal, sm), reps)
+                row = {"sweep": "attention", "HEAD_DIM": D, "causal": causal, "N_CTX": n_ctx,
+                       "fwd_ms": round(fwd, 4), "fwd_tflops": round(fl / fwd / 1e9, 1),
+                       "bwd_ms": round(bwd, 4), "bwd_tflops": round(2.5 * fl / bwd / 1e9, 1)}
+                if D == 64:
+                    one = med_ms(lambda: tb.attention_backward(q, k, v, o, m, do, causal, sm, one_pass=True), reps)
+                    row.update({"bwd_one_pass_ms": round(one, 4), "bwd_one_pass_tflops": round(2.5 * fl / one / 1e9, 1)})
+                print(json.dumps(row), flush=True)
+                del q, k, v, do, o, m
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -662,6 +723,8 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the short timings of configs 1, 3, 4, 5")
     ap.add_argument("--profile", default=None, choices=["c2", "c3", "c4", "c5", "c5two", "fp8attn", "grouped", "skinny"],
                     help="run three launches of one configuration and exit (for ncu captures)")
+    ap.add_argument("--sweep", default=None, choices=["matmul", "attention"],
+                    help="the ranges of the reference's benchmark plots, one JSON line per point, and exit")
     args = ap.parse_args()
     # torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU arm and the cpu_baseline leg are meant to
     # use every host core, and BLAS reads the variable when numpy is first imported (below, lazily)
@@ -672,7 +735,9 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
-    if args.profile:
+    if args.sweep:
+        run_sweep(args.sweep)
+    elif args.profile:
         run_profile_case(args.profile)
     elif args.impl == "reference":
         run_reference(args, rank, world)

@@ -46,7 +46,12 @@ constexpr int FWD_THREADS = 512;   // 8 softmax warps, MMA warp, TMA warp, 6 war
 // registers per thread after the re-division; one warp of each warpgroup shares a scheduler's 16K
 // registers: (2 * 216 + 56 + 24) * 32 lanes = 16384
 constexpr int REGS_SOFTMAX = 216, REGS_MMA_TMA = 56, REGS_IDLE = 24;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// Lazy rescale: the accumulator and the row sum keep their reference point m_ref until the running
+// maximum has grown past it by more than this many log2 units, so P may reach 2^threshold: 15 for an
+// fp16 P (largest finite value 65504), 60 for bf16 (fp32 range; the row sum of 2^14 such values and the
+// accumulator stay far below the fp32 limit).  The rounding of P is relative, so its bits do not
+// depend on the reference point as long as it stays in range.
+template <bool BF16> constexpr float kRescaleThreshold = BF16 ? 60.0f : 15.0f;
 
 // Column pairs out of every 8 whose exp2 is computed by a cubic on the FMA pipe (0: all on the
 // special-function unit).
@@ -487,10 +492,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         // rescales if any of its rows has to)
         // true on the first block (m_ref = -inf).  The 8-bit forward follows the exact running maximum,
         // as the reference does: the 2-bit mantissa of P makes its rounding depend on the scale
-        const bool grow = FP8 ? (m_new > m_ref) : ((m_new - m_ref) > kRescaleThreshold);
+        const bool grow = FP8 ? (m_new > m_ref) : ((m_new - m_ref) > kRescaleThreshold<BF16>);
         if (__any_sync(0xffffffffu, grow)) {
-          const float alpha = grow ? ex2(m_ref - m_new) : 1.f;  // 0 on the first block
-          if (grow) { m_ref = m_new; l *= alpha; }
+          // every row of the warp moves its reference point to its exact running maximum (this block
+          // included): the pass over O is paid for by the row that had to move, and the others start
+          // their next window from zero lag.  (Leaving 6 log2 units of headroom above the maximum as
+          // well bought another 2-3 % on sharply peaked scores; not taken: it costs P 6 bits of range.)
+          const float m_to = FP8 ? m_new : m_true;
+          const float alpha = (FP8 && !grow) ? 1.f : ex2(m_ref - m_to);  // 0 on the first block
+          if (!FP8 || grow) { m_ref = m_to; l *= alpha; }
           if (j > 0) {
             wait_pv();
 #pragma unroll 1
