@@ -168,7 +168,8 @@ B200_API int b200_grouped_matmul_run(b200_stream_t stream, const void* workspace
  * m: contiguous [Z, H, N] fp32.
  * dtype E5M2 is the reference's 8-bit forward (06-fused-attention.py:38-40, 66-69, 127, 609-615):
  * q, k, v and o are e5m2, both products run on 8-bit MMAs, P is converted to e5m2 (round to
- * nearest even, saturating) before the second product and O is stored as e5m2.  D must be 128;
+ * nearest even, saturating) before the second product and O is stored as e5m2.  D must be 64 (the
+ * reference's own fp8 benchmark shape, :570) or 128;
  * q, k, o need a d stride of 1 and other strides that are multiples of 16 elements; v must have its
  * KEY dimension contiguous (stride_v[2] == 1, the `v.permute(0, 1, 3, 2).contiguous().permute(0,
  * 1, 3, 2)` layout the reference gives an fp8 V) and stride_v[3] a multiple of 16. */

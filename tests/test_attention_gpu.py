@@ -337,7 +337,7 @@ def test_config5_full_size_forward_backward():
 @pytest.mark.skipif(not hasattr(torch, "float8_e5m2"), reason="torch without float8_e5m2")
 @pytest.mark.parametrize("causal", [True, False])
 @pytest.mark.parametrize("N,sm_scale,D", [(512, 0.0884, 128), (208, 0.0884, 128), (1024, 1.3, 128), (2048, 1.3, 128),
-                                          (1024, 1.3, 64), (384, 0.125, 64)])
+                                          (1024, 1.3, 64), (384, 0.125, 64), (208, 0.125, 64), (256, 0.18, 32)])
 def test_forward_e5m2(causal, N, sm_scale, D):
     """The reference's 8-bit forward (06-fused-attention.py:66-69, 609-615): e5m2 q, k, v (v with
     the key dimension contiguous), P converted to e5m2, e5m2 output.  The reference has no test for
@@ -345,8 +345,8 @@ def test_forward_e5m2(causal, N, sm_scale, D):
     autotune choices; the 2-bit mantissa of P makes the result depend on the block-wise running
     maximum, i.e. on BLOCK_N): relative Frobenius error <= 2e-2, in fact all but a few elements in
     a million are bit-identical.  Both are also compared with exact fp64 attention.  Head dim 64 is
-    the shape of the reference's own fp8 benchmark (:570); it runs on the head-dim-128 kernel with
-    zero columns appended."""
+    the shape of the reference's own fp8 benchmark (:570) and has a kernel of its own (rows of 64
+    bytes); head dim 32 runs on it with zero columns appended."""
     Z, H = 1, 2
     g = torch.Generator().manual_seed(N + int(causal) + D)
     q, k, v = ((torch.randn(Z, H, N, D, generator=g) * 0.5).to(torch.float8_e5m2) for _ in range(3))
@@ -382,14 +382,18 @@ def test_forward_e5m2(causal, N, sm_scale, D):
 @pytest.mark.skipif(not hasattr(torch, "float8_e5m2"), reason="torch without float8_e5m2")
 def test_forward_e5m2_errors():
     x = torch.zeros(1, 1, 128, 256, device=DEV).to(torch.float8_e5m2)
-    with pytest.raises(AssertionError, match="head dim 128"):
+    with pytest.raises(AssertionError, match="head dims 64 and 128"):
         triton_b200.attention_forward(x, x, x, True, 0.5)
     s4 = _lib.strides4
-    x64 = torch.zeros(1, 1, 128, 64, device=DEV).to(torch.float8_e5m2)
     m = torch.zeros(1, 1, 128, device=DEV)
-    code = _lib.lib().b200_attention_fwd(None, *([x64.data_ptr()] * 4), m.data_ptr(), 1, 1, 128, 64, *([s4(x64)] * 4),
+    code = _lib.lib().b200_attention_fwd(None, *([x.data_ptr()] * 4), m.data_ptr(), 1, 1, 128, 256, *([s4(x)] * 4),
                                          0.5, 1, _lib.E5M2)
-    assert code == _lib.ERR_UNSUPPORTED and "head dim 128" in _lib.last_error()  # the C entry point itself does not pad
+    assert code == _lib.ERR_UNSUPPORTED and "head dims 64 and 128" in _lib.last_error()
+    # the C entry point itself does not pad: head dim 32 is the wrapper's business
+    x32 = torch.zeros(1, 1, 128, 32, device=DEV).to(torch.float8_e5m2)
+    code = _lib.lib().b200_attention_fwd(None, *([x32.data_ptr()] * 4), m.data_ptr(), 1, 1, 128, 32, *([s4(x32)] * 4),
+                                         0.5, 1, _lib.E5M2)
+    assert code in (_lib.ERR_UNSUPPORTED, _lib.ERR_ARG)
 
 
 def test_long_sequence_forward_sampled_rows():

@@ -265,8 +265,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       constexpr int FMT = (BF16 || FP8) ? 1 : 0;  // kind::f16: bf16 = 1; kind::f8f6f4: e5m2 = 1
       constexpr uint32_t IDESC_S = make_idesc(FMT, FMT, 0, 0, 128, BLK);  // Q (K-major) x K (K-major)
       constexpr uint32_t IDESC_O = make_idesc(FMT, FMT, 0, FP8 ? 0 : 1, 128, D);  // P (TMEM) x V (N-major; K-major when 8-bit)
-      const uint64_t dq0 = smem_desc_sw128(smem_u32(sq), 0, 1024);
-      const uint64_t dk0 = smem_desc_sw128(smem_u32(skv), 0, 1024);
+      // Q and K: rows of 128 bytes (64 16-bit or 128 8-bit elements per box), 128-byte swizzle; the
+      // 8-bit forward at head dim 64 has rows of 64 bytes, 64-byte swizzle (8-row groups 512 B apart)
+      constexpr bool ROW64 = FP8 && D == 64;
+      const uint64_t dq0 = ROW64 ? smem_desc_sw64(smem_u32(sq), 0, 512) : smem_desc_sw128(smem_u32(sq), 0, 1024);
+      const uint64_t dk0 = ROW64 ? smem_desc_sw64(smem_u32(skv), 0, 512) : smem_desc_sw128(smem_u32(skv), 0, 1024);
       const uint64_t dv0 = smem_desc_sw128(smem_u32(skv), FP8 ? 0 : BLK * 128, 1024);  // LBO: next 64-column box
       uint32_t s = 0, ph = 0;        // ring position of the next unconsumed K / V block
       uint32_t pcnt[2] = {0, 0};     // blocks of tile i whose P has been consumed (parity of p_full)
@@ -597,7 +600,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         uint8_t* stg = sstage + warp * Cfg::STG_BYTES;
         const int warp_row0 = qb * ITEM_ROWS + i * BLK + quarter * 32;
         if constexpr (FP8) {
-          // 8-bit O: the 128 columns of a row are one 128-byte line of the staging buffer
+          // 8-bit O: the D columns of a row are one line of the staging buffer
           if (lane == 0) tma_store_wait_read<0>();
           __syncwarp();
 #pragma unroll 1
@@ -612,7 +615,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               for (int k = 0; k < 4; ++k)
                 wv[k] = pack4_e5m2(__uint_as_float(o[16 * ch + 4 * k]) * inv_l, __uint_as_float(o[16 * ch + 4 * k + 1]) * inv_l,
                                    __uint_as_float(o[16 * ch + 4 * k + 2]) * inv_l, __uint_as_float(o[16 * ch + 4 * k + 3]) * inv_l);
-              *reinterpret_cast<uint4*>(stg + sw128_offset(lane, (c >> 4) + ch)) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+              // one line of the staging buffer per row: 128 bytes (128-byte swizzle) or, at head dim 64, 64 bytes
+              const uint32_t off = (D == 64) ? sw64_offset(lane, (c >> 4) + ch) : sw128_offset(lane, (c >> 4) + ch);
+              *reinterpret_cast<uint4*>(stg + off) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
             }
           }
           fence_proxy_async_smem();
@@ -707,12 +712,12 @@ int launch_fwd_t(DeviceCtx* ctx, cudaStream_t stream, const CUtensorMap& tq, con
 }  // namespace
 
 bool encode_rows_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
-                     int64_t sn, int box_cols, int box_rows, bool swizzle128) {
+                     int64_t sn, int box_cols, int box_rows, int swizzle) {
   uint64_t dims[4] = {(uint64_t)D, (uint64_t)N, (uint64_t)H, (uint64_t)Z};
   const uint64_t eb = (uint64_t)dtype_bytes(dtype);
   uint64_t strides[3] = {(uint64_t)sn * eb, (uint64_t)sh * eb, (uint64_t)sz * eb};
   uint32_t box[4] = {(uint32_t)box_cols, (uint32_t)box_rows, 1, 1};
-  return encode_tmap(out, dtype, 4, base, dims, strides, box, swizzle128);
+  return encode_tmap(out, dtype, 4, base, dims, strides, box, swizzle);
 }
 
 // the operand maps: boxes of 64 columns (128 bytes, swizzled) x box_rows rows
@@ -726,16 +731,17 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
                     const int64_t* so, float sm_scale, int causal, int dtype) {
   if (dtype == B200_E5M2) {
     // 8-bit forward: rows of 128 bytes; V is addressed as [D rows][N keys] (keys contiguous)
-    if (D != 128) return fail(B200_ERR_UNSUPPORTED, "the 8-bit forward has a kernel for head dim 128 only");
+    if (D != 128 && D != 64) return fail(B200_ERR_UNSUPPORTED, "the 8-bit forward has kernels for head dims 64 and 128");
+    const int sw = (D == 64) ? 2 : 1;  // rows of 64 bytes take the 64-byte swizzle
     if (sq[3] != 1 || sk[3] != 1 || so[3] != 1) return fail(B200_ERR_UNSUPPORTED, "8-bit q, k, o need a contiguous head dimension");
     if (sv[2] != 1 && N != 1) return fail(B200_ERR_UNSUPPORTED, "an 8-bit v needs its key dimension contiguous (stride_v[2] == 1)");
     CUtensorMap tq8, tk8, tv8, to8;
-    if (!encode_rows_map(&tq8, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], 128, BLK, true)) return B200_ERR_UNSUPPORTED;
-    if (!encode_rows_map(&tk8, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], 128, BLK, true)) return B200_ERR_UNSUPPORTED;
-    // "rows" of the V map are head-dim indices, "columns" are keys
-    if (!encode_rows_map(&tv8, dtype, v, Z, H, D, N, sv[0], sv[1], sv[3], 128, 128, true)) return B200_ERR_UNSUPPORTED;
+    if (!encode_rows_map(&tq8, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], D, BLK, sw)) return B200_ERR_UNSUPPORTED;
+    if (!encode_rows_map(&tk8, dtype, k, Z, H, N, D, sk[0], sk[1], sk[2], D, BLK, sw)) return B200_ERR_UNSUPPORTED;
+    // "rows" of the V map are head-dim indices, "columns" are keys: a block is D rows of 128 keys
+    if (!encode_rows_map(&tv8, dtype, v, Z, H, D, N, sv[0], sv[1], sv[3], 128, D, 1)) return B200_ERR_UNSUPPORTED;
     FwdParams p8{};
-    p8.o_tma = encode_rows_map(&to8, dtype, o, Z, H, N, D, so[0], so[1], so[2], 128, 32, true) ? 1 : 0;
+    p8.o_tma = encode_rows_map(&to8, dtype, o, Z, H, N, D, so[0], so[1], so[2], D, 32, sw) ? 1 : 0;
     if (!p8.o_tma) to8 = tq8;
     p8.o = o; p8.m = m; p8.row_max = row_max;
     p8.o_sz = so[0]; p8.o_sh = so[1]; p8.o_sn = so[2];
@@ -746,7 +752,8 @@ int launch_attn_fwd(DeviceCtx* ctx, cudaStream_t stream, const void* q, const vo
     p8.status = ctx->status;
     p8.sched_counter = next_sched_counter(ctx, stream);
     if (!p8.sched_counter) return B200_ERR_CUDA;
-    return launch_fwd_t<128, false, true>(ctx, stream, tq8, tk8, tv8, to8, p8);
+    return D == 64 ? launch_fwd_t<64, false, true>(ctx, stream, tq8, tk8, tv8, to8, p8)
+                   : launch_fwd_t<128, false, true>(ctx, stream, tq8, tk8, tv8, to8, p8);
   }
   CUtensorMap tq, tk, tv;
   if (!encode_qkv_map(&tq, dtype, q, Z, H, N, D, sq[0], sq[1], sq[2], BLK)) return B200_ERR_UNSUPPORTED;

@@ -172,7 +172,7 @@ int* next_sched_counter(DeviceCtx* ctx, cudaStream_t stream) {
 }
 
 bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
-                 const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+                 const uint64_t* strides_bytes, const uint32_t* box, int swizzle) {
   CUtensorMapDataType dt;
   switch (dtype) {
     case B200_F16: dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16; break;
@@ -211,7 +211,7 @@ bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const 
     }
   }
   CUresult r = g_encode(out, dt, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                        swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : (swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     fail(B200_ERR_UNSUPPORTED, "cuTensorMapEncodeTiled failed with CUresult %d (rank %d, dims %llu x %llu)", (int)r,
@@ -465,7 +465,7 @@ int b200_attention_fwd_stats(b200_stream_t stream, const void* q, const void* k,
     return fail(B200_ERR_ARG, "forward attention dtype must be F16, BF16 or E5M2");
   if (D != 64 && D != 128 && D != 256)
     return fail(B200_ERR_UNSUPPORTED, "head dim %d: the forward has kernels for 64, 128 and 256", D);
-  if (D == 256 && dtype == B200_E5M2) return fail(B200_ERR_UNSUPPORTED, "the 8-bit forward has a kernel for head dim 128 only");
+  if (D == 256 && dtype == B200_E5M2) return fail(B200_ERR_UNSUPPORTED, "the 8-bit forward has kernels for head dims 64 and 128");
   if (!(sm_scale > 0.f)) return fail(B200_ERR_ARG, "sm_scale must be positive");
   if (!stride_q || !stride_k || !stride_v || !stride_o) return fail(B200_ERR_ARG, "null stride array");
   if (dtype != B200_E5M2 && (stride_q[3] != 1 || stride_k[3] != 1 || stride_v[3] != 1 || stride_o[3] != 1))

@@ -227,6 +227,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// The same for rows of 64 bytes under the 64-byte swizzle (mode 4): a K-major operand's 8-row groups
+// are 512 B apart.  Used by the 8-bit attention forward at head dim 64 (64 one-byte elements per row).
+__device__ __forceinline__ uint64_t smem_desc_sw64(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)4 << 61;
+  return d;
+}
+
 // Instruction descriptor (32 bit) for kind::f16 and kind::f8f6f4, fp32 accumulator.
 //   bits 4-5 D format (1 = f32); 7-9 A format; 10-12 B format; 15 A is MN-major; 16 B is MN-major;
 //   17-22 N >> 3; 24-28 M >> 4.   Formats: kind::f16 0 = f16, 1 = bf16; kind::f8f6f4 0 = e4m3, 1 = e5m2.
@@ -562,6 +574,11 @@ __device__ __forceinline__ void ex2_cubic2(float x0, float x1, float& p0, float&
 // rows are 128 B and whose base is 1024-byte aligned (the pattern TMA SWIZZLE_128B writes)
 __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk) {
   return row * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+// the same for rows of 64 B under the 64-byte swizzle (TMA SWIZZLE_64B: address bits 4-5 are XORed
+// with bits 7-8, i.e. the chunk index (0..3) with bits 1-2 of the row); base 512-byte aligned
+__device__ __forceinline__ uint32_t sw64_offset(uint32_t row, uint32_t chunk) {
+  return row * 64u + ((chunk ^ ((row >> 1) & 3u)) << 4);
 }
 
 }  // namespace tb

@@ -38,9 +38,9 @@ int* next_sched_counter(DeviceCtx* ctx, cudaStream_t stream);
 int fail(int code, const char* fmt, ...);
 
 // Encode a tiled tensor map.  dims/strides innermost first; strides_bytes[0] is the stride of
-// dimension 1 (dimension 0 is contiguous).  swizzle128: 128-byte swizzle when true, none otherwise.
+// dimension 1 (dimension 0 is contiguous).  swizzle: 0 none, 1 (or true) 128-byte, 2 64-byte swizzle.
 bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
-                 const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128);
+                 const uint64_t* strides_bytes, const uint32_t* box, int swizzle);
 
 // cudaFuncAttributeMaxDynamicSharedMemorySize of `kernel`, set once per device; `done` is the
 // launcher's static per-device flag array.  Host threads may race here: setting the attribute twice
@@ -119,7 +119,7 @@ float* attn_bwd_scratch(DeviceCtx* ctx);
 // 4-D tensor map over [Z, H, N, D] (D contiguous): boxes of 64 columns x box_rows rows, 128-byte swizzle
 // 4-D map over a [Z, H, N, D] tensor (D contiguous) with boxes of box_cols x box_rows elements
 bool encode_rows_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
-                     int64_t sn, int box_cols, int box_rows, bool swizzle128);
+                     int64_t sn, int box_cols, int box_rows, int swizzle);
 bool encode_qkv_map(CUtensorMap* out, int dtype, const void* base, int Z, int H, int N, int D, int64_t sz, int64_t sh,
                     int64_t sn, int box_rows);
 

@@ -322,18 +322,18 @@ def attention_forward(q, k, v, causal, sm_scale, return_row_max=False):
         qp, kp, vp = (torch.nn.functional.pad(t, (0, 64 - D)) for t in (q, k, v))
         o, *stats = attention_forward(qp, kp, vp, causal, sm_scale, return_row_max)
         return (o[..., :D].contiguous(), *stats)
-    if fp8 and D in (16, 32, 64):
-        # the 8-bit kernel is built for head dim 128 (rows of 128 bytes); smaller head dims - 64 is the
-        # reference's own fp8 benchmark shape, 06-fused-attention.py:570 - get zero columns appended,
-        # which leave q k^T, P and the kept columns of O bit for bit what they are without them
-        pad8 = lambda t: torch.nn.functional.pad(t.view(torch.uint8), (0, 128 - D)).view(torch.float8_e5m2)
+    if fp8 and D in (16, 32):
+        # the 8-bit kernels are built for head dims 64 and 128 (rows of 64 / 128 bytes); smaller head dims
+        # get zero columns appended, which leave q k^T, P and the kept columns of O bit for bit what they
+        # are without them
+        pad8 = lambda t: torch.nn.functional.pad(t.view(torch.uint8), (0, 64 - D)).view(torch.float8_e5m2)
         o, *stats = attention_forward(pad8(q), pad8(k), pad8(v), causal, sm_scale, return_row_max)
         return (o[..., :D].contiguous(), *stats)
     with _on_device(dev):
         if fp8:
             # the reference's fp8 forward (06-fused-attention.py:609-615) is given V with the key
             # dimension contiguous; any other V is brought into that layout first
-            assert D == 128, "the 8-bit forward has a kernel for head dim 128 (smaller ones are padded above)"
+            assert D in (64, 128), "the 8-bit forward has kernels for head dims 64 and 128 (smaller ones are padded above)"
             if v.stride(2) != 1:
                 v = v.permute(0, 1, 3, 2).contiguous().permute(0, 1, 3, 2)
             o = torch.empty((Z, H, N, D), device=dev, dtype=q.dtype)
