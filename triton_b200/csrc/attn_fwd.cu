@@ -518,6 +518,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
         if (traced) B200_TRACE_EVENT(p.status, i, 3);
+        wait_pv();  // (head dim 64) before the exponential loop, not inside it: a wait in the unrolled loop keeps the compiler from interleaving its chunks
         const float neg_m = -m_ref;
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
         [[maybe_unused]] uint64_t sum2[2] = {pk2(0.f, 0.f), pk2(0.f, 0.f)};
@@ -562,7 +563,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                                  __uint_as_float(r[c + 4 * k + 2]), __uint_as_float(r[c + 4 * k + 3]));
             tmem_st8(tm_s[i] + lane_addr + (c >> 2), wv);
           } else {
-            if (c == 0) wait_pv();  // as late as possible: the first 32 exponentials are done
             tmem_st16(tm_p(i) + lane_addr + (c >> 1), wv);
           }
           if (c == 32 || c == 96) {  // a half of P is complete: its four P V MMAs may start
