@@ -666,8 +666,8 @@ TRAFFIC_BYTES_PER_LAUNCH = 1_013_782_784
 
 
 def run_sweep(name):
-    """The ranges of the reference's own benchmark plots, one JSON line per point (not part of the
-    driver's contract; BASELINE.md quotes these).  "matmul": square fp16 problems M = N = K = 128 i,
+    """The ranges of the reference's own benchmark plots, one JSON line per point (beside the one-line
+    report of the default run).  "matmul": square fp16 problems M = N = K = 128 i,
     i = 2 .. 32, against cuBLAS (python/tutorials/03-matrix-multiplication.py:399-420).
     "attention": BATCH 4, N_HEADS 32, N_CTX 2^10 .. 2^14, HEAD_DIM 64 and 128, causal and not, forward
     and backward, fp16 (python/tutorials/06-fused-attention.py:566-620; FLOP count as there: 4 B H N^2 D,
