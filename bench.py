@@ -590,6 +590,31 @@ def run_ours(args, rank, local_rank, world):
         burst = (ms < 1000.0) and not capped
         peak = pk["burst"] if burst else pk["sustained"]
         sustained = sustained_loop(step, torch, local_rank) if world == 1 else None
+        # cuBLAS (torch.matmul, the library GEMM - not part of the product path) on the same operands,
+        # the same number of launches, after the same idle: what the same GPU gives the vendor library
+        # in this process, and the SM clock it runs at (the clock under a saturated tensor pipe drops
+        # within milliseconds whichever kernel runs; no throttle reason is reported for it)
+        cublas_same = None
+        if world == 1:
+            torch.cuda.synchronize()
+            time.sleep(0.25)
+            for _ in range(3):
+                torch.matmul(a, b, out=c)
+            cs = ClockSampler(local_rank)
+            cs.start()
+            torch.cuda.synchronize()
+            cs.mark()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.steps):
+                torch.matmul(a, b, out=c)
+            e1.record()
+            torch.cuda.synchronize()
+            cs.mark()
+            cc = cs.stop()
+            cms = e0.elapsed_time(e1) / args.steps
+            cublas_same = {"tflops": flops / cms / 1e9, "ms_per_launch": cms, "launches": args.steps,
+                           "sm_mhz_median": cc.get("sm_mhz"), "reasons": cc.get("reasons")}
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": per_launch_ms, "higher_is_better": True, "scaling": "weak",
@@ -614,6 +639,7 @@ def run_ours(args, rank, local_rank, world):
                          "frac_of_sustained_peak": achieved / pk["sustained"],
                          "frac_of_nominal_2250": achieved / 2250.0,
                          "sustained": sustained,
+                         "cublas_same_process": cublas_same,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch (ncu capture of this
                          # workload, summarised in profiles/gemm_fp16_8192.md)
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH},
