@@ -62,7 +62,7 @@ def test_matmul_shapes_layouts(dtype, shape, b_layout):
     np.testing.assert_allclose(f32(got), want, rtol=tol, atol=tol)
 
 
-@pytest.mark.parametrize("tile", ["128064", "128128", "128256", "256256", "2256", "2512"])
+@pytest.mark.parametrize("tile", ["128064", "128128", "128192", "128256", "256192", "256256", "2256", "2512"])
 def test_every_tile_shape(monkeypatch, tile):
     monkeypatch.setenv("B200_GEMM_TILE", tile)
     g = torch.Generator().manual_seed(11)

@@ -423,7 +423,7 @@ __global__ void __launch_bounds__(64 + BM + (BM == 256 ? 32 : 0), 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
             const __grid_constant__ CUtensorMap tma_c, const GemmParams p) {
   constexpr uint32_t A_BYTES = BM * KBYTES, B_BYTES = BN * KBYTES, STAGE_BYTES = A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));  // a power of two
   constexpr int MH = BM / 128;                  // 128-row MMAs per K step
   constexpr uint32_t NACC = (MH == 1) ? 2 : 1;  // accumulator sets in TMEM
 
@@ -1309,7 +1309,7 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     return B200_OK;
   }
 
-  // Tile shape.  B200_GEMM_TILE forces one: 128064, 128128, 128256, 256256, or 2256 / 2512 for the CTA pair
+  // Tile shape.  B200_GEMM_TILE forces one: 128064, 128128, 128192, 128256, 256192, 256256, or 2256 / 2512 for the CTA pair
   // (256 x 256 / 256 x 512).
   auto tiles = [&](int bm_, int bn_) { return (long long)((M + bm_ - 1) / bm_) * ((N + bn_ - 1) / bn_); };
   int bm = 128, bn = 64;
@@ -1337,11 +1337,17 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     // 256 x 256 in a 55 % wave; 3584: 128 x 256).  The pair shapes (`cta_group::2`) never won a size:
     // 256 x 256 on a pair has the fill traffic per flop of a 128 x 256 tile, 256 x 512 has no second
     // accumulator; they stay selectable through B200_GEMM_TILE.
+    // (The 192-column shapes exist for the wave count: 2560^3 is 100 tiles of 256 x 256 - two thirds
+    // of the SMs - or 400 of 128 x 128 - 2.7 waves - but 140 of 256 x 192, one full wave.  They need
+    // 64-element TMA boxes of B to divide 192: not with an 8-bit N-major B.)
     struct Cand { int bm, bn; double kb_us, tile_us; };
-    const Cand cands[4] = {{256, 256, 0.68, 1.0}, {128, 256, 0.36, 0.3}, {128, 128, 0.21, 0.3}, {128, 64, 0.20, 0.3}};
+    const bool wide_ok = !(elt == 1 && b_mn);
+    const Cand cands[6] = {{256, 256, 0.68, 1.0}, {256, 192, 0.52, 0.9}, {128, 256, 0.36, 0.3},
+                           {128, 192, 0.29, 0.3}, {128, 128, 0.21, 0.3}, {128, 64, 0.20, 0.3}};
     const int num_k_est = (int)(((long long)K * elt + KBYTES - 1) / KBYTES);
     double best = 1e300;
     for (const Cand& cd : cands) {
+      if (cd.bn == 192 && !wide_ok) continue;
       const long long t = tiles(cd.bm, cd.bn);
       const long long waves = (t + ctx->sm_count - 1) / ctx->sm_count;
       const double est = (double)waves * (num_k_est * cd.kb_us + cd.tile_us);
@@ -1350,7 +1356,9 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
   }
   if (pair) { bm = 256; bn = 256 * pair_nb; }
   if (elt == 1 && b_mn && bn < 128) bn = 128;  // an MN-major box is 128 columns of 1-byte elements
-  if (!pair && !((bm == 128 && (bn == 64 || bn == 128 || bn == 256)) || (bm == 256 && bn == 256)))
+  if (!pair && bn == 192 && elt == 1 && b_mn)
+    return fail(B200_ERR_ARG, "B200_GEMM_TILE=%d: a 192-column tile cannot take an 8-bit N-major B", force);
+  if (!pair && !((bm == 128 && (bn == 64 || bn == 128 || bn == 192 || bn == 256)) || (bm == 256 && (bn == 192 || bn == 256))))
     return fail(B200_ERR_ARG, "B200_GEMM_TILE=%d is not a tile shape of this library", force);
   const int a_rows = pair ? 128 : bm;  // rows of A / columns of B that one CTA stages
   const int b_rows = pair ? 128 : bn;
@@ -1408,6 +1416,10 @@ int launch_gemm(DeviceCtx* ctx, cudaStream_t stream, const void* a, const void* 
     case 256:
       rc = (bm == 256) ? launch_tile<256, 256, 3>(ctx, stream, ta, tbm, tcm, p)
                        : launch_tile<128, 256, 4>(ctx, stream, ta, tbm, tcm, p);
+      break;
+    case 192:
+      rc = (bm == 256) ? launch_tile<256, 192, 3>(ctx, stream, ta, tbm, tcm, p)
+                       : launch_tile<128, 192, 5>(ctx, stream, ta, tbm, tcm, p);
       break;
     case 128: rc = launch_tile<128, 128, 6>(ctx, stream, ta, tbm, tcm, p); break;
     default: rc = launch_tile<128, 64, 7>(ctx, stream, ta, tbm, tcm, p); break;
