@@ -459,10 +459,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
     tmem_alloc(tmem_slot, TMEM_COLS);
     tmem_relinquish();
   }
+  // The TMA warp initialised the barriers itself and needs nothing from the others (not the TMEM
+  // base either): it only arrives at the CTA's start-up barrier and goes on to its first loads, which
+  // are then in flight while TMEM is allocated and the other warps wait here.
   tc_fence_before();
-  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("bar.arrive 1, %0;" ::"r"((int)blockDim.x) : "memory");
+  } else {
+    asm volatile("bar.sync 1, %0;" ::"r"((int)blockDim.x) : "memory");
+  }
   tc_fence_after();
-  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const uint32_t tmem_base = (warp == 0) ? 0u : *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
   if (warp == 0) {
     // TMA producer.  The warp stays converged and every box of a stage has a lane of its own (K-major
